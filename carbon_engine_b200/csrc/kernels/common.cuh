@@ -1,0 +1,56 @@
+// Shared declarations of the engine's CUDA kernels (sm_100a).
+//
+// Every launcher is an extern "C" function that takes raw device pointers and a stream, checks
+// the sizes it is given, and returns 0 or a negative code after storing a message that
+// ce_last_error() returns.  A launcher never allocates memory and never synchronises.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+#define CE_OK 0
+#define CE_ERR_SIZE -1      // a size this kernel refuses
+#define CE_ERR_CUDA -2      // the launch itself failed
+#define CE_ERR_ARG -3       // a null pointer or an unknown dtype
+
+// dtype codes shared with the Python side
+#define CE_F32 0
+#define CE_BF16 1
+
+extern "C" const char* ce_last_error();
+int ce_fail(int code, const char* fmt, ...);
+int ce_check_launch(const char* what);
+
+template <typename T> struct CeType;
+template <> struct CeType<float> {
+    static __device__ __forceinline__ float load(const float* p) { return *p; }
+    static __device__ __forceinline__ void store(float* p, float v) { *p = v; }
+};
+template <> struct CeType<__nv_bfloat16> {
+    static __device__ __forceinline__ float load(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+};
+
+// Sum over a block in a fixed order: warp shuffles down, then warp 0 adds the warp sums in index
+// order.  The result depends on blockDim only, never on the grid or on other rows.
+__device__ __forceinline__ float ce_block_sum(float v, float* scratch /* >= 32 floats */) {
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_down_sync(0xffffffffu, v, o);
+    int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = (blockDim.x + 31) >> 5;
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float total = 0.f;
+    for (int w = 0; w < nwarp; ++w) total += scratch[w];
+    return total;
+}
+
+__device__ __forceinline__ float ce_block_max(float v, float* scratch) {
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_down_sync(0xffffffffu, v, o));
+    int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = (blockDim.x + 31) >> 5;
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float m = scratch[0];
+    for (int w = 1; w < nwarp; ++w) m = fmaxf(m, scratch[w]);
+    return m;
+}

@@ -1,0 +1,254 @@
+// Memory-bound kernels of a decoder step: embedding gather, RMSNorm, the fused per-head
+// q/k norm + rotary embedding + paged K/V write, the residual add and SwiGLU.
+//
+// The residual stream is float32 in both precisions; norms, rotation and SiLU are computed in
+// float32 and rounded once at the store.  The reference gets these ops from its tensor library
+// one by one (src/model/layers.rs:140-146 rms_norm, :315-325 rope, :151 silu,
+// src/model/mod.rs:781-784 embedding gather, src/kvcache/mod.rs:371-372 K/V scatter).
+#include "common.cuh"
+
+// ---------------------------------------------------------------------------------------------
+// Embedding: x[t, :] = float(table[token[t], :])
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ tokens,
+                             float* __restrict__ x, int H, int V, int* __restrict__ status) {
+    int t = blockIdx.x;
+    int tok = tokens[t];
+    if (tok < 0 || tok >= V) {
+        if (threadIdx.x == 0) atomicExch(status, 1);
+        for (int j = threadIdx.x; j < H; j += blockDim.x) x[(size_t)t * H + j] = 0.f;
+        return;
+    }
+    const T* row = table + (size_t)tok * H;
+    for (int j = threadIdx.x; j < H; j += blockDim.x) x[(size_t)t * H + j] = CeType<T>::load(row + j);
+}
+
+extern "C" int ce_embed(const void* table, int dtype, const int* tokens, float* x, int T, int H, int V,
+                        int* status, cudaStream_t stream) {
+    if (T == 0) return CE_OK;
+    if (!table || !tokens || !x || !status) return ce_fail(CE_ERR_ARG, "ce_embed: null pointer");
+    if (dtype == CE_F32)
+        embed_kernel<float><<<T, 256, 0, stream>>>((const float*)table, tokens, x, H, V, status);
+    else if (dtype == CE_BF16)
+        embed_kernel<__nv_bfloat16><<<T, 256, 0, stream>>>((const __nv_bfloat16*)table, tokens, x, H, V, status);
+    else
+        return ce_fail(CE_ERR_ARG, "ce_embed: unknown dtype %d", dtype);
+    return ce_check_launch("ce_embed");
+}
+
+// ---------------------------------------------------------------------------------------------
+// RMSNorm over the last dimension: out[r, :] = x[row(r), :] * (1/sqrt(mean(x^2) + eps)) * w
+// One block of 256 threads per row, so the order of the sum depends on the width only.
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w, T* __restrict__ out,
+                               const int* __restrict__ rows, int H, float eps) {
+    __shared__ float scratch[32];
+    int r = blockIdx.x;
+    const float* xr = x + (size_t)(rows ? rows[r] : r) * H;
+    float ss = 0.f;
+    for (int j = threadIdx.x; j < H; j += blockDim.x) {
+        float v = xr[j];
+        ss = fmaf(v, v, ss);
+    }
+    ss = ce_block_sum(ss, scratch);
+    float inv = 1.0f / sqrtf(ss / (float)H + eps);
+    T* o = out + (size_t)r * H;
+    for (int j = threadIdx.x; j < H; j += blockDim.x) CeType<T>::store(o + j, xr[j] * inv * w[j]);
+}
+
+extern "C" int ce_rmsnorm(const float* x, const float* w, void* out, int out_dtype, const int* rows, int R, int H,
+                          float eps, cudaStream_t stream) {
+    if (R == 0) return CE_OK;
+    if (!x || !w || !out) return ce_fail(CE_ERR_ARG, "ce_rmsnorm: null pointer");
+    if (H <= 0) return ce_fail(CE_ERR_SIZE, "ce_rmsnorm: width %d", H);
+    if (out_dtype == CE_F32)
+        rmsnorm_kernel<float><<<R, 256, 0, stream>>>(x, w, (float*)out, rows, H, eps);
+    else if (out_dtype == CE_BF16)
+        rmsnorm_kernel<__nv_bfloat16><<<R, 256, 0, stream>>>(x, w, (__nv_bfloat16*)out, rows, H, eps);
+    else
+        return ce_fail(CE_ERR_ARG, "ce_rmsnorm: unknown dtype %d", out_dtype);
+    return ce_check_launch("ce_rmsnorm");
+}
+
+// ---------------------------------------------------------------------------------------------
+// Per-head q/k RMSNorm, rotary embedding, and the write of K and V into the paged cache.
+//
+// Input  qkv [T, (nh + 2*nkv) * d]: q heads, then k heads, then v heads (one GEMM output).
+// q heads are normalised and rotated in place.  k heads are normalised, rotated and stored at
+// the token's place in the K pool; v heads are copied to the V pool.  Pools are
+// [num_pages, nkv, page_size, d].  A token's place is found from its sequence's block-table row:
+// page = table[slot, pos / page_size], offset = pos % page_size.
+//
+// Order follows the reference: norm over the head (weight shared by all heads) BEFORE the
+// rotation (src/model/attention.rs:884-889); rotate-half pairing (i, i + rd/2)
+// (src/model/layers.rs:159, spelled out in src/kernels/qsa.cu:107-116); K is stored after norm and
+// rotation, V as projected (src/model/attention.rs:890).
+// ---------------------------------------------------------------------------------------------
+struct QkRopeArgs {
+    void* qkv;
+    void* k_pool;
+    void* v_pool;
+    const float* q_weight;   // [d] or null: no q norm
+    const float* k_weight;   // [d] or null: no k norm
+    const float* cos_table;  // [max_pos, rd/2] or null: no rotation
+    const float* sin_table;
+    const int* positions;    // [T]
+    const int* seq_of_token; // [T]
+    const int* seq_slot;     // [B]
+    const int* block_table;  // [slots, max_pages]
+    int* status;
+    int T, nh, nkv, d, rd, page_size, max_pages, num_pages, max_pos, write_kv;
+    float eps;
+};
+
+template <typename T>
+__global__ void qk_rope_kvwrite_kernel(QkRopeArgs a) {
+    extern __shared__ float sh[];     // d floats + 32 scratch
+    float* vals = sh;
+    float* scratch = sh + a.d;
+    int t = blockIdx.x, hh = blockIdx.y, j = threadIdx.x;
+    int d = a.d;
+    bool is_q = hh < a.nh, is_k = !is_q && hh < a.nh + a.nkv;
+    if (!is_q && !a.write_kv) return;
+    T* src = (T*)a.qkv + (size_t)t * (a.nh + 2 * a.nkv) * d + (size_t)hh * d;
+    float v = j < d ? CeType<T>::load(src + j) : 0.f;
+    int pos = a.positions[t];
+
+    T* dst = nullptr;
+    if (is_q) {
+        dst = src;
+    } else {
+        int slot = a.seq_slot[a.seq_of_token[t]];
+        int page = a.block_table[(size_t)slot * a.max_pages + pos / a.page_size];
+        if (page < 0 || page >= a.num_pages) {
+            if (j == 0) atomicExch(a.status, 2);
+            return;
+        }
+        int kvh = is_k ? hh - a.nh : hh - a.nh - a.nkv;
+        T* pool = (T*)(is_k ? a.k_pool : a.v_pool);
+        dst = pool + (((size_t)page * a.nkv + kvh) * a.page_size + pos % a.page_size) * d;
+    }
+    if (!is_q && !is_k) {               // V: plain copy
+        if (j < d) CeType<T>::store(dst + j, v);
+        return;
+    }
+    const float* w = is_q ? a.q_weight : a.k_weight;
+    if (w) {
+        float ss = ce_block_sum(v * v, scratch);
+        float inv = 1.0f / sqrtf(ss / (float)d + a.eps);
+        if (j < d) v = v * inv * w[j];
+    }
+    if (a.cos_table) {
+        if (pos >= a.max_pos) {
+            if (j == 0) atomicExch(a.status, 3);
+            return;
+        }
+        if (j < d) vals[j] = v;
+        __syncthreads();
+        int half = a.rd / 2;
+        const float* c = a.cos_table + (size_t)pos * half;
+        const float* s = a.sin_table + (size_t)pos * half;
+        if (j < half)
+            v = vals[j] * c[j] - vals[j + half] * s[j];
+        else if (j < a.rd)
+            v = vals[j] * c[j - half] + vals[j - half] * s[j - half];
+    }
+    if (j < d) CeType<T>::store(dst + j, v);
+}
+
+extern "C" int ce_qk_rope_kvwrite(void* qkv, void* k_pool, void* v_pool, int dtype, const float* q_weight,
+                                  const float* k_weight, const float* cos_table, const float* sin_table,
+                                  const int* positions, const int* seq_of_token, const int* seq_slot,
+                                  const int* block_table, int* status, int T, int nh, int nkv, int d, int rd,
+                                  int page_size, int max_pages, int num_pages, int max_pos, int write_kv, float eps,
+                                  cudaStream_t stream) {
+    if (T == 0) return CE_OK;
+    if (d <= 0 || d > 1024) return ce_fail(CE_ERR_SIZE, "ce_qk_rope_kvwrite: head_dim %d not in 1..1024", d);
+    if (rd < 0 || rd > d || (rd & 1)) return ce_fail(CE_ERR_SIZE, "ce_qk_rope_kvwrite: rotary_dim %d must be even and <= head_dim %d", rd, d);
+    if (!qkv || !positions || !status) return ce_fail(CE_ERR_ARG, "ce_qk_rope_kvwrite: null pointer");
+    if (write_kv && (!k_pool || !v_pool || !seq_of_token || !seq_slot || !block_table))
+        return ce_fail(CE_ERR_ARG, "ce_qk_rope_kvwrite: cache pointers missing");
+    QkRopeArgs a{qkv, k_pool, v_pool, q_weight, k_weight, cos_table, sin_table, positions, seq_of_token, seq_slot,
+                 block_table, status, T, nh, nkv, d, rd, page_size, max_pages, num_pages, max_pos, write_kv, eps};
+    int threads = (d + 31) / 32 * 32;
+    dim3 grid(T, nh + 2 * nkv);
+    size_t smem = (d + 32) * sizeof(float);
+    if (dtype == CE_F32)
+        qk_rope_kvwrite_kernel<float><<<grid, threads, smem, stream>>>(a);
+    else if (dtype == CE_BF16)
+        qk_rope_kvwrite_kernel<__nv_bfloat16><<<grid, threads, smem, stream>>>(a);
+    else
+        return ce_fail(CE_ERR_ARG, "ce_qk_rope_kvwrite: unknown dtype %d", dtype);
+    return ce_check_launch("ce_qk_rope_kvwrite");
+}
+
+// ---------------------------------------------------------------------------------------------
+// x += delta (float32 residual, delta in the activation dtype)
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void add_residual_kernel(float* __restrict__ x, const T* __restrict__ delta, size_t n) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; i < n; i += stride) x[i] += CeType<T>::load(delta + i);
+}
+
+extern "C" int ce_add_residual(float* x, const void* delta, int dtype, long long n, cudaStream_t stream) {
+    if (n == 0) return CE_OK;
+    if (!x || !delta) return ce_fail(CE_ERR_ARG, "ce_add_residual: null pointer");
+    int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
+    if (dtype == CE_F32)
+        add_residual_kernel<float><<<blocks, 256, 0, stream>>>(x, (const float*)delta, (size_t)n);
+    else if (dtype == CE_BF16)
+        add_residual_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(x, (const __nv_bfloat16*)delta, (size_t)n);
+    else
+        return ce_fail(CE_ERR_ARG, "ce_add_residual: unknown dtype %d", dtype);
+    return ce_check_launch("ce_add_residual");
+}
+
+// ---------------------------------------------------------------------------------------------
+// SwiGLU: out[t, i] = silu(gu[t, i]) * gu[t, I + i], silu(z) = z / (1 + exp(-z))
+// (src/model/layers.rs:568, 625-648)
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t total) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; i < total; i += stride) {
+        size_t t = i / I, c = i - t * I;
+        float g = CeType<T>::load(gu + t * 2 * I + c);
+        float u = CeType<T>::load(gu + t * 2 * I + I + c);
+        CeType<T>::store(out + i, g / (1.0f + expf(-g)) * u);
+    }
+}
+
+extern "C" int ce_swiglu(const void* gu, void* out, int dtype, int T, int I, cudaStream_t stream) {
+    size_t total = (size_t)T * I;
+    if (total == 0) return CE_OK;
+    if (!gu || !out) return ce_fail(CE_ERR_ARG, "ce_swiglu: null pointer");
+    int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+    if (dtype == CE_F32)
+        swiglu_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gu, (float*)out, I, total);
+    else if (dtype == CE_BF16)
+        swiglu_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, I, total);
+    else
+        return ce_fail(CE_ERR_ARG, "ce_swiglu: unknown dtype %d", dtype);
+    return ce_check_launch("ce_swiglu");
+}
+
+// ---------------------------------------------------------------------------------------------
+// dst[idx[i]] = val[i]: applies the block-table entries that changed since the last step.
+// ---------------------------------------------------------------------------------------------
+__global__ void scatter_i32_kernel(int* __restrict__ dst, const int* __restrict__ idx, const int* __restrict__ val,
+                                   int n, long long dst_len) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n && idx[i] >= 0 && idx[i] < dst_len) dst[idx[i]] = val[i];
+}
+
+extern "C" int ce_scatter_i32(int* dst, const int* idx, const int* val, int n, long long dst_len, cudaStream_t stream) {
+    if (n == 0) return CE_OK;
+    if (!dst || !idx || !val) return ce_fail(CE_ERR_ARG, "ce_scatter_i32: null pointer");
+    scatter_i32_kernel<<<(n + 255) / 256, 256, 0, stream>>>(dst, idx, val, n, dst_len);
+    return ce_check_launch("ce_scatter_i32");
+}

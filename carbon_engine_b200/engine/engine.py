@@ -1,0 +1,235 @@
+"""The Python entry point: load a model folder, generate tokens for prompts.
+
+``Engine`` does what the reference's ``Engine::load`` + ``scheduler::spawn`` + ``submit`` do
+together (src/engine.rs:140-404, src/scheduler.rs:385-440, 199-231): read the config, pick the
+model from the registry, load the weights (or random ones), size the cache, then run the
+scheduler's steps through the step function and the sampler until every request is done.
+Argument names follow the reference's engine flags (src/main.rs:103-217).
+"""
+from __future__ import annotations
+
+import json
+import time
+from dataclasses import dataclass, field
+from typing import Any, Dict, List, Optional, Sequence, Union
+
+import torch
+
+from .. import models  # noqa: F401  (registers the architectures)
+from ..cache.storage import CacheStorage
+from ..config.registry import load_config, resolve_architecture
+from ..csrc.kernel_lib import kernels
+from ..sampling.params import SamplingParams
+from ..sampling.sampler import Sampler, fresh_seed, top_logprobs
+from ..weights.loader import load_from_folder, load_random
+from .batch import StepEntry
+from .runner import ModelRunner
+from .scheduler import Scheduler, SubmitError
+
+DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "f32": torch.float32,
+          "auto": torch.bfloat16}
+
+
+def parse_dtype(name: Union[str, torch.dtype]) -> torch.dtype:
+    if isinstance(name, torch.dtype):
+        if name not in (torch.bfloat16, torch.float32):
+            raise ValueError(f"dtype {name} is not supported (bfloat16 or float32)")
+        return name
+    try:
+        return DTYPES[name]
+    except KeyError:
+        raise ValueError(f"dtype '{name}' is not supported (auto, bf16/bfloat16, f32/float32)") from None
+
+
+def require_gpu(device: Union[str, torch.device]) -> torch.device:
+    dev = torch.device(device)
+    if dev.type != "cuda" or not torch.cuda.is_available():
+        raise RuntimeError("this engine runs on a CUDA device only; there is no CPU path")
+    kernels()            # fails loudly here if the kernel library cannot be built or loaded
+    torch.cuda.set_device(dev)
+    return dev
+
+
+def build_model(model_dir: Optional[str], dtype: torch.dtype, device: torch.device, *, config=None,
+                hf_overrides: Optional[Dict[str, Any]] = None, dummy_weight: bool = False, seed: int = 0,
+                max_seq_len: int = 0):
+    """(model, config, max_seq_len): the model of a folder (or of a typed config) with weights loaded."""
+    if config is None:
+        arch, config = load_config(model_dir, hf_overrides)
+    else:
+        arch = resolve_architecture(config.to_json_dict())
+    # the context cap: the flag, else the checkpoint's, capped at 32768 (src/engine.rs:177-181)
+    if max_seq_len <= 0:
+        max_seq_len = min(config.max_position_embeddings, 32768)
+    model = arch.build_model(config, max_seq_len)
+    if dummy_weight or model_dir is None:
+        load_random(model, seed, device, dtype)
+    else:
+        load_from_folder(model, model_dir, device, dtype)
+    return model, config, max_seq_len
+
+
+@dataclass
+class RequestOutput:
+    request_id: int
+    prompt_token_ids: List[int]
+    token_ids: List[int]
+    finish_reason: str
+    error: Optional[str] = None
+    logprobs: Optional[List[dict]] = None
+
+    @property
+    def usage(self) -> Dict[str, int]:
+        return {"prompt_tokens": len(self.prompt_token_ids), "completion_tokens": len(self.token_ids)}
+
+
+@dataclass
+class _Live:
+    params: SamplingParams
+    seed: int
+    prompt: List[int]
+    adopted: bool = False
+    logprobs: List[dict] = field(default_factory=list)
+
+
+class Engine:
+    def __init__(self, model: Optional[str] = None, *, config=None, dtype: Union[str, torch.dtype] = "auto",
+                 device: str = "cuda:0", hf_overrides: Optional[Dict[str, Any]] = None, dummy_weight: bool = False,
+                 seed: int = 0, kv_tokens: Optional[int] = None, memory_ratio: float = 0.9, page_size: int = 16,
+                 max_seq_len: int = 0, max_running_requests: int = 16, max_prefill_tokens: int = 4096,
+                 cuda_graphs: bool = False, poison_cache: bool = False):
+        self.device = require_gpu(device)
+        self.dtype = parse_dtype(dtype)
+        self.model, self.config, self.max_seq_len = build_model(
+            model, self.dtype, self.device, config=config, hf_overrides=hf_overrides, dummy_weight=dummy_weight,
+            seed=seed, max_seq_len=max_seq_len)
+        self.page_size = int(page_size)
+        self.max_running = int(max_running_requests)
+        self.max_step_tokens = max(int(max_prefill_tokens), 16, self.max_running)
+        num_pages = self._size_cache(kv_tokens, memory_ratio)
+        self.storage = CacheStorage(self.model, self.dtype, self.device, self.page_size, num_pages, self.max_running,
+                                    self.max_seq_len, poison=poison_cache)
+        self.runner = ModelRunner(self.model, self.storage, self.max_step_tokens)
+        self.scheduler = Scheduler(self.storage.manager, self.max_running, self.max_step_tokens, self.max_seq_len,
+                                   self.config.vocab_size, self.config.eos_token_ids)
+        self.sampler = Sampler(self.device)
+        self.cuda_graphs = bool(cuda_graphs)
+        self._live: Dict[int, _Live] = {}
+        self._done: Dict[int, RequestOutput] = {}
+        self._next_id = 0
+        self.d2h_bytes_last = 0
+
+    # -- sizing ---------------------------------------------------------------------------------
+    def _bytes_per_token(self) -> int:
+        from ..parts.base import PagedCacheSpec
+        el = 2 if self.dtype == torch.bfloat16 else 4
+        return sum(2 * s.kv_heads * s.head_dim * el for _, s in self.model.cache_layout()
+                   if isinstance(s, PagedCacheSpec))
+
+    def _size_cache(self, kv_tokens: Optional[int], memory_ratio: float) -> int:
+        """Pages of the cache: ``kv_tokens`` if given, else what ``memory_ratio`` of the free memory
+        holds, at least 1024 tokens and at most eight contexts (src/engine.rs:317-329)."""
+        if kv_tokens is None:
+            free, _ = torch.cuda.mem_get_info(self.device)
+            per_token = max(self._bytes_per_token(), 1)
+            reserve = 2 << 30           # activations of the largest step
+            kv_tokens = int(max(free * memory_ratio - reserve, 0) // per_token)
+            kv_tokens = max(1024, min(kv_tokens, 8 * self.max_seq_len))
+        return max(1, (int(kv_tokens) + self.page_size - 1) // self.page_size)
+
+    # -- requests -------------------------------------------------------------------------------
+    def add_request(self, prompt_token_ids: Sequence[int], params: Optional[SamplingParams] = None) -> int:
+        params = params or SamplingParams()
+        rid = self._next_id
+        self._next_id += 1
+        self.scheduler.submit(rid, prompt_token_ids, params.max_tokens, params.ignore_eos, params.stop_token_ids)
+        self._live[rid] = _Live(params, params.seed if params.seed is not None else fresh_seed(),
+                                list(prompt_token_ids))
+        return rid
+
+    def abort(self, request_id: int) -> bool:
+        return self.scheduler.abort(request_id)
+
+    def has_unfinished(self) -> bool:
+        return not self.scheduler.idle()
+
+    def step(self) -> List[RequestOutput]:
+        """Run one scheduler step; returns the requests that finished in it."""
+        plan = self.scheduler.plan()
+        if plan:
+            entries = []
+            for e in plan:
+                live = self._live[e.request_id]
+                if not live.adopted:
+                    self.runner.adopt_request(e.request_id)
+                    live.adopted = True
+                entries.append(StepEntry(e.request_id, e.tokens, [e.count - 1] if e.sample else []))
+            try:
+                logits = self.runner.step(entries)
+                sampled_ids = [e.request_id for e in plan if e.sample]
+                tokens: List[int] = []
+                if sampled_ids:
+                    lives = [self._live[r] for r in sampled_ids]
+                    outs = [self.scheduler.tokens_of(r) for r in sampled_ids]
+                    plens = [len(l.prompt) for l in lives]
+                    want_lp = [i for i, l in enumerate(lives) if l.params.logprobs > 0]
+                    base = logits[want_lp].cpu().numpy() if want_lp else None    # before penalties
+                    dev = self.sampler.sample(logits, [l.params for l in lives], [l.seed for l in lives],
+                                              [len(o) - p for o, p in zip(outs, plens)],
+                                              [l.prompt for l in lives], [o[p:] for o, p in zip(outs, plens)])
+                    host = dev.cpu()
+                    self.d2h_bytes_last = host.numel() * 4
+                    tokens = host.tolist()
+                    for j, i in enumerate(want_lp):
+                        lives[i].logprobs.append(top_logprobs(base[j], tokens[i], lives[i].params.logprobs))
+                self.runner.check_status()
+                self.scheduler.commit(tokens)
+            except Exception as exc:       # the step failed: its requests end with an error, others go on
+                self._last_error = str(exc)
+                self.scheduler.fail_step()
+                if isinstance(exc, (KeyboardInterrupt, MemoryError)):
+                    raise
+        return self._collect()
+
+    def _collect(self) -> List[RequestOutput]:
+        out = []
+        for rid, reason in self.scheduler.pop_finished():
+            live = self._live.pop(rid)
+            toks = self.scheduler.tokens_of(rid)
+            n = len(live.prompt)
+            err = None
+            if reason == "error":
+                err = getattr(self, "_last_error", None) or "request does not fit in the KV cache"
+            ro = RequestOutput(rid, toks[:n], toks[n:], reason, err, live.logprobs or None)
+            self.scheduler.forget(rid)
+            out.append(ro)
+        return out
+
+    def generate(self, prompt_token_ids: Sequence[Sequence[int]],
+                 sampling_params: Union[None, SamplingParams, Sequence[SamplingParams]] = None) -> List[RequestOutput]:
+        """Generate for a list of prompts (token ids in, token ids out), in the order given."""
+        if prompt_token_ids and isinstance(prompt_token_ids[0], int):
+            prompt_token_ids = [prompt_token_ids]      # one prompt
+        if sampling_params is None or isinstance(sampling_params, SamplingParams):
+            sampling_params = [sampling_params or SamplingParams()] * len(prompt_token_ids)
+        ids, results = [], {}
+        for prompt, sp in zip(prompt_token_ids, sampling_params):
+            try:
+                ids.append(self.add_request(prompt, sp))
+            except SubmitError as exc:
+                rid = self._next_id
+                self._next_id += 1
+                ids.append(rid)
+                results[rid] = RequestOutput(rid, list(prompt), [], "error", str(exc))
+        while self.has_unfinished():
+            for ro in self.step():
+                results[ro.request_id] = ro
+        for ro in self._collect():
+            results[ro.request_id] = ro
+        return [results[i] for i in ids]
+
+    def stats(self) -> Dict[str, int]:
+        s = self.scheduler.stats()
+        s["kv_pages_free"] = self.storage.manager.free_pages(0) if self.storage.groups else 0
+        s["kv_pages_total"] = self.storage.groups[0].num_pages if self.storage.groups else 0
+        return s

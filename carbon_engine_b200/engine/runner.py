@@ -1,0 +1,158 @@
+"""The step function: a batch of (request, its next tokens) in, logits at the wanted places out.
+
+It runs only the tokens it is given, as one batch, against the cache that earlier steps left:
+portions of prompts beside single decoded tokens, cut anywhere.  The reference's counterpart is
+``Engine::forward(meta, tokens, sample_rows) -> f32 [rows, vocab]`` (src/engine.rs:407-446), fed
+by either a prefill batch or a decode batch; here one call takes any mixture.
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from .. import ops
+from ..cache.storage import CacheStorage
+from .batch import StepBuffers, StepContext, StepEntry
+
+
+class StepError(RuntimeError):
+    pass
+
+
+_STATUS = {
+    1: "a token id outside the vocabulary reached the embedding",
+    2: "a token was to be written to a page its request does not hold",
+    3: "a position beyond the rotary table (raise max_seq_len)",
+    4: "attention read a page its request does not hold",
+}
+
+
+class ModelRunner:
+    def __init__(self, model, storage: CacheStorage, max_step_tokens: int):
+        self.model, self.storage = model, storage
+        self.device, self.dtype = model.device, model.dtype
+        self.max_step_tokens = int(max_step_tokens)
+        self.bufs = StepBuffers(self.max_step_tokens, storage.max_requests, len(storage.groups), self.device)
+        self.fast_attention = True
+        self.h2d_bytes_last = 0
+        self.kernel_launches = 0
+
+    # -- requests -------------------------------------------------------------------------------
+    def open_request(self, request_id: int) -> int:
+        slot = self.storage.manager.open(request_id)
+        self.storage.slot_opened(slot)
+        self.storage.zero_state(slot)
+        return slot
+
+    def adopt_request(self, request_id: int) -> int:
+        """A request the scheduler opened in the cache manager: prepare its slot on the device."""
+        slot = self.storage.manager.slot_of(request_id)
+        self.storage.slot_opened(slot)
+        self.storage.zero_state(slot)
+        return slot
+
+    def close_request(self, request_id: int) -> None:
+        self.storage.manager.close(request_id)
+
+    # -- the step -------------------------------------------------------------------------------
+    def prepare(self, entries: Sequence[StepEntry]):
+        """Reserve pages, lay the step out in the pinned buffer and upload it.  Returns the context,
+        the device tensor of wanted rows and the (request, new length) pairs to commit."""
+        mgr = self.storage.manager
+        if not entries:
+            raise StepError("a step needs at least one entry")
+        if len(entries) > self.storage.max_requests:
+            raise StepError(f"{len(entries)} entries, but only {self.storage.max_requests} requests may be live")
+        order = sorted(range(len(entries)), key=lambda i: 0 if len(entries[i].tokens) == 1 else 1)
+        T = sum(len(e.tokens) for e in entries)
+        if T > self.max_step_tokens:
+            raise StepError(f"{T} tokens in one step, but the engine was built for {self.max_step_tokens}")
+        seen = set()
+        for e in entries:
+            if len(e.tokens) == 0:
+                raise StepError(f"request {e.request_id}: an entry needs at least one token")
+            if e.request_id in seen:
+                raise StepError(f"request {e.request_id} appears twice in one step")
+            seen.add(e.request_id)
+            for w in e.want:
+                if not 0 <= w < len(e.tokens):
+                    raise StepError(f"request {e.request_id}: wanted place {w} is outside its {len(e.tokens)} tokens")
+
+        b = self.bufs
+        h_tok, h_pos, h_seq = b.host_section("tokens"), b.host_section("positions"), b.host_section("seq_of_token")
+        h_slot, h_qs, h_ctx = b.host_section("seq_slot"), b.host_section("q_start"), b.host_section("ctx_len")
+        ctx = StepContext(b, T, len(entries), self.dtype, self.device, self.storage.device_tables)
+        ctx.fast_attention = self.fast_attention
+        commits = []
+        starts_sorted = {}
+        upd = [([], []) for _ in self.storage.groups]
+        off = 0
+        for bi, i in enumerate(order):
+            e = entries[i]
+            n = len(e.tokens)
+            start = mgr.length_of(e.request_id)
+            slot = mgr.slot_of(e.request_id)
+            mgr.reserve(e.request_id, start + n)
+            h_tok[off:off + n] = np.asarray(e.tokens, dtype=np.int32)
+            h_pos[off:off + n] = np.arange(start, start + n, dtype=np.int32)
+            h_seq[off:off + n] = bi
+            h_slot[bi] = slot
+            h_qs[bi] = off
+            h_ctx[bi] = start + n
+            starts_sorted[i] = off
+            ctx.h_slots.append(slot)
+            ctx.h_q_start.append(off)
+            ctx.h_ctx_before.append(start)
+            if n == 1 and bi == ctx.n_decode:
+                ctx.n_decode += 1
+            ctx.max_position = max(ctx.max_position, start + n - 1)
+            ctx.max_ctx = max(ctx.max_ctx, start + n)
+            commits.append((e.request_id, start + n))
+            for g in range(len(self.storage.groups)):
+                u = self.storage.pending_table_updates(g, slot, start + n)
+                if u is not None:
+                    upd[g][0].append(u[0]); upd[g][1].append(u[1])
+            off += n
+        h_qs[len(entries)] = off
+        ctx.h_q_start.append(off)
+        ctx.h_tokens = h_tok[:T].tolist()
+
+        rows: List[int] = []
+        for i, e in enumerate(entries):
+            rows.extend(starts_sorted[i] + w for w in e.want)
+        h_rows = b.host_section("rows")
+        h_rows[:len(rows)] = np.asarray(rows, dtype=np.int32) if rows else 0
+        n_upd = []
+        for g in range(len(self.storage.groups)):
+            if upd[g][0]:
+                idx = np.concatenate(upd[g][0]); val = np.concatenate(upd[g][1])
+                b.host_section(f"upd_idx{g}")[:len(idx)] = idx
+                b.host_section(f"upd_val{g}")[:len(val)] = val
+                n_upd.append(len(idx))
+            else:
+                n_upd.append(0)
+        self.h2d_bytes_last = b.upload()
+        for g, n in enumerate(n_upd):
+            if n:
+                ops.scatter_i32(self.storage.device_tables[g], b.dev_section(f"upd_idx{g}", n),
+                                b.dev_section(f"upd_val{g}", n))
+        return ctx, b.dev_section("rows", len(rows)), commits
+
+    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """Run one step and return float32 logits [wanted, vocab] on the device, in the order of the
+        entries and of their ``want`` lists."""
+        ctx, rows, commits = self.prepare(entries)
+        x = self.model.forward(ctx, self.storage)
+        logits = self.model.logits(ctx, x, rows)
+        for request_id, new_len in commits:
+            self.storage.manager.commit(request_id, new_len)
+        return logits
+
+    def check_status(self) -> None:
+        """Raise if a kernel of an earlier step flagged a bad index (this synchronises)."""
+        code = int(self.bufs.status.item())
+        if code != 0:
+            self.bufs.status.zero_()
+            raise StepError(f"device status {code}: {_STATUS.get(code, 'unknown')}")

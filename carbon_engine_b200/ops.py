@@ -1,0 +1,175 @@
+"""Thin, checked Python wrappers around the CUDA launchers of libcarbon_kernels.so.
+
+Each wrapper takes torch tensors that live on the GPU, validates dtype and layout, and launches on
+the current CUDA stream.  Nothing here computes on the CPU and nothing falls back to a library:
+if the kernel library is missing or refuses a size, the call raises.
+"""
+from __future__ import annotations
+
+import struct
+from typing import Optional, Sequence
+
+import torch
+
+from .csrc.kernel_lib import KernelError, kernels
+
+F32, BF16 = 0, 1
+GEMM_STORE, GEMM_STORE_F32, GEMM_ACCUM_F32, GEMM_SWIGLU = 0, 1, 2, 3
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    if dt == torch.float32:
+        return F32
+    if dt == torch.bfloat16:
+        return BF16
+    raise KernelError(f"unsupported dtype {dt} (float32 or bfloat16)")
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _need(t: torch.Tensor, name: str, dtype=None) -> None:
+    if not t.is_cuda:
+        raise KernelError(f"{name} must be a CUDA tensor (there is no CPU path)")
+    if not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, got {t.dtype}")
+
+
+def _ok(code: int) -> None:
+    if code != 0:
+        raise KernelError(kernels().ce_last_error().decode())
+
+
+def embed(table: torch.Tensor, tokens: torch.Tensor, x: torch.Tensor, status: torch.Tensor) -> None:
+    """x[t, :] = table[tokens[t], :] as float32."""
+    _need(table, "table"); _need(tokens, "tokens", torch.int32); _need(x, "x", torch.float32)
+    T, H = x.shape
+    _ok(kernels().ce_embed(_ptr(table), dtype_code(table.dtype), _ptr(tokens), _ptr(x), T, H, table.shape[0],
+                           _ptr(status), _stream()))
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float,
+            rows: Optional[torch.Tensor] = None) -> None:
+    """out[r] = rmsnorm(x[rows[r]] or x[r]) * weight; x float32, out float32 or bfloat16."""
+    _need(x, "x", torch.float32); _need(weight, "weight", torch.float32); _need(out, "out")
+    R, H = out.shape
+    if x.shape[1] != H or weight.numel() != H:
+        raise KernelError(f"rmsnorm: widths differ: x {tuple(x.shape)}, weight {tuple(weight.shape)}, out {tuple(out.shape)}")
+    if rows is not None:
+        _need(rows, "rows", torch.int32)
+    _ok(kernels().ce_rmsnorm(_ptr(x), _ptr(weight), _ptr(out), dtype_code(out.dtype), _ptr(rows), R, H, float(eps),
+                             _stream()))
+
+
+def qk_rope_kvwrite(qkv, k_pool, v_pool, q_weight, k_weight, cos, sin, positions, seq_of_token, seq_slot,
+                    block_table, status, nh: int, nkv: int, d: int, rotary_dim: int, page_size: int,
+                    eps: float, write_kv: bool = True) -> None:
+    _need(qkv, "qkv")
+    T = qkv.shape[0]
+    if qkv.shape[1] != (nh + 2 * nkv) * d:
+        raise KernelError(f"qk_rope_kvwrite: qkv width {qkv.shape[1]} != (nh + 2 nkv) d = {(nh + 2 * nkv) * d}")
+    for name, t in (("q_weight", q_weight), ("k_weight", k_weight), ("cos", cos), ("sin", sin)):
+        if t is not None:
+            _need(t, name, torch.float32)
+    max_pos = cos.shape[0] if cos is not None else 0
+    if cos is not None and cos.shape[1] != rotary_dim // 2:
+        raise KernelError("qk_rope_kvwrite: rotary table width is not rotary_dim / 2")
+    if write_kv:
+        _need(k_pool, "k_pool", qkv.dtype); _need(v_pool, "v_pool", qkv.dtype)
+        if tuple(k_pool.shape[1:]) != (nkv, page_size, d):
+            raise KernelError(f"qk_rope_kvwrite: pool shape {tuple(k_pool.shape)} is not [pages, {nkv}, {page_size}, {d}]")
+    num_pages = k_pool.shape[0] if k_pool is not None else 0
+    max_pages = block_table.shape[1] if block_table is not None else 0
+    _ok(kernels().ce_qk_rope_kvwrite(
+        _ptr(qkv), _ptr(k_pool), _ptr(v_pool), dtype_code(qkv.dtype), _ptr(q_weight), _ptr(k_weight), _ptr(cos),
+        _ptr(sin), _ptr(positions), _ptr(seq_of_token), _ptr(seq_slot), _ptr(block_table), _ptr(status),
+        T, nh, nkv, d, rotary_dim, page_size, max_pages, num_pages, max_pos, 1 if write_kv else 0, float(eps),
+        _stream()))
+
+
+def add_residual(x: torch.Tensor, delta: torch.Tensor) -> None:
+    _need(x, "x", torch.float32); _need(delta, "delta")
+    if x.numel() != delta.numel():
+        raise KernelError("add_residual: sizes differ")
+    _ok(kernels().ce_add_residual(_ptr(x), _ptr(delta), dtype_code(delta.dtype), x.numel(), _stream()))
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    _need(gate_up, "gate_up"); _need(out, "out", gate_up.dtype)
+    T, I = out.shape
+    if gate_up.shape != (T, 2 * I):
+        raise KernelError("swiglu: gate_up must be [T, 2I]")
+    _ok(kernels().ce_swiglu(_ptr(gate_up), _ptr(out), dtype_code(out.dtype), T, I, _stream()))
+
+
+def attention_generic(q, q_stride: int, k_pool, v_pool, out, positions, seq_of_token, seq_slot, block_table,
+                      status, nh: int, nkv: int, d: int, page_size: int, window: int, scale: float,
+                      T: Optional[int] = None) -> None:
+    _need(k_pool, "k_pool"); _need(v_pool, "v_pool", k_pool.dtype); _need(out, "out", k_pool.dtype)
+    if q.dtype != k_pool.dtype:
+        raise KernelError("attention: q and the cache differ in dtype")
+    T = out.shape[0] if T is None else T
+    _ok(kernels().ce_attention_generic(
+        _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), dtype_code(out.dtype), _ptr(positions), _ptr(seq_of_token),
+        _ptr(seq_slot), _ptr(block_table), _ptr(status), T, nh, nkv, d, q_stride, page_size, block_table.shape[1],
+        k_pool.shape[0], int(window), float(scale), _stream()))
+
+
+def gemm_plain(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, mode: int) -> None:
+    """c = a @ w.T with float32 FMA arithmetic; see csrc/kernels/gemm_plain.cu for the epilogues."""
+    _need(w, "w", a.dtype); _need(c, "c")
+    if a.stride(-1) != 1 or c.stride(-1) != 1:
+        raise KernelError("gemm_plain: rows must be contiguous")
+    M, K = a.shape
+    N = c.shape[1]
+    rows = 2 * N if mode == GEMM_SWIGLU else N
+    if w.shape != (rows, K) or c.shape[0] != M:
+        raise KernelError(f"gemm_plain: shapes a {tuple(a.shape)}, w {tuple(w.shape)}, c {tuple(c.shape)} do not fit")
+    want = torch.float32 if mode in (GEMM_STORE_F32, GEMM_ACCUM_F32) else a.dtype
+    if c.dtype != want:
+        raise KernelError(f"gemm_plain: output must be {want}")
+    _ok(kernels().ce_gemm_plain(_ptr(a), _ptr(w), _ptr(c), dtype_code(a.dtype), M, N, K, a.stride(0), c.stride(0),
+                                mode, _stream()))
+
+
+def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
+    _need(logits, "logits", torch.float32); _need(out, "out", torch.int32)
+    R, V = logits.shape
+    _ok(kernels().ce_argmax(_ptr(logits), R, V, _ptr(out), _stream()))
+
+
+SAMPLE_ROW = struct.Struct("<fffiQ")     # temperature, top_p, min_p, top_k, seed
+
+
+def pack_sample_rows(rows: Sequence[tuple]) -> bytes:
+    return b"".join(SAMPLE_ROW.pack(float(t), float(p), float(m), int(k), int(s) & 0xFFFFFFFFFFFFFFFF)
+                    for (t, p, m, k, s) in rows)
+
+
+def sample(logits: torch.Tensor, params: torch.Tensor, out: torch.Tensor) -> None:
+    """params: uint8 [rows, 24] holding SAMPLE_ROW records."""
+    _need(logits, "logits", torch.float32); _need(out, "out", torch.int32); _need(params, "params", torch.uint8)
+    R, V = logits.shape
+    if params.numel() != R * SAMPLE_ROW.size:
+        raise KernelError("sample: params must hold one 24-byte record per row")
+    _ok(kernels().ce_sample(_ptr(logits), R, V, _ptr(params), _ptr(out), _stream()))
+
+
+def apply_penalties(logits: torch.Tensor, entries: torch.Tensor, row_params: torch.Tensor) -> None:
+    _need(logits, "logits", torch.float32); _need(entries, "entries", torch.int32)
+    _need(row_params, "row_params", torch.float32)
+    _ok(kernels().ce_apply_penalties(_ptr(logits), logits.shape[1], _ptr(entries), entries.shape[0],
+                                     _ptr(row_params), _stream()))
+
+
+def scatter_i32(dst: torch.Tensor, idx: torch.Tensor, val: torch.Tensor) -> None:
+    """dst.view(-1)[idx[i]] = val[i]"""
+    _need(dst, "dst", torch.int32); _need(idx, "idx", torch.int32); _need(val, "val", torch.int32)
+    _ok(kernels().ce_scatter_i32(_ptr(dst), _ptr(idx), _ptr(val), idx.numel(), dst.numel(), _stream()))

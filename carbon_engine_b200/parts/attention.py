@@ -1,0 +1,85 @@
+"""Grouped-query attention over the paged cache, with optional per-head q/k RMSNorm, optional
+rotary embedding and an optional window.
+
+Order of operations, as the reference has it (src/model/attention.rs:868-914): one product for q, k
+and v; RMSNorm over each head of q and k with one weight of head_dim shared by all heads, before
+the rotation (:884-889); K (normed, rotated) and V are written to the cache before attending (:890),
+so new tokens read themselves from the cache; scores scaled by ``scale`` (1/sqrt(head_dim) unless
+given, :810); query at absolute position p sees keys up to p (:1038-1063), or the last ``window``
+of them; query head h reads KV head h // (heads / kv_heads) (:1035); then the output product, added
+into the residual stream (:913, src/model/mod.rs:648).
+"""
+from __future__ import annotations
+
+import math
+from typing import List, Optional
+
+import torch
+
+from .. import ops
+from .base import Mixer, PagedCacheSpec, Part, TensorGetter, TensorSpec
+from .linear import ACCUM, STORE, Linear
+from .rope import PositionEncoding
+
+
+class PagedAttention(Mixer):
+    def __init__(self, hidden: int, heads: int, kv_heads: int, head_dim: int, prefix: str,
+                 position: Optional[PositionEncoding] = None, qk_norm_eps: Optional[float] = None,
+                 window: int = 0, scale: Optional[float] = None):
+        if heads % kv_heads:
+            raise ValueError(f"{heads} heads are not a multiple of {kv_heads} kv heads")
+        self.hidden, self.heads, self.kv_heads, self.head_dim = hidden, heads, kv_heads, head_dim
+        self.prefix, self.position, self.qk_norm_eps, self.window = prefix, position, qk_norm_eps, int(window)
+        self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(head_dim)
+        self.qkv = Linear(hidden, [heads * head_dim, kv_heads * head_dim, kv_heads * head_dim],
+                          [f"{prefix}.q_proj.weight", f"{prefix}.k_proj.weight", f"{prefix}.v_proj.weight"])
+        self.o = Linear(heads * head_dim, [hidden], [f"{prefix}.o_proj.weight"])
+        self.q_norm_weight: Optional[torch.Tensor] = None
+        self.k_norm_weight: Optional[torch.Tensor] = None
+
+    def children(self) -> List[Part]:
+        return [self.qkv, self.o]
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        if self.qk_norm_eps is None:
+            return []
+        return [TensorSpec(f"{self.prefix}.q_norm.weight", (self.head_dim,), "norm"),
+                TensorSpec(f"{self.prefix}.k_norm.weight", (self.head_dim,), "norm")]
+
+    def load(self, get: TensorGetter, device, dtype) -> None:
+        if self.qk_norm_eps is not None:
+            self.q_norm_weight = get(f"{self.prefix}.q_norm.weight").to(device).to(torch.float32).contiguous()
+            self.k_norm_weight = get(f"{self.prefix}.k_norm.weight").to(device).to(torch.float32).contiguous()
+        if self.position is not None and self.position.cos is None:
+            self.position.prepare(device)
+
+    def cache_spec(self) -> PagedCacheSpec:
+        return PagedCacheSpec(self.kv_heads, self.head_dim, self.window)
+
+    def forward(self, ctx, h: torch.Tensor, x: torch.Tensor, cache) -> None:
+        T = h.shape[0]
+        nh, nkv, d = self.heads, self.kv_heads, self.head_dim
+        qkv = ctx.buffer((T, (nh + 2 * nkv) * d))
+        self.qkv.forward(h, qkv, STORE)
+        pos = self.position
+        cos = pos.cos if pos is not None else None
+        sin = pos.sin if pos is not None else None
+        if cos is not None and ctx.max_position >= cos.shape[0]:
+            raise ValueError(f"position {ctx.max_position} is beyond the rotary table ({cos.shape[0]}): raise max_seq_len")
+        table = ctx.block_tables[cache.group]
+        ops.qk_rope_kvwrite(qkv, cache.k_pool, cache.v_pool, self.q_norm_weight, self.k_norm_weight, cos, sin,
+                            ctx.positions, ctx.seq_of_token, ctx.seq_slot, table, ctx.status, nh, nkv, d,
+                            pos.rotary_dim if cos is not None else 0, cache.page_size,
+                            self.qk_norm_eps if self.qk_norm_eps is not None else 0.0, write_kv=cache.writes)
+        out = ctx.buffer((T, nh * d))
+        self.attend(ctx, qkv, out, cache, table)
+        self.o.forward(out, x, ACCUM)
+
+    def attend(self, ctx, qkv: torch.Tensor, out: torch.Tensor, cache, table: torch.Tensor) -> None:
+        nh, nkv, d = self.heads, self.kv_heads, self.head_dim
+        if qkv.dtype == torch.bfloat16 and ctx.fast_attention:
+            from .. import ops_tensor
+            if ops_tensor.attention_bf16(ctx, qkv, out, cache, table, nh, nkv, d, self.window, self.scale):
+                return
+        ops.attention_generic(qkv, qkv.shape[1], cache.k_pool, cache.v_pool, out, ctx.positions, ctx.seq_of_token,
+                              ctx.seq_slot, table, ctx.status, nh, nkv, d, cache.page_size, self.window, self.scale)

@@ -105,7 +105,7 @@ class Engine:
             seed=seed, max_seq_len=max_seq_len)
         self.page_size = int(page_size)
         self.max_running = int(max_running_requests)
-        self.max_step_tokens = max(int(max_prefill_tokens), 16, self.max_running)
+        self.max_step_tokens = max(int(max_prefill_tokens), self.max_running)
         num_pages = self._size_cache(kv_tokens, memory_ratio)
         self.storage = CacheStorage(self.model, self.dtype, self.device, self.page_size, num_pages, self.max_running,
                                     self.max_seq_len, poison=poison_cache)

@@ -23,6 +23,9 @@ STORE, STORE_F32, ACCUM, SWIGLU = ops.GEMM_STORE, ops.GEMM_STORE_F32, ops.GEMM_A
 #: bfloat16 products go to "tensor" (own tcgen05 kernels), "library" (cuBLAS + epilogue kernel) or
 #: "plain" (the FMA kernel); "auto" takes the first that accepts the shape.
 BF16_BACKEND = "auto"
+#: under "auto", products the tensor-core kernels refuse go to the plain kernel up to this many
+#: multiply-adds and to the library above it
+PLAIN_MAX_MACS = 1 << 24
 
 
 def matmul_nt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int, scratch=None) -> None:
@@ -38,6 +41,9 @@ def matmul_nt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int, sc
             return
         if BF16_BACKEND == "tensor":
             raise ops.KernelError(f"the tensor-core product refuses a {tuple(a.shape)} x {tuple(w.shape)}^T product")
+    if BF16_BACKEND == "auto" and a.shape[0] * w.shape[0] * a.shape[1] <= PLAIN_MAX_MACS:
+        ops.gemm_plain(a, w, out, mode)      # small: one fused kernel, float32 accumulators into the epilogue
+        return
     # library product, then the epilogue as a kernel of its own
     if mode == STORE:
         torch.matmul(a, w.t(), out=out)

@@ -40,6 +40,13 @@ TINY = {
 # tolerances, relative to the largest |logit| of the compared rows: the reference's own kernel
 # self-test accepts 1e-4 in float32 and 3e-2 in 16-bit (src/device.rs:776-848)
 TOL = {"float32": 1e-4, "bfloat16": 3e-2}
+# Whole-model logits in bfloat16 pass through 4 roundings of the activations per layer, and the tiny
+# models are 64 to 96 wide, so little averages out: measured on these models the typical row is off
+# by 1.5e-2 and the worst of some 3000 rows by 3.4e-2.  A row may therefore be off by 5e-2, but the
+# median row by no more than 2e-2.  (A cache fault moves a sharpened model's logits by far more, and
+# the float32 replay of the same trace, at 1e-4, shares every line of the cache and step code.)
+TOL_MODEL_BF16_ROW = 5e-2
+TOL_MODEL_BF16_MEDIAN = 2e-2
 
 
 def write_safetensors_plain(path: str, tensors: Dict[str, torch.Tensor]) -> None:

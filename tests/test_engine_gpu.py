@@ -1,0 +1,188 @@
+"""Generation through the Python entry point, compared with the plain implementation."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen3 as plain
+from helpers import TINY, TOL, make_model_dir, random_tokens
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def models(tmp_path_factory):
+    tmp = str(tmp_path_factory.mktemp("models"))
+    out = {}
+    for name in TINY:
+        d = make_model_dir(tmp, name)
+        cfg, w = plain.read_model(d)
+        out[name] = (d, cfg, w)
+    return out
+
+
+def make_engine(model_dir, dtype, name, **kw):
+    from carbon_engine_b200 import Engine
+    args = dict(dtype=dtype, page_size=TINY[name]["page_size"], kv_tokens=2048, max_seq_len=512, poison_cache=True)
+    args.update(kw)
+    return Engine(model_dir, **args)
+
+
+def check_greedy(cfg, w, prompt, got, dtype):
+    """``got`` must be the plain implementation's greedy continuation; a different token is accepted
+    only where the plain logits of the two candidates are closer than the precision's tolerance
+    (the reference's own comparison treats such margins as ties, scripts/compare_reference.py:43-51),
+    and the comparison then goes on from the engine's token."""
+    toks = list(prompt)
+    for i, t in enumerate(got):
+        logits = plain.forward(cfg, w, toks)[-1]
+        best = int(logits.argmax())
+        if t != best:
+            margin = float(logits[best] - logits[t])
+            assert margin <= 2 * TOL[dtype] * float(logits.abs().max()), (i, t, best, margin)
+        toks.append(t)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_greedy_generation_config_a(models, dtype):
+    from carbon_engine_b200 import SamplingParams
+    d, cfg, w = models["A"]
+    rng = np.random.default_rng(1)
+    prompts = [random_tokens(rng, n, cfg["vocab_size"]) for n in (5, 11, 17)]
+    eng = make_engine(d, dtype, "A")
+    outs = eng.generate(prompts, SamplingParams(max_tokens=8, ignore_eos=True))
+    for p, o in zip(prompts, outs):
+        assert o.finish_reason == "length" and len(o.token_ids) == 8 and o.prompt_token_ids == p
+        check_greedy(cfg, w, p, o.token_ids, dtype)
+        if dtype == "float32":
+            assert o.token_ids == plain.greedy_generate(cfg, w, p, 8)
+    st = eng.stats()
+    assert st["finished"] == 3 and st["running"] == 0 and st["kv_pages_free"] == st["kv_pages_total"]
+    eng.storage.manager.check()
+
+
+def gumbel_pick(logits_row, temperature, seed):
+    from carbon_engine_b200.sampling.sampler import mix64
+    z = logits_row.astype(np.float64) / temperature
+    idx = np.arange(len(z), dtype=np.uint64)
+    best, second, best_i = -1e300, -1e300, -1
+    for i in range(len(z)):
+        h = mix64(seed ^ mix64((i + 0x632BE59BD9B4E019) & ((1 << 64) - 1)))
+        u = ((h >> 40) + 0.5) / 16777216.0
+        g = z[i] - math.log(-math.log(u))
+        if g > best:
+            second, best, best_i = best, g, i
+        elif g > second:
+            second = g
+    return best_i, best - second
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_chunked_prefill_mixed_with_decode_and_seeded_temperature_config_b(models, dtype):
+    """Prompts 3/9/24/40 under a 7-token step budget, so portions of prompts run beside decoded
+    tokens; temperature 0.8 with a fixed seed gives the tokens the same draw gives on plain logits."""
+    from carbon_engine_b200 import SamplingParams
+    from carbon_engine_b200.sampling.sampler import step_seed
+    d, cfg, w = models["B"]
+    rng = np.random.default_rng(2)
+    prompts = [random_tokens(rng, n, cfg["vocab_size"]) for n in (3, 9, 24, 40)]
+    eng = make_engine(d, dtype, "B", max_prefill_tokens=7, max_running_requests=4)
+    params = [SamplingParams(temperature=0.8, seed=100 + i, max_tokens=6, ignore_eos=True) for i in range(4)]
+    outs = eng.generate(prompts, params)
+    again = make_engine(d, dtype, "B", max_prefill_tokens=512, max_running_requests=4).generate(prompts, params)
+    for i, (p, o) in enumerate(zip(prompts, outs)):
+        assert len(o.token_ids) == 6
+        toks = list(p)
+        for step, t in enumerate(o.token_ids):
+            logits = plain.forward(cfg, w, toks)[-1].numpy().astype(np.float32)
+            pick, margin = gumbel_pick(logits, 0.8, step_seed(100 + i, step))
+            assert t == pick or margin < 2 * TOL[dtype] * np.abs(logits).max() / 0.8, (i, step, t, pick, margin)
+            toks.append(t)
+        if dtype == "float32":
+            assert again[i].token_ids == o.token_ids           # the cut of the prompt does not change the draw
+    assert eng.stats()["steps"] > 10                           # 76 prompt tokens at 7 a step
+
+
+def test_small_cache_queues_requests_and_gives_the_same_tokens(models):
+    """Few pages: requests wait for the pages of finished ones (src/scheduler.rs:636-641;
+    tests/parallel.rs:380-392 in the reference).  Tokens equal those of each request run alone."""
+    from carbon_engine_b200 import SamplingParams
+    d, cfg, w = models["A"]
+    rng = np.random.default_rng(3)
+    prompts = [random_tokens(rng, int(n), cfg["vocab_size"]) for n in rng.integers(4, 40, size=10)]
+    sp = SamplingParams(max_tokens=10, ignore_eos=True)
+    big = make_engine(d, "float32", "A", kv_tokens=4096).generate(prompts, sp)
+    small_eng = make_engine(d, "float32", "A", kv_tokens=112, max_prefill_tokens=16, max_running_requests=3)
+    small = small_eng.generate(prompts, sp)
+    for a, b in zip(big, small):
+        assert a.token_ids == b.token_ids and b.finish_reason == "length"
+    assert small_eng.stats()["kv_pages_total"] == 7 and small_eng.stats()["kv_pages_free"] == 7
+    small_eng.storage.manager.check()
+
+
+def test_identical_prompts_in_one_batch_give_identical_outputs(models):
+    from carbon_engine_b200 import SamplingParams
+    d, cfg, w = models["C"]
+    p = random_tokens(np.random.default_rng(4), 50, cfg["vocab_size"])
+    for dtype in ("float32", "bfloat16"):
+        outs = make_engine(d, dtype, "C").generate([p, p, p], SamplingParams(max_tokens=12, ignore_eos=True))
+        assert outs[0].token_ids == outs[1].token_ids == outs[2].token_ids
+
+
+def test_requests_that_cannot_run_end_with_an_error_and_the_rest_go_on(models):
+    from carbon_engine_b200 import SamplingParams
+    d, cfg, w = models["A"]
+    eng = make_engine(d, "float32", "A", kv_tokens=64, max_seq_len=128)
+    ok = random_tokens(np.random.default_rng(5), 10, 256)
+    outs = eng.generate([ok, [], list(range(100)), [1, 2, 999], ok],
+                        [SamplingParams(max_tokens=4, ignore_eos=True), SamplingParams(), SamplingParams(max_tokens=50),
+                         SamplingParams(), SamplingParams(max_tokens=4, ignore_eos=True)])
+    assert [o.finish_reason for o in outs] == ["length", "error", "error", "error", "length"]
+    assert "empty" in outs[1].error and "fit" in outs[2].error and "vocabulary" in outs[3].error
+    assert outs[0].token_ids == outs[4].token_ids == plain.greedy_generate(cfg, w, ok, 4)
+
+
+def test_eos_stop_and_sampling_options_through_the_entry_point(models):
+    from carbon_engine_b200 import SamplingParams
+    d, cfg, w = models["A"]
+    p = random_tokens(np.random.default_rng(6), 12, 256)
+    free_run = plain.greedy_generate(cfg, w, p, 8)
+    eng = make_engine(d, "float32", "A")
+    stop_at = free_run[3]
+    first = free_run.index(stop_at)
+    outs = eng.generate([p, p, p, p], [
+        SamplingParams(max_tokens=8, stop_token_ids=[stop_at]),
+        SamplingParams(max_tokens=8, stop_token_ids=[stop_at], ignore_eos=True),
+        SamplingParams(max_tokens=8, temperature=0.9, top_k=1, seed=1),               # top_k 1 is greedy
+        SamplingParams(max_tokens=8, logprobs=3),
+    ])
+    assert outs[0].finish_reason == "stop" and outs[0].token_ids == free_run[:first + 1]
+    assert outs[1].finish_reason == "length" and outs[1].token_ids == free_run
+    assert outs[2].token_ids == free_run and outs[3].token_ids == free_run           # logprobs do not change tokens
+    lp = outs[3].logprobs
+    assert len(lp) == 8 and lp[0]["token"] == free_run[0] and lp[0]["top"][0][0] == free_run[0]
+    want = torch.log_softmax(plain.forward(cfg, w, p)[-1], dim=-1)
+    assert abs(lp[0]["logprob"] - float(want[free_run[0]])) < 1e-4
+    # a repetition penalty large enough forbids repeating the prompt's or the output's tokens
+    rep = eng.generate([p], SamplingParams(max_tokens=8, repetition_penalty=1e6, presence_penalty=100.0, ignore_eos=True))[0]
+    assert len(set(rep.token_ids)) == 8
+
+
+def test_dummy_weights_equal_the_written_folder(models, tmp_path):
+    """--dummy-weight makes, on the GPU, the same tensors that the random-weights mode writes."""
+    from carbon_engine_b200 import Engine, SamplingParams
+    d, cfg, w = models["B"]
+    # the written folder of this fixture has sharpened q/k norms; compare with an untouched one
+    plain_dir = make_model_dir(str(tmp_path), "B", sharpen=1.0)
+    p = random_tokens(np.random.default_rng(7), 20, cfg["vocab_size"])
+    sp = SamplingParams(max_tokens=6, ignore_eos=True)
+    a = Engine(plain_dir, dtype="float32", kv_tokens=256, page_size=8).generate([p], sp)[0]
+    b = Engine(plain_dir, dtype="float32", kv_tokens=256, page_size=8, dummy_weight=True, seed=TINY["B"]["seed"]).generate([p], sp)[0]
+    assert a.token_ids == b.token_ids
+
+
+def test_no_cpu_path():
+    from carbon_engine_b200.engine.engine import require_gpu
+    with pytest.raises(RuntimeError, match="CUDA device only"):
+        require_gpu("cpu")

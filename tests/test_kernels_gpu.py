@@ -1,0 +1,349 @@
+"""Each CUDA kernel alone against a plain PyTorch reference, at sizes other than the engine's."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen3 as plain
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+TOL = {torch.float32: 1e-5, torch.bfloat16: 2e-2}
+
+
+def dev():
+    return torch.device("cuda:0")
+
+
+def rel_err(got: torch.Tensor, want: torch.Tensor) -> float:
+    want = want.to(torch.float64).cpu()
+    return float((got.to(torch.float64).cpu() - want).abs().max() / want.abs().max().clamp_min(1e-30))
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from carbon_engine_b200 import ops as o
+    return o
+
+
+def status():
+    return torch.zeros(1, dtype=torch.int32, device=dev())
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embedding(ops, dtype):
+    V, H = 301, 80
+    table = torch.randn(V, H, device=dev()).to(dtype)
+    toks = torch.tensor([0, 300, 17, 17, 5], dtype=torch.int32, device=dev())
+    x = torch.empty(5, H, dtype=torch.float32, device=dev())
+    st = status()
+    ops.embed(table, toks, x, st)
+    assert torch.equal(x, table[toks.long()].float()) and st.item() == 0
+    bad = torch.tensor([1, 301], dtype=torch.int32, device=dev())
+    ops.embed(table, bad, x[:2], st)
+    assert st.item() == 1 and torch.equal(x[1], torch.zeros(H, device=dev()))      # flagged, not read
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H", [48, 80, 1000, 4104])
+def test_rmsnorm(ops, dtype, H):
+    x = torch.randn(7, H, device=dev()) * 3
+    w = 1 + 0.1 * torch.randn(H, device=dev())
+    out = torch.empty(7, H, dtype=dtype, device=dev())
+    ops.rmsnorm(x, w, out, 1e-5)
+    want = plain.rms_norm(x.double().cpu(), w.double().cpu(), 1e-5)
+    assert rel_err(out, want) < TOL[dtype]
+    rows = torch.tensor([6, 0, 3], dtype=torch.int32, device=dev())
+    out2 = torch.empty(3, H, dtype=dtype, device=dev())
+    ops.rmsnorm(x, w, out2, 1e-5, rows)
+    assert torch.equal(out2, out[rows.long()])
+
+
+def paged_layout(seq_lens, page_size, nkv, d, dtype, shuffle_seed=0, extra_pages=3):
+    """Block table and empty pools for sequences of the given lengths, pages handed out in a
+    shuffled order so that nothing lies where a contiguous layout would put it."""
+    need = [(n + page_size - 1) // page_size for n in seq_lens]
+    total = sum(need) + extra_pages
+    perm = np.random.default_rng(shuffle_seed).permutation(total)
+    max_pages = max(need) + 2
+    table = np.full((len(seq_lens), max_pages), -1, dtype=np.int32)
+    k = 0
+    for b, n in enumerate(need):
+        table[b, :n] = perm[k:k + n]
+        k += n
+    pool = lambda: torch.full((total, nkv, page_size, d), float("nan"), dtype=dtype, device=dev())
+    return torch.from_numpy(table).to(dev()), pool(), pool()
+
+
+def fill_pools(kp, vp, table, seq, k, v, page_size, start=0):
+    """Write k, v [n, nkv, d] of sequence ``seq`` at positions start.. into the pools (test-side)."""
+    for i in range(k.shape[0]):
+        pos = start + i
+        page = int(table[seq, pos // page_size])
+        kp[page, :, pos % page_size, :] = k[i]
+        vp[page, :, pos % page_size, :] = v[i]
+
+
+def step_meta(seqs):
+    """seqs: list of (ctx_before, q_len).  Device int32 arrays positions, seq_of_token, seq_slot."""
+    pos, sot = [], []
+    for b, (c, n) in enumerate(seqs):
+        pos += list(range(c, c + n))
+        sot += [b] * n
+    mk = lambda a: torch.tensor(a, dtype=torch.int32, device=dev())
+    return mk(pos), mk(sot), mk(list(range(len(seqs))))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,d,rd,ps", [(6, 3, 48, 48, 8), (4, 1, 16, 16, 16), (5, 5, 80, 32, 4), (2, 2, 256, 256, 64)])
+def test_qk_norm_rope_and_cache_write(ops, dtype, nh, nkv, d, rd, ps):
+    torch.manual_seed(1)
+    seqs = [(5, 9), (0, 3), (30, 1)]
+    T = sum(n for _, n in seqs)
+    table, kp, vp = paged_layout([c + n for c, n in seqs], ps, nkv, d, dtype)
+    qkv = (torch.randn(T, (nh + 2 * nkv) * d, device=dev()) * 2).to(dtype)
+    qw, kw = 1 + 0.2 * torch.randn(d, device=dev()), 1 + 0.2 * torch.randn(d, device=dev())
+    theta, eps = 3000.0, 1e-5
+    positions, sot, slots = step_meta(seqs)
+    half = rd // 2
+    inv = theta ** (-torch.arange(half, dtype=torch.float64) * 2 / rd)
+    ang = torch.arange(64, dtype=torch.float64)[:, None] * inv[None]
+    cos, sin = ang.cos().float().to(dev()), ang.sin().float().to(dev())
+    src = qkv.clone()
+    st = status()
+    ops.qk_rope_kvwrite(qkv, kp, vp, qw, kw, cos, sin, positions, sot, slots, table, st, nh, nkv, d, rd, ps, eps)
+    assert st.item() == 0
+    s64 = src.double().cpu()
+    q = s64[:, :nh * d].view(T, nh, d)
+    k = s64[:, nh * d:(nh + nkv) * d].view(T, nkv, d)
+    v = s64[:, (nh + nkv) * d:].view(T, nkv, d)
+    c, s = plain.rope_tables(positions.cpu(), rd, theta)
+    q_want = plain.apply_rope(plain.rms_norm(q, qw.double().cpu(), eps), c, s)
+    k_want = plain.apply_rope(plain.rms_norm(k, kw.double().cpu(), eps), c, s)
+    assert rel_err(qkv[:, :nh * d].view(T, nh, d), q_want) < TOL[dtype]
+    t = 0
+    for b, (ctx, n) in enumerate(seqs):
+        for i in range(n):
+            pos = ctx + i
+            page = int(table[b, pos // ps])
+            assert rel_err(kp[page, :, pos % ps, :], k_want[t]) < TOL[dtype]
+            assert torch.equal(vp[page, :, pos % ps, :].double().cpu(), v[t])          # V is copied as it is
+            t += 1
+    # nothing else was written: all other places still hold the poison
+    written = T * nkv * d
+    assert int((~torch.isnan(kp.float())).sum()) == written and int((~torch.isnan(vp.float())).sum()) == written
+
+
+def test_qk_kernel_flags_a_page_the_request_does_not_hold(ops):
+    table, kp, vp = paged_layout([4], 4, 1, 16, torch.float32)
+    qkv = torch.randn(1, 3 * 16, device=dev())
+    positions, sot, slots = step_meta([(5, 1)])               # position 5 lies in page index 1, which is not held
+    st = status()
+    ops.qk_rope_kvwrite(qkv, kp, vp, None, None, None, None, positions, sot, slots, table, st, 1, 1, 16, 0, 4, 0.0)
+    assert st.item() == 2 and torch.isnan(kp).all()
+
+
+def reference_attention(q_all, k_all, v_all, ctx, n, scale, window):
+    """Rows ctx..ctx+n of the whole-sequence attention."""
+    return plain.causal_attention(q_all, k_all, v_all, scale, window)[ctx:ctx + n]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,d,ps,window", [(6, 3, 48, 8, 0), (8, 2, 32, 16, 0), (4, 4, 16, 4, 0), (3, 1, 128, 32, 0),
+                                                 (6, 2, 64, 8, 37), (2, 1, 16, 16, 130)])
+def test_attention_generic_over_pages(ops, dtype, nh, nkv, d, ps, window):
+    torch.manual_seed(2)
+    seqs = [(0, 19), (140, 1), (257, 1), (61, 7), (0, 2), (126, 5)]       # whole, decode (past a chunk edge), portions
+    lens = [c + n for c, n in seqs]
+    table, kp, vp = paged_layout(lens, ps, nkv, d, dtype, shuffle_seed=3)
+    T = sum(n for _, n in seqs)
+    q_step = torch.empty(T, nh * d, dtype=dtype, device=dev())
+    want = []
+    t = 0
+    for b, (ctx, n) in enumerate(seqs):
+        L = ctx + n
+        q_all = (torch.randn(L, nh, d) * 1.5).to(dtype)
+        k_all = (torch.randn(L, nkv, d) * 1.5).to(dtype)
+        v_all = torch.randn(L, nkv, d).to(dtype)
+        fill_pools(kp, vp, table.cpu().numpy(), b, k_all.to(dev()), v_all.to(dev()), ps)
+        q_step[t:t + n] = q_all[ctx:].reshape(n, nh * d).to(dev())
+        want.append(reference_attention(q_all.double(), k_all.double(), v_all.double(), ctx, n, 1 / math.sqrt(d), window))
+        t += n
+    positions, sot, slots = step_meta(seqs)
+    out = torch.empty(T, nh * d, dtype=dtype, device=dev())
+    st = status()
+    ops.attention_generic(q_step, nh * d, kp, vp, out, positions, sot, slots, table, st, nh, nkv, d, ps, window,
+                          1 / math.sqrt(d))
+    assert st.item() == 0
+    assert rel_err(out.view(T, nh, d), torch.cat(want)) < (2e-5 if dtype == torch.float32 else 2e-2)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_finds_one_far_key_among_hundreds_and_respects_the_window_edge(ops, dtype):
+    """One key is made to stand out: the output must be that key's value.  It is put at the first
+    position, at a page's last place, right at the window's edge and one before it."""
+    nh, nkv, d, ps = 2, 1, 32, 16
+    L = 700
+    torch.manual_seed(3)
+    for far, window, visible in ((0, 0, True), (15, 0, True), (699 - 99, 100, True), (699 - 100, 100, False), (383, 0, True)):
+        table, kp, vp = paged_layout([L], ps, nkv, d, dtype, shuffle_seed=far)
+        k_all = torch.randn(L, nkv, d) * 0.1
+        v_all = torch.randn(L, nkv, d)
+        q = torch.randn(1, nh, d)
+        k_all[far, 0] = q[0, 1] * 4.0              # head 1's score for this key: 4 |q|^2 / sqrt(d), far above the rest
+        k_all, v_all, q = k_all.to(dtype), v_all.to(dtype), q.to(dtype)
+        fill_pools(kp, vp, table.cpu().numpy(), 0, k_all.to(dev()), v_all.to(dev()), ps)
+        positions, sot, slots = step_meta([(L - 1, 1)])
+        out = torch.empty(1, nh * d, dtype=dtype, device=dev())
+        st = status()
+        ops.attention_generic(q.reshape(1, nh * d).to(dev()), nh * d, kp, vp, out, positions, sot, slots, table, st,
+                              nh, nkv, d, ps, window, 1.0)
+        got = out.view(nh, d)[1].float().cpu()
+        hit = (got - v_all[far, 0].float()).abs().max() < 0.05
+        assert bool(hit) == visible, (far, window)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("M,N,K", [(1, 7, 5), (3, 64, 16), (65, 129, 33), (130, 70, 200), (2, 301, 80)])
+def test_gemm_plain_all_epilogues(ops, dtype, M, N, K):
+    torch.manual_seed(4)
+    a = torch.randn(M, K, device=dev()).to(dtype)
+    w = torch.randn(N, K, device=dev()).to(dtype)
+    ref = a.double().cpu() @ w.double().cpu().T
+    c = torch.empty(M, N, dtype=dtype, device=dev())
+    ops.gemm_plain(a, w, c, ops.GEMM_STORE)
+    assert rel_err(c, ref) < TOL[dtype]
+    c32 = torch.empty(M, N, dtype=torch.float32, device=dev())
+    ops.gemm_plain(a, w, c32, ops.GEMM_STORE_F32)
+    assert rel_err(c32, ref) < 1e-5
+    x = torch.randn(M, N, device=dev())
+    x0 = x.clone()
+    ops.gemm_plain(a, w, x, ops.GEMM_ACCUM_F32)
+    assert rel_err(x, x0.double().cpu() + ref) < 1e-5
+    w2 = torch.randn(2 * N, K, device=dev()).to(dtype)
+    g = a.double().cpu() @ w2[:N].double().cpu().T
+    u = a.double().cpu() @ w2[N:].double().cpu().T
+    s = torch.empty(M, N, dtype=dtype, device=dev())
+    ops.gemm_plain(a, w2, s, ops.GEMM_SWIGLU)
+    assert rel_err(s, g * torch.sigmoid(g) * u) < TOL[dtype]
+
+
+def test_gemm_plain_rows_do_not_depend_on_their_neighbours(ops):
+    """The same row gives the same bits whatever else is in the batch."""
+    a = torch.randn(77, 96, device=dev())
+    w = torch.randn(50, 96, device=dev())
+    full = torch.empty(77, 50, device=dev())
+    ops.gemm_plain(a, w, full, ops.GEMM_STORE)
+    one = torch.empty(1, 50, device=dev())
+    ops.gemm_plain(a[70:71].contiguous(), w, one, ops.GEMM_STORE)
+    assert torch.equal(one[0], full[70])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_swiglu_and_residual_add(ops, dtype):
+    gu = torch.randn(5, 2 * 112, device=dev()).to(dtype)
+    out = torch.empty(5, 112, dtype=dtype, device=dev())
+    ops.swiglu(gu, out)
+    g, u = gu[:, :112].double().cpu(), gu[:, 112:].double().cpu()
+    assert rel_err(out, g * torch.sigmoid(g) * u) < TOL[dtype]
+    x = torch.randn(5, 80, device=dev())
+    dlt = torch.randn(5, 80, device=dev()).to(dtype)
+    want = x.double().cpu() + dlt.double().cpu()
+    ops.add_residual(x, dlt)
+    assert rel_err(x, want) < 1e-6
+
+
+def test_scatter_i32(ops):
+    dst = torch.full((4, 5), -1, dtype=torch.int32, device=dev())
+    ops.scatter_i32(dst, torch.tensor([0, 7, 19], dtype=torch.int32, device=dev()),
+                    torch.tensor([4, 5, 6], dtype=torch.int32, device=dev()))
+    want = torch.full((20,), -1, dtype=torch.int32)
+    want[[0, 7, 19]] = torch.tensor([4, 5, 6], dtype=torch.int32)
+    assert torch.equal(dst.cpu().view(-1), want)
+
+
+def test_argmax_takes_the_first_maximum(ops):
+    V = 151936 // 8 + 3
+    logits = torch.randn(3, V, device=dev())
+    logits[0, 777] = 50.0
+    logits[0, 12000] = 50.0                 # a tie: the lower index wins (src/sampling.rs:96-106)
+    logits[1, V - 1] = 60.0
+    logits[2] = -1.0                        # all equal: index 0
+    out = torch.empty(3, dtype=torch.int32, device=dev())
+    ops.argmax(logits, out)
+    assert out.tolist() == [777, V - 1, 0]
+
+
+def run_sampler(ops, logits, rows):
+    params = torch.from_numpy(np.frombuffer(ops.pack_sample_rows(rows), dtype=np.uint8).copy()).to(dev())
+    out = torch.empty(logits.shape[0], dtype=torch.int32, device=dev())
+    ops.sample(logits, params, out)
+    return out.tolist()
+
+
+def gumbel_reference(logits_row, temperature, kept, seed):
+    """The draw the kernel makes, from the same counter-based uniforms (src/kernels/sampling.cu:30-42)."""
+    from carbon_engine_b200.sampling.sampler import mix64
+    best, best_i = -1e300, -1
+    for i in sorted(int(k) for k in kept):
+        h = mix64(seed ^ mix64((i + 0x632BE59BD9B4E019) & ((1 << 64) - 1)))
+        u = ((h >> 40) + 0.5) / 16777216.0
+        g = float(logits_row[i]) / max(temperature, 1e-5) - math.log(-math.log(u))
+        if g > best:
+            best, best_i = g, i
+    return best_i
+
+
+def test_sampler_options_follow_the_host_rules(ops):
+    rng = np.random.default_rng(5)
+    V = 1000
+    logits = torch.from_numpy(rng.normal(size=(6, V)).astype(np.float32) * 3).to(dev())
+    rows = [(0.0, 1.0, 0.0, 0, 1), (0.8, 1.0, 0.0, 1, 2), (0.8, 1.0, 0.0, 5, 3), (1.3, 0.6, 0.0, 0, 4),
+            (0.7, 1.0, 0.2, 0, 5), (1.0, 0.9, 0.05, 50, 6)]
+    got = run_sampler(ops, logits, rows)
+    host = logits.cpu().numpy()
+    assert got[0] == int(host[0].argmax()) and got[1] == int(host[1].argmax())     # temperature 0, top_k 1: greedy
+    for r in range(2, 6):
+        t, p, m, k, seed = rows[r]
+        kept, _ = plain.sample_kept_set(host[r], t, k, p, m)
+        assert got[r] in set(kept.tolist()), r
+        assert got[r] == gumbel_reference(host[r], t, kept, seed), r
+    assert run_sampler(ops, logits, rows) == got                                    # same seeds, same tokens
+    other = run_sampler(ops, logits, [(t, p, m, k, s + 100) for (t, p, m, k, s) in rows])
+    assert other[:2] == got[:2] and other[2:] != got[2:]
+
+
+def test_sampler_draws_from_the_softmax(ops):
+    probs = np.array([0.4, 0.3, 0.15, 0.1, 0.05])
+    n = 4000
+    logits = torch.from_numpy(np.tile(np.log(probs).astype(np.float32) * 0.7, (n, 1))).to(dev())   # temperature undoes the 0.7
+    got = np.array(run_sampler(ops, logits, [(0.7, 1.0, 0.0, 0, 1000 + i) for i in range(n)]))
+    freq = np.bincount(got, minlength=5) / n
+    assert np.abs(freq - probs).max() < 0.03
+    got = np.array(run_sampler(ops, logits, [(0.7, 0.8, 0.0, 0, 5000 + i) for i in range(n)]))    # nucleus: 0.4+0.3+0.15
+    freq = np.bincount(got, minlength=5) / n
+    assert freq[3] == 0 and freq[4] == 0 and np.abs(freq[:3] - probs[:3] / 0.85).max() < 0.03
+
+
+def test_penalties(ops):
+    logits = torch.tensor([[2.0, -2.0, 1.0, 0.5], [1.0, 1.0, 1.0, 1.0]], device=dev())
+    # row 0: token 0 seen in the prompt, token 1 generated twice, token 2 generated once; row 1 has no penalties
+    entries = torch.tensor([[0, 0, 1, 0], [0, 1, 1, 2], [0, 2, 1, 1]], dtype=torch.int32, device=dev())
+    row_params = torch.tensor([[2.0, 0.5, 0.25], [1.0, 0.0, 0.0]], device=dev())
+    ops.apply_penalties(logits, entries, row_params)
+    want = [[2.0 / 2, -2.0 * 2 - (0.5 + 0.25 * 2), 1.0 / 2 - (0.5 + 0.25), 0.5], [1.0, 1.0, 1.0, 1.0]]
+    assert torch.allclose(logits.cpu(), torch.tensor(want))
+
+
+def test_kernels_refuse_sizes_they_cannot_take(ops):
+    from carbon_engine_b200.csrc.kernel_lib import KernelError
+    with pytest.raises(KernelError, match="head_dim"):
+        table, kp, vp = paged_layout([4], 4, 1, 2048, torch.float32)
+        positions, sot, slots = step_meta([(0, 1)])
+        q = torch.zeros(1, 2048, device=dev())
+        ops.attention_generic(q, 2048, kp, vp, torch.empty(1, 2048, device=dev()), positions, sot, slots, table,
+                              status(), 1, 1, 2048, 4, 0, 1.0)
+    with pytest.raises(KernelError, match="CUDA tensor"):
+        ops.rmsnorm(torch.zeros(1, 8), torch.ones(8), torch.zeros(1, 8), 1e-6)

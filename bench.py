@@ -1,0 +1,188 @@
+#!/usr/bin/env python3
+"""Benchmark of the engine's decode step (and a 2,048-token prefill) at Qwen3-8B layer sizes.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L] [--impl ours|reference]
+
+Prints ONE JSON line.  ``value`` is decoded tokens per second at the given batch (default 8), each
+sequence holding ``context_len`` tokens of context, timed on the device with CUDA events around
+exactly K decode steps after W warm-up steps; a step includes the greedy pick of every sequence's
+next token on the device.  ``e2e`` is the same measured through the Python entry point (the
+scheduler, the step function and the sampler): every step copies its inputs from pinned host memory
+to the device and reads the sampled tokens back to the host.  ``prefill`` is one 2,048-token prompt
+in one step; ``roofline`` compares the bytes a decode step has to read (every weight once, and the
+cache of the live requests) with the measured copy bandwidth; ``points`` holds decode at batch 1 and
+64.  Weights are random (seeded), token ids are uniform-random (seeded): no dataset is involved.
+The weights alone (over 15 GB) exceed the L2 cache many times over, so no flush is needed between
+steps.  Runs on one GPU only.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+SIZES_8B = dict(num_hidden_layers=36, hidden_size=4096, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
+                intermediate_size=12288, vocab_size=151936, rope_theta=1e6, rms_norm_eps=1e-6,
+                tie_word_embeddings=False, max_position_embeddings=40960)
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            with open(path) as fh:
+                p = json.load(fh)
+            return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"]),
+                    "bf16_tflops_sustained": float(p.get("bf16_tflops_sustained", p["bf16_tflops"])), "source": "measured"}
+        except (OSError, ValueError, KeyError):
+            pass
+    return dict(FALLBACK_PEAKS, bf16_tflops_sustained=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.samples, self.proc = [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.samples.append((time.time(), line.strip()))
+
+    def mark(self):
+        return time.time()
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+
+    def summary(self, t0, t1):
+        mhz, mx, reasons = [], 0, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for t, line in self.samples:
+            if not (t0 - 0.05 <= t <= t1 + 0.15):
+                continue
+            f = [x.strip() for x in line.split(",")]
+            try:
+                mhz.append(int(f[0])); mx = max(mx, int(f[1]))
+            except (ValueError, IndexError):
+                continue
+            for n, v in zip(names, f[2:]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": int(statistics.median(mhz)) if mhz else None, "sm_max_mhz": mx or None,
+                "reasons": sorted(reasons), "samples": len(mhz)}
+
+
+def decode_bytes(cfg, layers, batch, ctx, el=2):
+    H, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    q, kv = cfg["num_attention_heads"] * cfg["head_dim"], cfg["num_key_value_heads"] * cfg["head_dim"]
+    per_layer = (q + 2 * kv) * H + H * q + 3 * H * I + 2 * H + 2 * cfg["head_dim"]
+    weights = layers * per_layer + V * H + H + batch * H            # head, final norm, the embedding rows that are read
+    cache = layers * 2 * kv * ctx * batch
+    return (weights + cache) * el
+
+
+def prefill_flops(cfg, layers, T):
+    H, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    nh, d = cfg["num_attention_heads"], cfg["head_dim"]
+    q, kv = nh * d, cfg["num_key_value_heads"] * d
+    linear = 2 * T * ((q + 2 * kv) * H + H * q + 3 * H * I)
+    attn = 4 * d * nh * T * (T + 1) // 2
+    return layers * (linear + attn) + 2 * V * H
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=2048, help="tokens of context each sequence holds when decoding starts")
+    ap.add_argument("--layers", type=int, default=SIZES_8B["num_hidden_layers"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
+    ap.add_argument("--no-graphs", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable": "the reference is a Rust crate on the candle library: no "
+                          "Python package to install offline, and neither cargo/rustc nor its crates are on this machine"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU only; --gpus {args.gpus} is not supported")
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import torch
+    from carbon_engine_b200.bench_support import BenchHarness
+    pk = peaks()
+    cfg = dict(SIZES_8B, num_hidden_layers=args.layers)
+    h = BenchHarness(cfg, max_batch=max(64 if not args.no_points else args.batch, args.batch), context=args.context,
+                     new_tokens=max(256, args.steps + args.warmup + 8), graphs=not args.no_graphs)
+    clocks = ClockSampler()
+    clocks.start()
+    time.sleep(0.3)
+
+    t0 = clocks.mark()
+    main_run = h.decode(args.batch, args.steps, args.warmup)
+    t1 = clocks.mark()
+    e2e = h.decode_e2e(args.batch, args.steps, args.warmup)
+    points, prefill = {}, None
+    if not args.no_points:
+        for b in (1, 64):
+            r = h.decode(b, min(args.steps, 32), 3)
+            points[f"decode_b{b}"] = round(r["tokens_per_s"], 1)
+        pf = h.prefill(2048, 3, 3)
+        flops = prefill_flops(cfg, args.layers, 2048)
+        prefill = {"value": round(2048 / (pf["ms"] / 1e3), 1), "tokens": 2048, "ms": round(pf["ms"], 3),
+                   "frac": round(flops / (pf["ms"] / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
+    clocks.stop()
+
+    ms = main_run["ms_per_step"]
+    need = decode_bytes(cfg, args.layers, args.batch, args.context + args.warmup + args.steps // 2)
+    achieved = need / (ms / 1e3) / 1e9
+    out = {
+        "metric": "decode tok/s at batch 8 (Qwen3-8B sizes, bf16, 2048-token contexts)", "value": round(main_run["tokens_per_s"], 1),
+        "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic: seeded random weights, seeded uniform-random token ids", "impl": "ours",
+        "config": {"model": "Qwen3-8B sizes", "layers": args.layers, "layers_of_model": SIZES_8B["num_hidden_layers"],
+                   "hidden_size": cfg["hidden_size"], "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
+                   "head_dim": cfg["head_dim"], "intermediate_size": cfg["intermediate_size"], "vocab_size": cfg["vocab_size"],
+                   "global_batch": args.batch, "seq_len": args.context, "max_seq_len": 4096, "new_tokens": args.steps,
+                   "page_size": h.page_size, "parallelism": "single GPU", "cuda_graphs": h.graphs,
+                   "l2": "inputs larger than L2 (weights over 15 GB per step)", "peaks": pk["source"]},
+        "clocks": clocks.summary(t0, t1),
+        "e2e": {"value": round(e2e["tokens_per_s"], 1), "unit": "tokens/s", "ms_per_step": round(e2e["ms_per_step"], 4),
+                "h2d_bytes_per_step": e2e["h2d_bytes"], "d2h_bytes_per_step": e2e["d2h_bytes"]},
+        "gpu_launches": main_run["launches"],
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+    }
+    if prefill is not None:
+        out["prefill"] = prefill
+        out["points"] = points
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

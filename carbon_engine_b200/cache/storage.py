@@ -77,6 +77,9 @@ class CacheStorage:
             return base
         return LayerCacheView(base.kind, base.group, base.page_size, base.k_pool, base.v_pool, base.state, False)
 
+    def paged_views(self) -> List[LayerCacheView]:
+        return [e for e in self._entries.values() if e.kind == "paged"]
+
     def bytes_per_token(self) -> int:
         total = 0
         for e in self._entries.values():

@@ -45,6 +45,7 @@ class StepBuffers:
         self.host_np = self.host.numpy()
         self.dev = torch.zeros(self.total, dtype=torch.int32, device=device)
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        self._uploaded = None
 
     def host_section(self, name: str) -> np.ndarray:
         off, n = self.offsets[name]
@@ -54,8 +55,17 @@ class StepBuffers:
         off, cap = self.offsets[name]
         return self.dev[off:off + (cap if n is None else n)]
 
+    def wait_host_free(self) -> None:
+        """Block until the last upload has left the pinned buffer, so that it may be rewritten."""
+        if self._uploaded is not None:
+            self._uploaded.synchronize()
+
     def upload(self) -> int:
         self.dev.copy_(self.host, non_blocking=True)
+        if self.dev.is_cuda:
+            if self._uploaded is None:
+                self._uploaded = torch.cuda.Event()
+            self._uploaded.record()
         return self.total * 4
 
 

@@ -36,6 +36,7 @@ class ModelRunner:
         self.max_step_tokens = int(max_step_tokens)
         self.bufs = StepBuffers(self.max_step_tokens, storage.max_requests, len(storage.groups), self.device)
         self.fast_attention = True
+        self.graphs_enabled = False
         self.h2d_bytes_last = 0
         self.kernel_launches = 0
 
@@ -81,6 +82,7 @@ class ModelRunner:
                     raise StepError(f"request {e.request_id}: wanted place {w} is outside its {len(e.tokens)} tokens")
 
         b = self.bufs
+        b.wait_host_free()
         h_tok, h_pos, h_seq = b.host_section("tokens"), b.host_section("positions"), b.host_section("seq_of_token")
         h_slot, h_qs, h_ctx = b.host_section("seq_slot"), b.host_section("q_start"), b.host_section("ctx_len")
         ctx = StepContext(b, T, len(entries), self.dtype, self.device, self.storage.device_tables)

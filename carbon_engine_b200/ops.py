@@ -42,9 +42,24 @@ def _need(t: torch.Tensor, name: str, dtype=None) -> None:
         raise KernelError(f"{name} must be {dtype}, got {t.dtype}")
 
 
-def _ok(code: int) -> None:
+_launches = 0
+
+
+def launch_count() -> int:
+    """Kernels launched through this module so far (replays of captured graphs included)."""
+    return _launches
+
+
+def add_launches(n: int) -> None:
+    global _launches
+    _launches += n
+
+
+def _ok(code: int, n: int = 1) -> None:
+    global _launches
     if code != 0:
         raise KernelError(kernels().ce_last_error().decode())
+    _launches += n
 
 
 def embed(table: torch.Tensor, tokens: torch.Tensor, x: torch.Tensor, status: torch.Tensor) -> None:

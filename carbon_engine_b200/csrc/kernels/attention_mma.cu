@@ -1,0 +1,476 @@
+// bfloat16 attention over the paged cache on the tensor cores (mma.sync m16n8k16, float32
+// accumulators): a split-KV kernel for sequences that bring one token, and a flash kernel for
+// sequences that bring a portion of a prompt.  Both read keys and values through the block table.
+//
+// Decode: one block per (sequence, KV head, group of up to 16 query heads, split of 256 positions).
+// The query heads that share the KV head are the 16 rows of the MMA tile, so K and V are read once
+// per KV head (the reference's paged_decode_tc does the same for up to 8 heads,
+// src/kernels/attention_tc.cu:682-807).  Each of the 4 warps takes 16 of every 64 staged keys and
+// keeps a running (max, sum, output); the warps are combined in shared memory and the block writes
+// one partial per split to scratch memory; a merge kernel combines the splits
+// (src/kernels/attention_tc.cu:810-830).  Splits are cut at fixed positions, so a sequence's result
+// does not depend on the batch or on the longest sequence beside it.
+//
+// Prefill: one block per (tile of 64 new tokens of one sequence, query head); each warp owns 16
+// queries, keys are staged 64 at a time, causal and window limits are applied per row
+// (src/kernels/attention_tc.cu:180-565 is the reference's counterpart).
+//
+// Scores are scaled in float32, the softmax runs in float32 with exp2, probabilities are rounded to
+// bfloat16 for the PV product (as in src/kernels/attention_tc.cu:505-515), outputs are rounded once.
+#include "common.cuh"
+
+#define AM_THREADS 128
+#define AM_TILE 64           // keys staged per iteration
+#define AM_SPLIT 256         // positions per decode split
+#define AM_PAD 8             // padding of a staged row, in elements (keeps 32-bit and ldmatrix reads conflict-free)
+
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const bf16* p) {
+    uint32_t addr = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void cp_async16(bf16* dst, const bf16* src, bool valid) {
+    uint32_t addr = (uint32_t)__cvta_generic_to_shared(dst);
+    int n = valid ? 16 : 0;      // 0 bytes read: the 16 bytes are filled with zeros
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(addr), "l"(src), "r"(n));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+struct MmaAttnArgs {
+    const bf16* q;              // [T, q_stride]; head h at column h*d
+    const bf16* k_pool;         // [num_pages, nkv, page_size, d]
+    const bf16* v_pool;
+    bf16* out;                  // [T, nh*d]
+    float* part_o;              // decode scratch [rows, nh, max_splits, d]
+    float* part_ml;             // decode scratch [rows, nh, max_splits, 2]
+    const int* positions;       // [T]
+    const int* seq_slot;        // [B]
+    const int* q_start;         // [B+1]
+    const int* ctx_len;         // [B]  keys of the sequence after this step
+    const int* block_table;     // [slots, max_pages]
+    const int* tiles;           // prefill: [n_tiles, 2] = (sequence, first new token of the tile)
+    int* status;
+    int nh, nkv, d, q_stride, page_size, max_pages, num_pages, window, max_splits, first_seq;
+    float scale_log2;           // scale * log2(e)
+};
+
+// Stage keys [k0, k0 + AM_TILE) of one KV head into shared memory rows of d + AM_PAD elements.
+// Keys outside [lo, hi] are filled with zeros, so that a masked probability of 0 never meets a NaN.
+__device__ __forceinline__ void stage_tile(bf16* Ks, bf16* Vs, const MmaAttnArgs& a, const int* table, int kvh, int k0,
+                                           int lo, int hi) {
+    int d = a.d, ld = d + AM_PAD, chunks = d / 8;
+    for (int c = threadIdx.x; c < AM_TILE * chunks; c += AM_THREADS) {
+        int kl = c / chunks, part = c - kl * chunks;
+        int key = k0 + kl;
+        bool valid = key >= lo && key <= hi;
+        size_t row = 0;
+        if (valid) {
+            int page = table[key / a.page_size];
+            if (page < 0 || page >= a.num_pages) {
+                atomicExch(a.status, 4);
+                valid = false;
+            } else {
+                row = (((size_t)page * a.nkv + kvh) * a.page_size + key % a.page_size) * d + part * 8;
+            }
+        }
+        cp_async16(Ks + kl * ld + part * 8, a.k_pool + row, valid);
+        cp_async16(Vs + kl * ld + part * 8, a.v_pool + row, valid);
+    }
+}
+
+// One warp: scores of its 16 rows against NK8*8 staged keys, online softmax, output update.
+// lo/hi: first and last visible key of rows (lane/4) and (lane/4 + 8).
+template <int DMAX, int NK8>
+__device__ __forceinline__ void warp_tile(const uint32_t (&qf)[DMAX / 16][4], float (&o)[DMAX / 8][4], float (&m)[2],
+                                          float (&l)[2], const bf16* Ks, const bf16* Vs, int ld, int d, int key_base,
+                                          const int (&lo)[2], const int (&hi)[2], float scale_log2) {
+    int lane = threadIdx.x & 31, quad = lane & 3, grp = lane >> 2;
+    float s[NK8][4];
+#pragma unroll
+    for (int j = 0; j < NK8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+#pragma unroll
+    for (int kk = 0; kk < DMAX / 16; ++kk) {
+        if (kk * 16 < d) {
+#pragma unroll
+            for (int j = 0; j < NK8; ++j) {
+                const bf16* kp = Ks + (j * 8 + grp) * ld + kk * 16 + 2 * quad;
+                uint32_t b0 = *reinterpret_cast<const uint32_t*>(kp);
+                uint32_t b1 = *reinterpret_cast<const uint32_t*>(kp + 8);
+                mma16816(s[j], qf[kk], b0, b1);
+            }
+        }
+    }
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int j = 0; j < NK8; ++j) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            int r = e >> 1;
+            int key = key_base + j * 8 + 2 * quad + (e & 1);
+            float v = (key >= lo[r] && key <= hi[r]) ? s[j][e] * scale_log2 : -INFINITY;
+            s[j][e] = v;
+            mx[r] = fmaxf(mx[r], v);
+        }
+    }
+    float alpha[2], muse[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+        float mn = fmaxf(m[r], mx[r]);
+        muse[r] = mn == -INFINITY ? 0.f : mn;
+        alpha[r] = exp2f(m[r] - muse[r]);
+        m[r] = mn;
+        l[r] *= alpha[r];
+    }
+#pragma unroll
+    for (int j = 0; j < NK8; ++j) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            float p = exp2f(s[j][e] - muse[e >> 1]);
+            s[j][e] = p;
+            l[e >> 1] += p;
+        }
+    }
+#pragma unroll
+    for (int dn = 0; dn < DMAX / 8; ++dn) {
+        o[dn][0] *= alpha[0]; o[dn][1] *= alpha[0]; o[dn][2] *= alpha[1]; o[dn][3] *= alpha[1];
+    }
+#pragma unroll
+    for (int c = 0; c < NK8 / 2; ++c) {
+        uint32_t pa[4] = {pack_bf16(s[2 * c][0], s[2 * c][1]), pack_bf16(s[2 * c][2], s[2 * c][3]),
+                          pack_bf16(s[2 * c + 1][0], s[2 * c + 1][1]), pack_bf16(s[2 * c + 1][2], s[2 * c + 1][3])};
+        int mi = lane >> 3, rr = lane & 7;
+        const bf16* vrow = Vs + (c * 16 + (mi & 1) * 8 + rr) * ld + (mi >> 1) * 8;
+#pragma unroll
+        for (int dn = 0; dn < DMAX / 8; dn += 2) {
+            if (dn * 8 < d) {
+                uint32_t vb[4];
+                ldmatrix_x4_trans(vb, vrow + dn * 8);
+                mma16816(o[dn], pa, vb[0], vb[1]);
+                mma16816(o[dn + 1], pa, vb[2], vb[3]);
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Decode: grid (n_seqs * max_splits, nkv, head groups of 16)
+// ---------------------------------------------------------------------------------------------
+template <int DMAX>
+__global__ void __launch_bounds__(AM_THREADS) attention_decode_kernel(MmaAttnArgs a) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    int b = blockIdx.x / a.max_splits, split = blockIdx.x % a.max_splits;
+    int kvh = blockIdx.y, hg = blockIdx.z;
+    int G = a.nh / a.nkv;
+    int t = a.q_start[b];                         // the sequence's single token
+    int pos = a.positions[t];
+    int lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
+    int k_begin = split * AM_SPLIT, k_end = min(k_begin + AM_SPLIT, pos + 1);
+    if (k_begin > pos || k_end <= lo) return;     // the merge kernel skips these splits too
+    const int* table = a.block_table + (size_t)a.seq_slot[b] * a.max_pages;
+    int d = a.d, ld = d + AM_PAD;
+    bf16* Ks = reinterpret_cast<bf16*>(smem_raw);
+    bf16* Vs = Ks + 2 * AM_TILE * ld;             // two stages of each
+
+    int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, quad = lane & 3, grp = lane >> 2;
+    int heads_here = min(16, G - hg * 16);
+    uint32_t qf[DMAX / 16][4];
+    {
+        int h0 = kvh * G + hg * 16;
+        const bf16* q0 = a.q + (size_t)t * a.q_stride + (size_t)(h0 + grp) * d;
+        const bf16* q1 = q0 + (size_t)8 * d;
+        bool v0 = grp < heads_here, v1 = grp + 8 < heads_here;
+#pragma unroll
+        for (int kk = 0; kk < DMAX / 16; ++kk) {
+            int col = kk * 16 + 2 * quad;
+            bool in = kk * 16 < d;
+            qf[kk][0] = (in && v0) ? *reinterpret_cast<const uint32_t*>(q0 + col) : 0u;
+            qf[kk][1] = (in && v1) ? *reinterpret_cast<const uint32_t*>(q1 + col) : 0u;
+            qf[kk][2] = (in && v0) ? *reinterpret_cast<const uint32_t*>(q0 + col + 8) : 0u;
+            qf[kk][3] = (in && v1) ? *reinterpret_cast<const uint32_t*>(q1 + col + 8) : 0u;
+        }
+    }
+    float o[DMAX / 8][4];
+#pragma unroll
+    for (int i = 0; i < DMAX / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    int los[2] = {lo, lo}, his[2] = {pos, pos};
+
+    int n_tiles = (k_end - k_begin + AM_TILE - 1) / AM_TILE;
+    stage_tile(Ks, Vs, a, table, kvh, k_begin, lo, pos);
+    cp_async_commit();
+    for (int it = 0; it < n_tiles; ++it) {
+        int cur = it & 1;
+        if (it + 1 < n_tiles)
+            stage_tile(Ks + (cur ^ 1) * AM_TILE * ld, Vs + (cur ^ 1) * AM_TILE * ld, a, table, kvh,
+                       k_begin + (it + 1) * AM_TILE, lo, pos);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        int k0 = k_begin + it * AM_TILE + warp * 16;
+        if (k0 <= pos)
+            warp_tile<DMAX, 2>(qf, o, m, l, Ks + (cur * AM_TILE + warp * 16) * ld, Vs + (cur * AM_TILE + warp * 16) * ld,
+                               ld, d, k0, los, his, a.scale_log2);
+        __syncthreads();
+    }
+    cp_async_wait<0>();
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+    }
+    // combine the 4 warps through shared memory (the staging buffers are free now)
+    float* so = reinterpret_cast<float*>(smem_raw);          // [4][16][d]
+    float* sm = so + 4 * 16 * d;                             // [4][16]
+    float* sl = sm + 64;                                     // [4][16]
+#pragma unroll
+    for (int dn = 0; dn < DMAX / 8; ++dn) {
+        if (dn * 8 < d) {
+            int col = dn * 8 + 2 * quad;
+            so[(warp * 16 + grp) * d + col] = o[dn][0];
+            so[(warp * 16 + grp) * d + col + 1] = o[dn][1];
+            so[(warp * 16 + grp + 8) * d + col] = o[dn][2];
+            so[(warp * 16 + grp + 8) * d + col + 1] = o[dn][3];
+        }
+    }
+    if (quad == 0) {
+        sm[warp * 16 + grp] = m[0]; sm[warp * 16 + grp + 8] = m[1];
+        sl[warp * 16 + grp] = l[0]; sl[warp * 16 + grp + 8] = l[1];
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < heads_here * d; e += AM_THREADS) {
+        int r = e / d, col = e - r * d;
+        float M = fmaxf(fmaxf(sm[r], sm[16 + r]), fmaxf(sm[32 + r], sm[48 + r]));
+        float acc = 0.f, L = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            float f = sm[w * 16 + r] == -INFINITY ? 0.f : exp2f(sm[w * 16 + r] - M);
+            acc += so[(w * 16 + r) * d + col] * f;
+            L += sl[w * 16 + r] * f;
+        }
+        int h = kvh * G + hg * 16 + r;
+        size_t base = ((size_t)b * a.nh + h) * a.max_splits + split;
+        a.part_o[base * d + col] = acc;
+        if (col == 0) {
+            a.part_ml[base * 2] = M;
+            a.part_ml[base * 2 + 1] = L;
+        }
+    }
+}
+
+// grid (n_seqs, nh): out[t, h, :] = sum_s O_s 2^(m_s - M) / sum_s l_s 2^(m_s - M)
+__global__ void attention_merge_kernel(MmaAttnArgs a) {
+    int b = blockIdx.x, h = blockIdx.y;
+    int t = a.q_start[b];
+    int pos = a.positions[t];
+    int lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
+    int s0 = lo / AM_SPLIT, s1 = pos / AM_SPLIT;            // splits that hold visible keys
+    size_t base = ((size_t)b * a.nh + h) * a.max_splits;
+    float M = -INFINITY;
+    for (int s = s0; s <= s1; ++s) M = fmaxf(M, a.part_ml[(base + s) * 2]);
+    float L = 0.f;
+    for (int s = s0; s <= s1; ++s) {
+        float ms = a.part_ml[(base + s) * 2];
+        L += ms == -INFINITY ? 0.f : a.part_ml[(base + s) * 2 + 1] * exp2f(ms - M);
+    }
+    float inv = L > 0.f ? 1.0f / L : 0.f;
+    for (int col = threadIdx.x; col < a.d; col += blockDim.x) {
+        float acc = 0.f;
+        for (int s = s0; s <= s1; ++s) {
+            float ms = a.part_ml[(base + s) * 2];
+            if (ms != -INFINITY) acc += a.part_o[(base + s) * a.d + col] * exp2f(ms - M);
+        }
+        a.out[((size_t)t * a.nh + h) * a.d + col] = __float2bfloat16_rn(acc * inv);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Prefill: grid (n_tiles, nh)
+// ---------------------------------------------------------------------------------------------
+template <int DMAX>
+__global__ void __launch_bounds__(AM_THREADS) attention_prefill_kernel(MmaAttnArgs a) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    int b = a.tiles[2 * blockIdx.x], q0 = a.tiles[2 * blockIdx.x + 1];
+    int h = blockIdx.y, kvh = h / (a.nh / a.nkv);
+    int t0 = a.q_start[b], q_len = a.q_start[b + 1] - t0;
+    int ctx_before = a.ctx_len[b] - q_len;
+    int nq = min(64, q_len - q0);
+    int p_first = ctx_before + q0, p_last = p_first + nq - 1;
+    int lo_tile = a.window > 0 ? max(0, p_first - a.window + 1) : 0;
+    const int* table = a.block_table + (size_t)a.seq_slot[b] * a.max_pages;
+    int d = a.d, ld = d + AM_PAD;
+    bf16* Ks = reinterpret_cast<bf16*>(smem_raw);
+    bf16* Vs = Ks + 2 * AM_TILE * ld;
+
+    int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, quad = lane & 3, grp = lane >> 2;
+    int r0 = warp * 16 + grp, r1 = r0 + 8;                   // this thread's two query rows within the tile
+    bool v0 = r0 < nq, v1 = r1 < nq;
+    uint32_t qf[DMAX / 16][4];
+    {
+        const bf16* qa = a.q + (size_t)(t0 + q0 + r0) * a.q_stride + (size_t)h * d;
+        const bf16* qb = a.q + (size_t)(t0 + q0 + r1) * a.q_stride + (size_t)h * d;
+#pragma unroll
+        for (int kk = 0; kk < DMAX / 16; ++kk) {
+            int col = kk * 16 + 2 * quad;
+            bool in = kk * 16 < d;
+            qf[kk][0] = (in && v0) ? *reinterpret_cast<const uint32_t*>(qa + col) : 0u;
+            qf[kk][1] = (in && v1) ? *reinterpret_cast<const uint32_t*>(qb + col) : 0u;
+            qf[kk][2] = (in && v0) ? *reinterpret_cast<const uint32_t*>(qa + col + 8) : 0u;
+            qf[kk][3] = (in && v1) ? *reinterpret_cast<const uint32_t*>(qb + col + 8) : 0u;
+        }
+    }
+    float o[DMAX / 8][4];
+#pragma unroll
+    for (int i = 0; i < DMAX / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    int his[2] = {v0 ? p_first + r0 : -1, v1 ? p_first + r1 : -1};
+    int los[2] = {a.window > 0 ? max(0, his[0] - a.window + 1) : 0, a.window > 0 ? max(0, his[1] - a.window + 1) : 0};
+    int warp_hi = p_first + min(warp * 16 + 15, nq - 1);     // last key any row of this warp sees
+    int warp_lo = a.window > 0 ? max(0, p_first + warp * 16 - a.window + 1) : 0;
+
+    int k_begin = lo_tile / AM_TILE * AM_TILE;
+    int n_tiles = (p_last - k_begin) / AM_TILE + 1;
+    stage_tile(Ks, Vs, a, table, kvh, k_begin, lo_tile, p_last);
+    cp_async_commit();
+    for (int it = 0; it < n_tiles; ++it) {
+        int cur = it & 1;
+        if (it + 1 < n_tiles)
+            stage_tile(Ks + (cur ^ 1) * AM_TILE * ld, Vs + (cur ^ 1) * AM_TILE * ld, a, table, kvh,
+                       k_begin + (it + 1) * AM_TILE, lo_tile, p_last);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        int k0 = k_begin + it * AM_TILE;
+        if (warp * 16 < nq && k0 <= warp_hi && k0 + AM_TILE > warp_lo)
+            warp_tile<DMAX, 8>(qf, o, m, l, Ks + cur * AM_TILE * ld, Vs + cur * AM_TILE * ld, ld, d, k0, los, his,
+                               a.scale_log2);
+        __syncthreads();
+    }
+    cp_async_wait<0>();
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+    }
+    float inv0 = l[0] > 0.f ? 1.0f / l[0] : 0.f, inv1 = l[1] > 0.f ? 1.0f / l[1] : 0.f;
+    bf16* oa = a.out + ((size_t)(t0 + q0 + r0) * a.nh + h) * d;
+    bf16* ob = a.out + ((size_t)(t0 + q0 + r1) * a.nh + h) * d;
+#pragma unroll
+    for (int dn = 0; dn < DMAX / 8; ++dn) {
+        if (dn * 8 < d) {
+            int col = dn * 8 + 2 * quad;
+            if (v0) *reinterpret_cast<uint32_t*>(oa + col) = pack_bf16(o[dn][0] * inv0, o[dn][1] * inv0);
+            if (v1) *reinterpret_cast<uint32_t*>(ob + col) = pack_bf16(o[dn][2] * inv1, o[dn][3] * inv1);
+        }
+    }
+}
+
+static size_t stage_bytes(int d) { return (size_t)2 * 2 * AM_TILE * (d + AM_PAD) * sizeof(bf16); }
+
+static int check_common(const char* who, int nh, int nkv, int d, int q_stride) {
+    if (d < 16 || d > 256 || d % 16) return ce_fail(CE_ERR_SIZE, "%s: head_dim %d must be a multiple of 16 in 16..256", who, d);
+    if (nkv <= 0 || nh % nkv) return ce_fail(CE_ERR_SIZE, "%s: %d heads are not a multiple of %d kv heads", who, nh, nkv);
+    if (q_stride % 2) return ce_fail(CE_ERR_SIZE, "%s: the row stride of q must be even", who);
+    return CE_OK;
+}
+
+template <typename F> static int set_smem(F kernel, size_t bytes, const char* who) {
+    if (bytes > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+        if (e != cudaSuccess) return ce_fail(CE_ERR_CUDA, "%s: %s", who, cudaGetErrorString(e));
+    }
+    return CE_OK;
+}
+
+// Scratch floats the decode kernel needs for n_seqs sequences.
+extern "C" long long ce_attention_decode_scratch(int n_seqs, int nh, int d, int max_splits) {
+    return (long long)n_seqs * nh * max_splits * (d + 2);
+}
+
+// The first n_seqs sequences of the step bring one token each (tokens 0 .. n_seqs-1).
+// max_splits >= ceil(longest context / 256); it fixes the grid, not the result.
+extern "C" int ce_attention_decode_bf16(const void* q, const void* k_pool, const void* v_pool, void* out, float* scratch,
+                                        const int* positions, const int* seq_slot, const int* q_start,
+                                        const int* ctx_len, const int* block_table, int* status, int n_seqs, int nh,
+                                        int nkv, int d, int q_stride, int page_size, int max_pages, int num_pages,
+                                        int window, float scale, int max_splits, cudaStream_t stream) {
+    if (n_seqs == 0) return CE_OK;
+    if (!q || !k_pool || !v_pool || !out || !scratch || !positions || !seq_slot || !q_start || !ctx_len || !block_table || !status)
+        return ce_fail(CE_ERR_ARG, "ce_attention_decode_bf16: null pointer");
+    int rc = check_common("ce_attention_decode_bf16", nh, nkv, d, q_stride);
+    if (rc) return rc;
+    if (max_splits <= 0 || (long long)n_seqs * max_splits > 2147483647LL)
+        return ce_fail(CE_ERR_SIZE, "ce_attention_decode_bf16: %d sequences x %d splits", n_seqs, max_splits);
+    MmaAttnArgs a{};
+    a.q = (const bf16*)q; a.k_pool = (const bf16*)k_pool; a.v_pool = (const bf16*)v_pool; a.out = (bf16*)out;
+    a.part_o = scratch; a.part_ml = scratch + (size_t)n_seqs * nh * max_splits * d;
+    a.positions = positions; a.seq_slot = seq_slot; a.q_start = q_start; a.ctx_len = ctx_len; a.block_table = block_table;
+    a.status = status; a.nh = nh; a.nkv = nkv; a.d = d; a.q_stride = q_stride; a.page_size = page_size;
+    a.max_pages = max_pages; a.num_pages = num_pages; a.window = window; a.max_splits = max_splits;
+    a.scale_log2 = scale * 1.4426950408889634f;
+    int G = nh / nkv;
+    dim3 grid(n_seqs * max_splits, nkv, (G + 15) / 16);
+    size_t smem = stage_bytes(d);
+    size_t comb = (size_t)(4 * 16 * d + 128) * sizeof(float);
+    if (comb > smem) smem = comb;
+    if (d <= 64) {
+        if ((rc = set_smem(attention_decode_kernel<64>, smem, "ce_attention_decode_bf16"))) return rc;
+        attention_decode_kernel<64><<<grid, AM_THREADS, smem, stream>>>(a);
+    } else if (d <= 128) {
+        if ((rc = set_smem(attention_decode_kernel<128>, smem, "ce_attention_decode_bf16"))) return rc;
+        attention_decode_kernel<128><<<grid, AM_THREADS, smem, stream>>>(a);
+    } else {
+        if ((rc = set_smem(attention_decode_kernel<256>, smem, "ce_attention_decode_bf16"))) return rc;
+        attention_decode_kernel<256><<<grid, AM_THREADS, smem, stream>>>(a);
+    }
+    if ((rc = ce_check_launch("ce_attention_decode_bf16"))) return rc;
+    attention_merge_kernel<<<dim3(n_seqs, nh), 128, 0, stream>>>(a);
+    return ce_check_launch("ce_attention_decode_bf16 (merge)");
+}
+
+// tiles: [n_tiles, 2] = (sequence, first new token of the tile); tiles cover the sequences that
+// bring more than one token, 64 tokens at a time.
+extern "C" int ce_attention_prefill_bf16(const void* q, const void* k_pool, const void* v_pool, void* out,
+                                         const int* positions, const int* seq_slot, const int* q_start,
+                                         const int* ctx_len, const int* block_table, const int* tiles, int* status,
+                                         int n_tiles, int nh, int nkv, int d, int q_stride, int page_size,
+                                         int max_pages, int num_pages, int window, float scale, cudaStream_t stream) {
+    if (n_tiles == 0) return CE_OK;
+    if (!q || !k_pool || !v_pool || !out || !positions || !seq_slot || !q_start || !ctx_len || !block_table || !tiles || !status)
+        return ce_fail(CE_ERR_ARG, "ce_attention_prefill_bf16: null pointer");
+    int rc = check_common("ce_attention_prefill_bf16", nh, nkv, d, q_stride);
+    if (rc) return rc;
+    if (nh > 65535) return ce_fail(CE_ERR_SIZE, "ce_attention_prefill_bf16: %d heads", nh);
+    MmaAttnArgs a{};
+    a.q = (const bf16*)q; a.k_pool = (const bf16*)k_pool; a.v_pool = (const bf16*)v_pool; a.out = (bf16*)out;
+    a.positions = positions; a.seq_slot = seq_slot; a.q_start = q_start; a.ctx_len = ctx_len; a.block_table = block_table;
+    a.tiles = tiles; a.status = status; a.nh = nh; a.nkv = nkv; a.d = d; a.q_stride = q_stride; a.page_size = page_size;
+    a.max_pages = max_pages; a.num_pages = num_pages; a.window = window;
+    a.scale_log2 = scale * 1.4426950408889634f;
+    dim3 grid(n_tiles, nh);
+    size_t smem = stage_bytes(d);
+    if (d <= 64) {
+        if ((rc = set_smem(attention_prefill_kernel<64>, smem, "ce_attention_prefill_bf16"))) return rc;
+        attention_prefill_kernel<64><<<grid, AM_THREADS, smem, stream>>>(a);
+    } else if (d <= 128) {
+        if ((rc = set_smem(attention_prefill_kernel<128>, smem, "ce_attention_prefill_bf16"))) return rc;
+        attention_prefill_kernel<128><<<grid, AM_THREADS, smem, stream>>>(a);
+    } else {
+        if ((rc = set_smem(attention_prefill_kernel<256>, smem, "ce_attention_prefill_bf16"))) return rc;
+        attention_prefill_kernel<256><<<grid, AM_THREADS, smem, stream>>>(a);
+    }
+    return ce_check_launch("ce_attention_prefill_bf16");
+}

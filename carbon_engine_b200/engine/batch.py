@@ -31,7 +31,7 @@ class StepBuffers:
         T, B = self.max_tokens, self.max_seqs
         upd = T + 2 * B + 8                      # the most table entries one step can add per group
         sizes = [("tokens", T), ("positions", T), ("seq_of_token", T), ("seq_slot", B), ("q_start", B + 1),
-                 ("ctx_len", B), ("rows", T)]
+                 ("ctx_len", B), ("rows", T), ("tiles", 2 * (B + T // 64 + 1))]
         for g in range(num_groups):
             sizes += [(f"upd_idx{g}", upd), (f"upd_val{g}", upd)]
         self.offsets = {}
@@ -88,10 +88,22 @@ class StepContext:
         self.h_slots: List[int] = []
         self.h_q_start: List[int] = []       # B + 1 entries
         self.h_ctx_before: List[int] = []    # tokens of each sequence already in the cache
+        self.tiles = bufs.dev_section("tiles")
+        self.n_tiles = 0                     # 64-token tiles of the sequences that bring more than one token
+        self.decode_splits = 1               # grid size of the split-KV decode kernel: >= ceil(longest decode context / 256)
+        self._scratch = {}
         self.n_decode = 0                    # the first n_decode sequences bring exactly one token
         self.max_position = 0
         self.max_ctx = 0
         self.fast_attention = True
+
+    def scratch(self, name: str, numel: int) -> torch.Tensor:
+        """float32 scratch memory shared by the layers of this step."""
+        t = self._scratch.get(name)
+        if t is None or t.numel() < numel:
+            t = torch.empty(max(int(numel), 1), dtype=torch.float32, device=self.device)
+            self._scratch[name] = t
+        return t
 
     def buffer(self, shape, dtype: Optional[torch.dtype] = None) -> torch.Tensor:
         return torch.empty(shape, dtype=dtype or self.dtype, device=self.device)

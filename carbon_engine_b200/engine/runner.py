@@ -119,6 +119,19 @@ class ModelRunner:
             off += n
         h_qs[len(entries)] = off
         ctx.h_q_start.append(off)
+        h_tiles = b.host_section("tiles")
+        nt = 0
+        dec_ctx = 1
+        for bi, i in enumerate(order):
+            n = len(entries[i].tokens)
+            if bi < ctx.n_decode:
+                dec_ctx = max(dec_ctx, int(h_ctx[bi]))
+                continue
+            for q0 in range(0, n, 64):
+                h_tiles[2 * nt], h_tiles[2 * nt + 1] = bi, q0
+                nt += 1
+        ctx.n_tiles = nt
+        ctx.decode_splits = (dec_ctx + 255) // 256
         ctx.h_tokens = h_tok[:T].tolist()
 
         rows: List[int] = []

@@ -64,9 +64,10 @@ def write_safetensors_plain(path: str, tensors: Dict[str, torch.Tensor]) -> None
         fh.write(struct.pack("<Q", len(hb)) + hb + b"".join(blobs))
 
 
-def make_model_dir(tmp_dir: str, name: str, sharpen: float = 3.0) -> str:
+def make_model_dir(tmp_dir: str, name: str, sharpen: float = 2.0) -> str:
     """Write tiny model ``name`` with the engine's random-weights mode, then scale the q/k norm weights
-    so that attention is peaked: a key that is missed or misplaced then moves the logits visibly."""
+    (scores grow by ``sharpen``) so that attention is peaked: a key that is missed or misplaced then moves
+    the logits visibly.  Scores much larger than that lose absolute precision in bfloat16 keys and queries."""
     import carbon_engine_b200.models  # noqa: F401
     from carbon_engine_b200.config.qwen3 import Qwen3Config
     from carbon_engine_b200.weights.loader import write_random_model

@@ -347,3 +347,123 @@ def test_kernels_refuse_sizes_they_cannot_take(ops):
                               status(), 1, 1, 2048, 4, 0, 1.0)
     with pytest.raises(KernelError, match="CUDA tensor"):
         ops.rmsnorm(torch.zeros(1, 8), torch.ones(8), torch.zeros(1, 8), 1e-6)
+
+
+# ---- bfloat16 tensor-core attention (decode split-KV + flash prefill) -----------------------------
+class FakeCtx:
+    """The fields of a step context the attention kernels read."""
+
+    def __init__(self, seqs):
+        mk = lambda a: torch.tensor(a, dtype=torch.int32, device=dev())
+        order = sorted(range(len(seqs)), key=lambda i: 0 if seqs[i][1] == 1 else 1)
+        self.order = order
+        pos, qs, ctx, tiles = [], [0], [], []
+        self.n_decode = sum(1 for c, n in seqs if n == 1)
+        dec = 1
+        for bi, i in enumerate(order):
+            c, n = seqs[i]
+            pos += list(range(c, c + n))
+            qs.append(qs[-1] + n)
+            ctx.append(c + n)
+            if n == 1:
+                dec = max(dec, c + n)
+            else:
+                tiles += [[bi, q0] for q0 in range(0, n, 64)]
+        self.T = qs[-1]
+        self.positions, self.q_start, self.ctx_len = mk(pos), mk(qs), mk(ctx)
+        self.seq_slot = mk(order)                  # sequence bi of the step uses block-table row order[bi]
+        self.tiles = mk(tiles if tiles else [[0, 0]])
+        self.n_tiles = len(tiles)
+        self.decode_splits = (dec + 255) // 256
+        self.status = status()
+        self.device = dev()
+        self._s = {}
+
+    def scratch(self, name, numel):
+        if name not in self._s or self._s[name].numel() < numel:
+            self._s[name] = torch.full((max(numel, 1),), float("nan"), device=dev())
+        return self._s[name]
+
+
+class FakeCache:
+    def __init__(self, kp, vp, ps):
+        self.k_pool, self.v_pool, self.page_size = kp, vp, ps
+
+
+def run_mma_attention(seqs, nh, nkv, d, ps, window, scale, seed=0, far=None, extra_splits=0):
+    """Returns (got [T, nh, d] in the caller's sequence order, want)."""
+    from carbon_engine_b200 import ops_tensor
+    torch.manual_seed(seed)
+    lens = [c + n for c, n in seqs]
+    table, kp, vp = paged_layout(lens, ps, nkv, d, torch.bfloat16, shuffle_seed=seed + 1)
+    ctx = FakeCtx(seqs)
+    ctx.decode_splits += extra_splits
+    q_step = torch.zeros(ctx.T, nh * d + 2 * nkv * d, dtype=torch.bfloat16, device=dev())    # q inside a wider qkv row
+    want = {}
+    t = 0
+    for bi, i in enumerate(ctx.order):
+        c, n = seqs[i]
+        L = c + n
+        q_all = (torch.randn(L, nh, d) * 1.5).to(torch.bfloat16)
+        k_all = (torch.randn(L, nkv, d) * 1.5).to(torch.bfloat16)
+        v_all = torch.randn(L, nkv, d).to(torch.bfloat16)
+        if far is not None and i == far[0]:
+            k_all[far[1], 0] = (q_all[L - 1, nh - 1].float() * 3.0).to(torch.bfloat16)     # last head's last query loves this key
+        fill_pools(kp, vp, table.cpu().numpy(), i, k_all.to(dev()), v_all.to(dev()), ps)
+        q_step[t:t + n, :nh * d] = q_all[c:].reshape(n, nh * d).to(dev())
+        want[i] = plain.causal_attention(q_all.double(), k_all.double(), v_all.double(), scale, window)[c:]
+        t += n
+    out = torch.full((ctx.T, nh * d), float("nan"), dtype=torch.bfloat16, device=dev())
+    ok = ops_tensor.attention_bf16(ctx, q_step, out, FakeCache(kp, vp, ps), table, nh, nkv, d, window, scale)
+    assert ok and ctx.status.item() == 0
+    got, t = {}, 0
+    for bi, i in enumerate(ctx.order):
+        n = seqs[i][1]
+        got[i] = out[t:t + n].view(n, nh, d)
+        t += n
+    return got, want
+
+
+@pytest.mark.parametrize("nh,nkv,d,ps,window", [(32, 8, 128, 64, 0), (6, 3, 48, 8, 0), (8, 2, 32, 16, 0), (4, 4, 16, 4, 0),
+                                                 (3, 1, 256, 32, 0), (40, 2, 64, 16, 0), (6, 2, 64, 8, 37), (4, 1, 80, 16, 300)])
+def test_mma_attention_decode_and_prefill_mixed(nh, nkv, d, ps, window):
+    # decode rows at contexts around the split (256) and tile (64) edges, portions with and without a cached prefix
+    seqs = [(0, 19), (255, 1), (256, 1), (700, 1), (61, 7), (0, 2), (126, 130), (0, 1), (63, 1), (300, 65)]
+    got, want = run_mma_attention(seqs, nh, nkv, d, ps, window, 1 / math.sqrt(d))
+    for i in range(len(seqs)):
+        assert rel_err(got[i], want[i]) < 2e-2, (i, seqs[i])
+
+
+def test_mma_decode_result_does_not_depend_on_the_grid():
+    """More splits in the grid than the longest context needs (as under a captured graph): same bits."""
+    from carbon_engine_b200 import ops_tensor
+    seqs = [(511, 1), (100, 1)]
+    a, _ = run_mma_attention(seqs, 8, 2, 64, 16, 0, 0.125, seed=7)
+    b, _ = run_mma_attention(seqs, 8, 2, 64, 16, 0, 0.125, seed=7, extra_splits=5)
+    assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1])
+    alone, _ = run_mma_attention(seqs[1:], 8, 2, 64, 16, 0, 0.125, seed=7)
+    # (not the same random draws as above, so only the shape of the call is checked here)
+    assert alone[0].shape == (1, 8, 64)
+
+
+@pytest.mark.parametrize("far,window,visible", [(0, 0, True), (63, 0, True), (64, 0, True), (255, 0, True), (256, 0, True),
+                                                 (899 - 99, 100, True), (899 - 100, 100, False), (511, 0, True)])
+@pytest.mark.parametrize("n_new", [1, 5])
+def test_mma_attention_finds_one_far_key(far, window, visible, n_new):
+    """One key among 900 stands out for the last query of the last head: at the first position, at tile
+    and split edges, at the window's edge and one before it.  Both the decode and the flash kernel."""
+    nh, nkv, d, ps = 4, 1, 64, 16
+    L = 900
+    seqs = [(L - n_new, n_new)]
+    got, want = run_mma_attention(seqs, nh, nkv, d, ps, window, 1.0, seed=far, far=(0, far))
+    assert rel_err(got[0], want[0]) < 2e-2
+    # the plain result itself shows that the key decides the output when (and only when) it is visible
+    _, base = run_mma_attention(seqs, nh, nkv, d, ps, window, 1.0, seed=far, far=None)
+    moved = float((want[0][-1, -1] - base[0][-1, -1]).abs().max()) > 0.5
+    assert moved == visible
+
+
+def test_mma_attention_refuses_odd_head_sizes():
+    from carbon_engine_b200 import ops_tensor
+    assert not ops_tensor.attention_supported(40, 128) and not ops_tensor.attention_supported(272, 1024)
+    assert ops_tensor.attention_supported(48, 96)

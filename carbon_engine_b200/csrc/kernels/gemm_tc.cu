@@ -1,0 +1,415 @@
+// y = x * W^T in bfloat16 on the 5th-generation tensor cores (tcgen05.mma, accumulators in tensor
+// memory, operands brought into shared memory by TMA), with the epilogue fused: store in bfloat16,
+// store float32 (logits), add into the float32 residual stream, or SwiGLU.
+//
+// The product is computed "swapped": a tile of 128 weight rows (output features) is the M operand of
+// the MMA, the tokens are its N operand (16 to 256 of them), so that decode steps with a handful of
+// tokens still fill the tensor core's M dimension and stream each weight exactly once.  Both operands
+// are K-major as stored (W is [out, in], x is [tokens, in]), in 128-byte-swizzled tiles of 64 k.
+//
+// One CTA computes one 128 x BN output tile (two accumulators for SwiGLU: gate and up rows of the
+// same features), optionally over a slice of K (split-K, used when there are fewer tiles than SMs).
+// Warp 0 issues the TMA loads, warp 1 owns tensor memory and issues the MMAs, warps 2-5 read the
+// accumulators back (tcgen05.ld) and run the epilogue.  With split-K every CTA writes its partial
+// sums to scratch memory; the CTA that arrives last for a tile adds the partials in split order
+// (a fixed order, so the result does not depend on which CTA came last) and runs the epilogue.
+// No load uses cluster multicast.  Every wait on an mbarrier is bounded: on a timeout the kernel sets
+// status 5, waits (bounded) for its own copies in flight, frees its tensor memory and returns.
+//
+// The reference calls a library (cuBLAS through candle) for these products and runs the residual
+// add, SiLU and multiply as separate kernels (src/model/layers.rs:441, 625-648).
+#include "common.cuh"
+#include <cuda.h>
+#include <mutex>
+#include <unordered_map>
+
+namespace {
+
+constexpr int BM = 128;          // weight rows per tile = UMMA M
+constexpr int BK = 64;           // k per stage: 64 bf16 = 128 bytes = one swizzle row
+constexpr int UMMA_K = 16;
+constexpr int THREADS = 192;
+constexpr uint32_t SPIN_LIMIT = 1u << 20;     // with the back-off below: about a second at most
+
+enum { TC_STORE = 0, TC_STORE_F32 = 1, TC_ACCUM_F32 = 2, TC_SWIGLU = 3 };
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false if the phase did not complete within the limit.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (i > 1024) __nanosleep(256);
+    }
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+    // K-major, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);          // start address
+    d |= (uint64_t)1 << 16;                                // leading byte offset (unused for this layout)
+    d |= (uint64_t)(1024 >> 4) << 32;                      // stride byte offset
+    d |= (uint64_t)1 << 46;                                // descriptor version of sm_100
+    d |= (uint64_t)2 << 61;                                // SWIZZLE_128B
+    return d;
+}
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+                 ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
+    uint32_t r[16];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+struct TcArgs {
+    void* out;               // [M, ldo] bf16 or float32
+    float* scratch;          // split-K partials: [splits][tiles][nacc][BN][128]
+    int* counters;           // one per output tile, zero between launches
+    int* status;
+    int M, N, K, ldo, mode, splits, kblocks_per_split, kblocks;
+};
+
+__device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + __expf(-g)) * u; }
+
+__device__ __forceinline__ void epilogue_store(const TcArgs& a, int m, int n, float v, float up) {
+    size_t o = (size_t)m * a.ldo + n;
+    if (a.mode == TC_STORE) ((__nv_bfloat16*)a.out)[o] = __float2bfloat16_rn(v);
+    else if (a.mode == TC_STORE_F32) ((float*)a.out)[o] = v;
+    else if (a.mode == TC_ACCUM_F32) ((float*)a.out)[o] += v;
+    else ((__nv_bfloat16*)a.out)[o] = __float2bfloat16_rn(silu_mul(v, up));
+}
+
+template <int BN, int NACC>
+__global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,
+                                                         const __grid_constant__ CUtensorMap map_x, TcArgs a, int stages) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    __shared__ __align__(8) uint64_t full_bar[8], empty_bar[8], acc_bar;
+    __shared__ uint32_t tmem_slot;
+    __shared__ int s_ticket, s_abort;
+
+    constexpr uint32_t W_BYTES = BM * BK * 2, X_BYTES = BN * BK * 2;
+    constexpr uint32_t STAGE_BYTES = NACC * W_BYTES + X_BYTES;
+    constexpr uint32_t TMEM_COLS = (NACC * BN) < 32 ? 32 : (NACC * BN);
+    // the dynamic buffer is aligned to 1024 bytes by hand: the swizzle pattern is keyed on address bits
+    uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    unsigned char* tiles = smem_raw + (base - smem_u32(smem_raw));
+
+    int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    int n0 = blockIdx.x * BM, m0 = blockIdx.y * BN, split = blockIdx.z;
+    int kb0 = split * a.kblocks_per_split;
+    int kb1 = min(kb0 + a.kblocks_per_split, a.kblocks);
+    int nkb = kb1 - kb0;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < stages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+        mbar_init(&acc_bar, 1);
+        s_abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(TMEM_COLS));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    uint32_t tmem = tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // ---- producer: TMA loads of the weight tile(s) and the token tile, stage after stage
+            int issued = 0;
+            bool ok = true;
+            for (int i = 0; i < nkb && ok; ++i) {
+                int s = i % stages;
+                if (i >= stages) ok = mbar_wait(&empty_bar[s], ((i / stages) - 1) & 1);
+                if (!ok) break;
+                unsigned char* st = tiles + (size_t)s * STAGE_BYTES;
+                mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+                int k = (kb0 + i) * BK;
+                tma_load_2d(st, &map_w, &full_bar[s], k, n0);
+                if (NACC == 2) tma_load_2d(st + W_BYTES, &map_w, &full_bar[s], k, a.N + n0);
+                tma_load_2d(st + NACC * W_BYTES, &map_x, &full_bar[s], k, m0);
+                issued = i + 1;
+            }
+            if (!ok) {
+                atomicExch(a.status, 5);
+                atomicExch(&s_abort, 1);
+                // our own copies may still be in flight: wait for them (bounded) before the block ends
+                for (int i = max(0, issued - stages); i < issued; ++i) mbar_wait(&full_bar[i % stages], (i / stages) & 1);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // ---- MMA issuer
+            uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+            bool ok = true;
+            for (int i = 0; i < nkb; ++i) {
+                int s = i % stages;
+                ok = mbar_wait(&full_bar[s], (i / stages) & 1);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                uint32_t st = base + s * STAGE_BYTES;
+#pragma unroll
+                for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+                    uint64_t bdesc = umma_desc(st + NACC * W_BYTES + kk * UMMA_K * 2);
+                    uint32_t acc = (i > 0 || kk > 0) ? 1u : 0u;
+                    umma_bf16(tmem, umma_desc(st + kk * UMMA_K * 2), bdesc, idesc, acc);
+                    if (NACC == 2) umma_bf16(tmem + BN, umma_desc(st + W_BYTES + kk * UMMA_K * 2), bdesc, idesc, acc);
+                }
+                umma_commit(&empty_bar[s]);          // the stage is free once these MMAs have read it
+            }
+            if (ok) umma_commit(&acc_bar);           // the accumulators are complete
+            else { atomicExch(a.status, 5); atomicExch(&s_abort, 1); }
+        }
+    } else {
+        // ---- epilogue: 4 warps, each reads the 32 accumulator lanes of its quadrant
+        int quad = warp & 3;
+        int row = quad * 32 + lane;                  // feature within the tile
+        int n = n0 + row;
+        int m_valid = min(BN, a.M - m0);
+        bool ok = nkb > 0 ? mbar_wait(&acc_bar, 0) : true;
+        if (!ok) { atomicExch(a.status, 5); atomicExch(&s_abort, 1); }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        uint32_t taddr = tmem + ((uint32_t)(quad * 32) << 16);
+        if (a.splits == 1) {
+            if (ok) {
+#pragma unroll 1
+                for (int c = 0; c < BN; c += 16) {
+                    if (c >= m_valid) break;
+                    float g[16], u[16];
+                    tmem_ld16(taddr + c, g);
+                    if (NACC == 2) tmem_ld16(taddr + BN + c, u);
+                    if (n < a.N) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            if (c + j < m_valid) epilogue_store(a, m0 + c + j, n, g[j], NACC == 2 ? u[j] : 0.f);
+                    }
+                }
+            }
+        } else {
+            // partial sums to scratch: [split][tile][acc][m][128]
+            int tile = blockIdx.y * gridDim.x + blockIdx.x;
+            int n_tiles = gridDim.x * gridDim.y;
+            float* mine = a.scratch + (((size_t)split * n_tiles + tile) * NACC) * BN * BM;
+            if (ok) {
+#pragma unroll 1
+                for (int c = 0; c < BN; c += 16) {
+                    if (c >= m_valid) break;
+                    float g[16], u[16];
+                    if (nkb > 0) {
+                        tmem_ld16(taddr + c, g);
+                        if (NACC == 2) tmem_ld16(taddr + BN + c, u);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) g[j] = u[j] = 0.f;
+                    }
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        if (c + j < m_valid) {
+                            mine[(size_t)(c + j) * BM + row] = g[j];
+                            if (NACC == 2) mine[(size_t)(BN + c + j) * BM + row] = u[j];
+                        }
+                    }
+                }
+            }
+            __threadfence();
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (threadIdx.x == 64) s_ticket = atomicAdd(&a.counters[tile], 1);
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (s_ticket == a.splits - 1) {
+                __threadfence();
+                if (n < a.N && s_abort == 0) {
+                    for (int m = 0; m < m_valid; ++m) {
+                        float g = 0.f, u = 0.f;
+                        for (int s = 0; s < a.splits; ++s) {
+                            const float* p = a.scratch + (((size_t)s * n_tiles + tile) * NACC) * BN * BM;
+                            g += __ldcg(p + (size_t)m * BM + row);
+                            if (NACC == 2) u += __ldcg(p + (size_t)(BN + m) * BM + row);
+                        }
+                        epilogue_store(a, m0 + m, n, g, u);
+                    }
+                }
+                if (threadIdx.x == 64) a.counters[tile] = 0;      // ready for the next launch
+            }
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    }
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS));
+    }
+}
+
+// ---- host side ------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_fn() {
+    static EncodeTiled fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiled)p;
+    });
+    return fn;
+}
+
+struct MapKey {
+    const void* ptr; long long rows, cols, ld; int box_rows;
+    bool operator==(const MapKey& o) const { return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows; }
+};
+struct MapHash {
+    size_t operator()(const MapKey& k) const {
+        size_t h = (size_t)k.ptr;
+        for (long long v : {k.rows, k.cols, k.ld, (long long)k.box_rows}) h = h * 1000003u ^ (size_t)v;
+        return h;
+    }
+};
+
+// A tensor map of a row-major bf16 matrix [rows, cols] with row stride ld, boxes of box_rows x 64.
+int get_map(const void* ptr, long long rows, long long cols, long long ld, int box_rows, CUtensorMap* out) {
+    static std::unordered_map<MapKey, CUtensorMap, MapHash> cache;
+    static std::mutex mu;
+    MapKey key{ptr, rows, cols, ld, box_rows};
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) { *out = it->second; return CE_OK; }
+    EncodeTiled enc = encode_fn();
+    if (!enc) return ce_fail(CE_ERR_CUDA, "ce_gemm_tc: cuTensorMapEncodeTiled is not available in this driver");
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    CUtensorMap m;
+    CUresult r = enc(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return ce_fail(CE_ERR_CUDA, "ce_gemm_tc: cuTensorMapEncodeTiled failed (%d)", (int)r);
+    if (cache.size() > 4096) cache.clear();
+    cache.emplace(key, m);
+    *out = m;
+    return CE_OK;
+}
+
+template <int BN, int NACC>
+int launch(const CUtensorMap& mw, const CUtensorMap& mx, const TcArgs& a, dim3 grid, cudaStream_t stream) {
+    constexpr size_t stage = NACC * BM * BK * 2 + BN * BK * 2;
+    // decode-sized tiles: two CTAs per SM; large tiles: one
+    size_t budget = BN <= 64 ? 100 * 1024 : 200 * 1024;
+    int stages = (int)(budget / stage);
+    if (stages > 8) stages = 8;
+    if (stages < 2) stages = 2;
+    size_t smem = stages * stage + 1024;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, NACC>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 2048);
+        if (e != cudaSuccess) return ce_fail(CE_ERR_CUDA, "ce_gemm_tc: %s", cudaGetErrorString(e));
+        attr_set = true;
+    }
+    gemm_tc_kernel<BN, NACC><<<grid, THREADS, smem, stream>>>(mw, mx, a, stages);
+    return ce_check_launch("ce_gemm_tc");
+}
+
+}  // namespace
+
+// How many splits of K a product of these sizes uses (it depends on N and K only while the tokens
+// fit one tile, so a token's sums are taken in the same order whatever else is in the batch).
+extern "C" int ce_gemm_tc_splits(int M, int N, int K) {
+    int kblocks = (K + BK - 1) / BK;
+    if (M > 256) return 1;
+    int tiles = (N + BM - 1) / BM;
+    int s = 148 / tiles;
+    if (s > kblocks / 4) s = kblocks / 4;
+    if (s > 8) s = 8;
+    return s < 1 ? 1 : s;
+}
+
+extern "C" int ce_gemm_tc_tile_tokens(int M) {
+    return M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
+}
+
+// Scratch floats a product needs (0 without split-K).
+extern "C" long long ce_gemm_tc_scratch(int M, int N, int K, int mode) {
+    int s = ce_gemm_tc_splits(M, N, K);
+    if (s == 1) return 0;
+    int bn = ce_gemm_tc_tile_tokens(M);
+    long long tiles = (long long)((N + BM - 1) / BM) * ((M + bn - 1) / bn);
+    return (long long)s * tiles * (mode == TC_SWIGLU ? 2 : 1) * bn * BM;
+}
+
+extern "C" int ce_gemm_tc_supported(int M, int N, int K, int lda) {
+    return M > 0 && N > 0 && K > 0 && K % 8 == 0 && lda % 8 == 0 && (long long)((N + BM - 1) / BM) <= 65535 * 32;
+}
+
+// A [M, K] bf16 (row stride lda), W [N or 2N, K] bf16, C [M, ldc].  N counts output columns
+// (for SwiGLU the intermediate width).  counters: at least ceil(N/128) * ceil(M/BN) zeroed ints.
+extern "C" int ce_gemm_tc(const void* A, const void* W, void* C, int M, int N, int K, int lda, int ldc, int mode,
+                          float* scratch, long long scratch_floats, int* counters, int n_counters, int* status,
+                          cudaStream_t stream) {
+    if (M == 0 || N == 0) return CE_OK;
+    if (!A || !W || !C || !status) return ce_fail(CE_ERR_ARG, "ce_gemm_tc: null pointer");
+    if (!ce_gemm_tc_supported(M, N, K, lda))
+        return ce_fail(CE_ERR_SIZE, "ce_gemm_tc: K=%d and the row stride %d must be multiples of 8", K, lda);
+    if (((uintptr_t)A | (uintptr_t)W) & 15) return ce_fail(CE_ERR_SIZE, "ce_gemm_tc: operands must be 16-byte aligned");
+    if (mode < 0 || mode > 3) return ce_fail(CE_ERR_ARG, "ce_gemm_tc: unknown epilogue %d", mode);
+    int nacc = mode == TC_SWIGLU ? 2 : 1;
+    int bn = ce_gemm_tc_tile_tokens(M);
+    int splits = ce_gemm_tc_splits(M, N, K);
+    int kblocks = (K + BK - 1) / BK;
+    dim3 grid((N + BM - 1) / BM, (M + bn - 1) / bn, splits);
+    if (grid.y > 65535) return ce_fail(CE_ERR_SIZE, "ce_gemm_tc: M=%d is too large", M);
+    if (splits > 1) {
+        if (!scratch || !counters || scratch_floats < ce_gemm_tc_scratch(M, N, K, mode) || n_counters < (int)(grid.x * grid.y))
+            return ce_fail(CE_ERR_ARG, "ce_gemm_tc: split-K needs %lld scratch floats and %d counters",
+                           ce_gemm_tc_scratch(M, N, K, mode), grid.x * grid.y);
+    }
+    CUtensorMap mw, mx;
+    int rc = get_map(W, (long long)N * nacc, K, K, BM, &mw);
+    if (rc) return rc;
+    if ((rc = get_map(A, M, K, lda, bn, &mx))) return rc;
+    TcArgs a{C, scratch, counters, status, M, N, K, ldc, mode, splits, (kblocks + splits - 1) / splits, kblocks};
+#define TC_CASE(BN_)                                                                  \
+    case BN_:                                                                         \
+        return nacc == 2 ? launch<BN_, 2>(mw, mx, a, grid, stream) : launch<BN_, 1>(mw, mx, a, grid, stream);
+    switch (bn) {
+        TC_CASE(16)
+        TC_CASE(32)
+        TC_CASE(64)
+        TC_CASE(128)
+        TC_CASE(256)
+    }
+#undef TC_CASE
+    return ce_fail(CE_ERR_SIZE, "ce_gemm_tc: no tile for M=%d", M);
+}

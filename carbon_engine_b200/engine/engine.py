@@ -113,7 +113,7 @@ class Engine:
         self.scheduler = Scheduler(self.storage.manager, self.max_running, self.max_step_tokens, self.max_seq_len,
                                    self.config.vocab_size, self.config.eos_token_ids)
         self.sampler = Sampler(self.device)
-        self.cuda_graphs = bool(cuda_graphs)
+        self.cuda_graphs = bool(cuda_graphs) and self.runner.enable_graphs()
         self._live: Dict[int, _Live] = {}
         self._done: Dict[int, RequestOutput] = {}
         self._next_id = 0

@@ -37,6 +37,8 @@ class ModelRunner:
         self.bufs = StepBuffers(self.max_step_tokens, storage.max_requests, len(storage.groups), self.device)
         self.fast_attention = True
         self.graphs_enabled = False
+        self._graphs = {}
+        self._graph_pool = None
         self.h2d_bytes_last = 0
         self.kernel_launches = 0
 
@@ -157,12 +159,50 @@ class ModelRunner:
 
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         """Run one step and return float32 logits [wanted, vocab] on the device, in the order of the
-        entries and of their ``want`` lists."""
+        entries and of their ``want`` lists.  With CUDA graphs on, the logits of a pure decode step
+        live in a buffer that the next such step overwrites."""
         ctx, rows, commits = self.prepare(entries)
-        x = self.model.forward(ctx, self.storage)
-        logits = self.model.logits(ctx, x, rows)
+        if self.graphs_enabled and ctx.n_decode == ctx.B and all(len(e.want) == 1 for e in entries):
+            logits = self._replay_decode(ctx, rows)
+        else:
+            x = self.model.forward(ctx, self.storage)
+            logits = self.model.logits(ctx, x, rows)
         for request_id, new_len in commits:
             self.storage.manager.commit(request_id, new_len)
+        return logits
+
+    # -- CUDA graphs for decode steps -----------------------------------------------------------
+    def enable_graphs(self) -> bool:
+        """Replay pure decode steps as CUDA graphs, one per (batch size, split count), captured at
+        first use (the reference does the same per batch size, src/model/graph.rs:50-120).  Only
+        models whose mixers read the step from device buffers alone can be captured."""
+        self.graphs_enabled = bool(getattr(self.model, "graph_safe", False))
+        return self.graphs_enabled
+
+    def _replay_decode(self, ctx: StepContext, rows: torch.Tensor) -> torch.Tensor:
+        bucket = 1
+        while bucket < ctx.decode_splits:
+            bucket *= 2
+        ctx.decode_splits = bucket          # a larger grid, the same result
+        key = (ctx.B, bucket)
+        entry = self._graphs.get(key)
+        if entry is None:
+            # once eagerly, so that lazy initialisation (library handles, kernel attributes) is not captured
+            x = self.model.forward(ctx, self.storage)
+            self.model.logits(ctx, x, rows)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            before = ops.launch_count()
+            with torch.cuda.graph(graph, pool=self._graph_pool):
+                x = self.model.forward(ctx, self.storage)
+                logits = self.model.logits(ctx, x, rows)
+            if self._graph_pool is None:
+                self._graph_pool = graph.pool()
+            entry = (graph, logits, ops.launch_count() - before)
+            self._graphs[key] = entry
+        graph, logits, launches = entry
+        graph.replay()
+        ops.add_launches(launches)
         return logits
 
     def check_status(self) -> None:

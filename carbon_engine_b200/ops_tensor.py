@@ -19,11 +19,61 @@ kernel_lib.declare("ce_attention_decode_bf16", _i, [_p] * 11 + [_i] * 9 + [_f, _
 # n_tiles, nh, nkv, d, q_stride, page_size, max_pages, num_pages, window, scale, stream
 kernel_lib.declare("ce_attention_prefill_bf16", _i, [_p] * 11 + [_i] * 9 + [_f, _p])
 
+kernel_lib.declare("ce_gemm_tc_supported", _i, [_i, _i, _i, _i])
+kernel_lib.declare("ce_gemm_tc_scratch", _ll, [_i, _i, _i, _i])
+kernel_lib.declare("ce_gemm_tc_splits", _i, [_i, _i, _i])
+# A, W, C, M, N, K, lda, ldc, mode, scratch, scratch_floats, counters, n_counters, status, stream
+kernel_lib.declare("ce_gemm_tc", _i, [_p, _p, _p, _i, _i, _i, _i, _i, _i, _p, _ll, _p, _i, _p, _p])
+
 DECODE_SPLIT = 256
+GEMM_SCRATCH_FLOATS = 16 << 20        # 64 MB of split-K partial sums
+GEMM_COUNTERS = 1 << 16
+
+#: set to False to keep bfloat16 products off the tcgen05 kernel
+USE_TENSOR_GEMM = True
+
+_workspaces = {}
+
+
+class _Workspace:
+    def __init__(self, device):
+        self.scratch = torch.empty(GEMM_SCRATCH_FLOATS, dtype=torch.float32, device=device)
+        self.counters = torch.zeros(GEMM_COUNTERS, dtype=torch.int32, device=device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+
+
+def gemm_workspace(device) -> _Workspace:
+    ws = _workspaces.get(device)
+    if ws is None:
+        ws = _workspaces[device] = _Workspace(device)
+    return ws
+
+
+def gemm_status(device) -> int:
+    """0, or the code a tensor-core product left behind (5: a wait inside the kernel timed out)."""
+    ws = _workspaces.get(device)
+    return 0 if ws is None else int(ws.status.item())
 
 
 def gemm_bf16(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int) -> bool:
-    return False
+    """out (op)= a @ w.T on the tcgen05 kernel; False if the shape is refused."""
+    if not USE_TENSOR_GEMM or a.dtype != torch.bfloat16:
+        return False
+    M, K = a.shape
+    N = out.shape[1]
+    k = kernels()
+    if a.stride(1) != 1 or not w.is_contiguous() or out.stride(1) != 1:
+        return False
+    if not k.ce_gemm_tc_supported(M, N, K, a.stride(0)) or (a.data_ptr() | w.data_ptr()) & 15:
+        return False
+    need = k.ce_gemm_tc_scratch(M, N, K, mode)
+    ws = gemm_workspace(a.device)
+    if need > ws.scratch.numel():
+        return False
+    ops._ok(k.ce_gemm_tc(a.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), out.stride(0), mode,
+                         ws.scratch.data_ptr(), ws.scratch.numel(), ws.counters.data_ptr(), ws.counters.numel(),
+                         ws.status.data_ptr(), torch.cuda.current_stream().cuda_stream))
+    return True
 
 
 def attention_supported(d: int, q_stride: int) -> bool:

@@ -23,6 +23,8 @@ from .rope import PositionEncoding
 
 
 class PagedAttention(Mixer):
+    graph_safe = True       # reads positions, tables and lengths from device buffers only
+
     def __init__(self, hidden: int, heads: int, kv_heads: int, head_dim: int, prefix: str,
                  position: Optional[PositionEncoding] = None, qk_norm_eps: Optional[float] = None,
                  window: int = 0, scale: Optional[float] = None):

@@ -52,6 +52,12 @@ class DecoderModel(Part):
     def children(self) -> List[Part]:
         return [self.embedding, *self.blocks, self.head]
 
+    @property
+    def graph_safe(self) -> bool:
+        """True if a step of this model can be captured in a CUDA graph: every mixer reads the step
+        from device buffers only."""
+        return all(getattr(b.mixer, "graph_safe", False) for b in self.blocks)
+
     def cache_layout(self) -> List[tuple]:
         """(cache id, spec) for every cache of the schedule, taken from the mixer that writes it."""
         out = []

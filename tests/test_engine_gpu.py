@@ -186,3 +186,21 @@ def test_no_cpu_path():
     from carbon_engine_b200.engine.engine import require_gpu
     with pytest.raises(RuntimeError, match="CUDA device only"):
         require_gpu("cpu")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_cuda_graphs_give_the_same_tokens_as_eager(models, dtype):
+    """Decode steps replayed as CUDA graphs (src/model/graph.rs:50-120; tests/parallel.rs:826-868 in the
+    reference): same tokens, while batch size and context length change under the captured graphs."""
+    from carbon_engine_b200 import SamplingParams
+    d, cfg, w = models["B"]
+    rng = np.random.default_rng(8)
+    prompts = [random_tokens(rng, n, cfg["vocab_size"]) for n in (30, 3, 250, 77, 12)]
+    sps = [SamplingParams(max_tokens=m, ignore_eos=True) for m in (40, 25, 30, 9, 50)]
+    eager = make_engine(d, dtype, "B", max_seq_len=1024).generate(prompts, sps)
+    eng = make_engine(d, dtype, "B", max_seq_len=1024, cuda_graphs=True)
+    assert eng.cuda_graphs
+    graphed = eng.generate(prompts, sps)
+    for a, b in zip(eager, graphed):
+        assert a.token_ids == b.token_ids
+    assert len(eng.runner._graphs) >= 3            # several batch sizes were captured

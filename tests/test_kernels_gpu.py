@@ -467,3 +467,63 @@ def test_mma_attention_refuses_odd_head_sizes():
     from carbon_engine_b200 import ops_tensor
     assert not ops_tensor.attention_supported(40, 128) and not ops_tensor.attention_supported(272, 1024)
     assert ops_tensor.attention_supported(48, 96)
+
+
+# ---- bfloat16 products on tcgen05 ------------------------------------------------------------------
+def tc_product(a, w, mode, N, x0=None):
+    from carbon_engine_b200 import ops_tensor, ops as o
+    M = a.shape[0]
+    if mode == o.GEMM_STORE_F32:
+        out = torch.full((M, N), float("nan"), device=dev())
+    elif mode == o.GEMM_ACCUM_F32:
+        out = x0.clone()
+    else:
+        out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=dev())
+    assert ops_tensor.gemm_bf16(a, w, out, mode), "the tensor-core product refused the shape"
+    torch.cuda.synchronize()
+    assert ops_tensor.gemm_status(a.device) == 0
+    return out
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 128, 64), (8, 256, 4096), (16, 96, 80), (17, 301, 136), (64, 4096, 512), (100, 200, 1000),
+                                   (256, 384, 256), (300, 520, 192), (5, 1000, 2048), (2048, 512, 256)])
+def test_tcgen05_product_all_epilogues(ops, M, N, K):
+    torch.manual_seed(M * 7 + N)
+    a = torch.randn(M, K, device=dev()).to(torch.bfloat16)
+    w = (torch.randn(N, K, device=dev()) / math.sqrt(K)).to(torch.bfloat16)
+    ref = a.double().cpu() @ w.double().cpu().T
+    assert rel_err(tc_product(a, w, ops.GEMM_STORE, N), ref) < 1e-2
+    assert rel_err(tc_product(a, w, ops.GEMM_STORE_F32, N), ref) < 2e-5
+    x0 = torch.randn(M, N, device=dev())
+    assert rel_err(tc_product(a, w, ops.GEMM_ACCUM_F32, N, x0), x0.double().cpu() + ref) < 2e-5
+    w2 = (torch.randn(2 * N, K, device=dev()) / math.sqrt(K)).to(torch.bfloat16)
+    g = a.double().cpu() @ w2[:N].double().cpu().T
+    u = a.double().cpu() @ w2[N:].double().cpu().T
+    assert rel_err(tc_product(a, w2, ops.GEMM_SWIGLU, N), g * torch.sigmoid(g) * u) < 1e-2
+
+
+def test_tcgen05_product_is_repeatable_and_rows_stand_alone(ops):
+    """Split-K adds the partial sums in a fixed order: the same bits every time, and a token's row does
+    not depend on how many other tokens share the step (while they fit one tile of tokens)."""
+    from carbon_engine_b200.csrc.kernel_lib import kernels
+    a = torch.randn(16, 4096, device=dev()).to(torch.bfloat16)
+    w = (torch.randn(256, 4096, device=dev()) / 64).to(torch.bfloat16)
+    assert kernels().ce_gemm_tc_splits(16, 256, 4096) > 1
+    first = tc_product(a, w, ops.GEMM_STORE_F32, 256)
+    for _ in range(5):
+        assert torch.equal(tc_product(a, w, ops.GEMM_STORE_F32, 256), first)
+    one = tc_product(a[5:6].contiguous(), w, ops.GEMM_STORE_F32, 256)
+    assert torch.equal(one[0], first[5])
+    sixty = tc_product(torch.cat([a, a, a, a])[:60].contiguous(), w, ops.GEMM_STORE_F32, 256)
+    assert torch.equal(sixty[21], first[5])
+
+
+def test_tcgen05_product_refuses_what_tma_cannot_address(ops):
+    from carbon_engine_b200 import ops_tensor
+    a = torch.randn(4, 100, device=dev()).to(torch.bfloat16)          # K = 100 is no multiple of 8
+    w = torch.randn(32, 100, device=dev()).to(torch.bfloat16)
+    out = torch.empty(4, 32, dtype=torch.bfloat16, device=dev())
+    assert not ops_tensor.gemm_bf16(a, w, out, ops.GEMM_STORE)
+    from carbon_engine_b200.parts import linear
+    linear.matmul_nt(a, w, out, linear.STORE)                          # the plain kernel takes it
+    assert rel_err(out, a.double().cpu() @ w.double().cpu().T) < 1e-2

@@ -79,7 +79,9 @@ class BenchHarness:
         """Through Engine.add_request / Engine.step: real prompts are prefilled, then ``steps`` decode
         steps are timed on the host clock between two synchronisations."""
         eng = self.engine
-        sp = SamplingParams(max_tokens=warmup + steps + 4, ignore_eos=True)
+        # long enough that no request ends inside the timed region (requests whose prompts were done
+        # first have decoded through the other prompts' steps already)
+        sp = SamplingParams(max_tokens=warmup + steps + batch + 8, ignore_eos=True)
         for _ in range(batch):
             eng.add_request(self._tokens(self.context), sp)
         while eng.scheduler.stats()["prefill_tokens"] < batch * self.context:

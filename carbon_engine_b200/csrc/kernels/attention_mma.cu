@@ -2,12 +2,12 @@
 // accumulators): a split-KV kernel for sequences that bring one token, and a flash kernel for
 // sequences that bring a portion of a prompt.  Both read keys and values through the block table.
 //
-// Decode: one block per (sequence, KV head, group of up to 16 query heads, split of 256 positions).
+// Decode: one block per (sequence, KV head, group of up to 16 query heads, split of 512 positions).
 // The query heads that share the KV head are the 16 rows of the MMA tile, so K and V are read once
 // per KV head (the reference's paged_decode_tc does the same for up to 8 heads,
 // src/kernels/attention_tc.cu:682-807).  Each of the 4 warps takes 16 of every 64 staged keys and
 // keeps a running (max, sum, output); the warps are combined in shared memory and the block writes
-// one partial per split to scratch memory; a merge kernel combines the splits
+// one partial per split to scratch memory; a merge kernel combines the splits in split order
 // (src/kernels/attention_tc.cu:810-830).  Splits are cut at fixed positions, so a sequence's result
 // does not depend on the batch or on the longest sequence beside it.
 //
@@ -21,7 +21,8 @@
 
 #define AM_THREADS 128
 #define AM_TILE 64           // keys staged per iteration
-#define AM_SPLIT 256         // positions per decode split
+#define AM_SPLIT 512         // positions per decode split
+#define AM_STAGES 3          // staged tiles in flight: loads of tiles i+1, i+2 run while tile i is computed
 #define AM_PAD 8             // padding of a staged row, in elements (keeps 32-bit and ldmatrix reads conflict-free)
 
 typedef __nv_bfloat16 bf16;
@@ -61,6 +62,7 @@ struct MmaAttnArgs {
     const int* ctx_len;         // [B]  keys of the sequence after this step
     const int* block_table;     // [slots, max_pages]
     const int* tiles;           // prefill: [n_tiles, 2] = (sequence, first new token of the tile)
+    int* counters;              // decode: one per (sequence, KV head, head group), zero between launches
     int* status;
     int nh, nkv, d, q_stride, page_size, max_pages, num_pages, window, max_splits, first_seq;
     float scale_log2;           // scale * log2(e)
@@ -175,7 +177,7 @@ __global__ void __launch_bounds__(AM_THREADS) attention_decode_kernel(MmaAttnArg
     int b = blockIdx.x / a.max_splits, split = blockIdx.x % a.max_splits;
     int kvh = blockIdx.y, hg = blockIdx.z;
     int G = a.nh / a.nkv;
-    int t = a.q_start[b];                         // the sequence's single token
+    int t = b;                                    // one-token sequences come first: sequence b brings token b
     int pos = a.positions[t];
     int lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
     int k_begin = split * AM_SPLIT, k_end = min(k_begin + AM_SPLIT, pos + 1);
@@ -183,7 +185,7 @@ __global__ void __launch_bounds__(AM_THREADS) attention_decode_kernel(MmaAttnArg
     const int* table = a.block_table + (size_t)a.seq_slot[b] * a.max_pages;
     int d = a.d, ld = d + AM_PAD;
     bf16* Ks = reinterpret_cast<bf16*>(smem_raw);
-    bf16* Vs = Ks + 2 * AM_TILE * ld;             // two stages of each
+    bf16* Vs = Ks + AM_STAGES * AM_TILE * ld;
 
     int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, quad = lane & 3, grp = lane >> 2;
     int heads_here = min(16, G - hg * 16);
@@ -210,23 +212,28 @@ __global__ void __launch_bounds__(AM_THREADS) attention_decode_kernel(MmaAttnArg
     int los[2] = {lo, lo}, his[2] = {pos, pos};
 
     int n_tiles = (k_end - k_begin + AM_TILE - 1) / AM_TILE;
-    stage_tile(Ks, Vs, a, table, kvh, k_begin, lo, pos);
-    cp_async_commit();
-    for (int it = 0; it < n_tiles; ++it) {
-        int cur = it & 1;
-        if (it + 1 < n_tiles)
-            stage_tile(Ks + (cur ^ 1) * AM_TILE * ld, Vs + (cur ^ 1) * AM_TILE * ld, a, table, kvh,
-                       k_begin + (it + 1) * AM_TILE, lo, pos);
+#pragma unroll
+    for (int p = 0; p < AM_STAGES - 1; ++p) {
+        if (p < n_tiles) stage_tile(Ks + p * AM_TILE * ld, Vs + p * AM_TILE * ld, a, table, kvh, k_begin + p * AM_TILE, lo, pos);
         cp_async_commit();
-        cp_async_wait<1>();
-        __syncthreads();
+    }
+    for (int it = 0; it < n_tiles; ++it) {
+        cp_async_wait<AM_STAGES - 2>();       // tile `it` has landed
+        __syncthreads();                      // ... for everyone, and everyone is done with tile it-1
+        int nxt = it + AM_STAGES - 1;
+        if (nxt < n_tiles) {
+            int st = nxt % AM_STAGES;         // the stage tile it-1 was computed from
+            stage_tile(Ks + st * AM_TILE * ld, Vs + st * AM_TILE * ld, a, table, kvh, k_begin + nxt * AM_TILE, lo, pos);
+        }
+        cp_async_commit();
+        int cur = it % AM_STAGES;
         int k0 = k_begin + it * AM_TILE + warp * 16;
         if (k0 <= pos)
             warp_tile<DMAX, 2>(qf, o, m, l, Ks + (cur * AM_TILE + warp * 16) * ld, Vs + (cur * AM_TILE + warp * 16) * ld,
                                ld, d, k0, los, his, a.scale_log2);
-        __syncthreads();
     }
     cp_async_wait<0>();
+    __syncthreads();
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
@@ -271,29 +278,41 @@ __global__ void __launch_bounds__(AM_THREADS) attention_decode_kernel(MmaAttnArg
     }
 }
 
-// grid (n_seqs, nh): out[t, h, :] = sum_s O_s 2^(m_s - M) / sum_s l_s 2^(m_s - M)
+// grid (n_seqs, nh), one warp per 32 output columns: out[t, h, :] = sum_s O_s w_s with
+// w_s = 2^(m_s - M) / sum_s l_s 2^(m_s - M).  The weights are computed once per block by warp 0
+// (lanes over splits, fixed shuffle order), then every thread adds its column in split order.
 __global__ void attention_merge_kernel(MmaAttnArgs a) {
+    extern __shared__ float wts[];                              // [s1 - s0 + 1]
     int b = blockIdx.x, h = blockIdx.y;
     int t = a.q_start[b];
     int pos = a.positions[t];
     int lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
-    int s0 = lo / AM_SPLIT, s1 = pos / AM_SPLIT;            // splits that hold visible keys
-    size_t base = ((size_t)b * a.nh + h) * a.max_splits;
-    float M = -INFINITY;
-    for (int s = s0; s <= s1; ++s) M = fmaxf(M, a.part_ml[(base + s) * 2]);
-    float L = 0.f;
-    for (int s = s0; s <= s1; ++s) {
-        float ms = a.part_ml[(base + s) * 2];
-        L += ms == -INFINITY ? 0.f : a.part_ml[(base + s) * 2 + 1] * exp2f(ms - M);
+    int s0 = lo / AM_SPLIT, s1 = pos / AM_SPLIT;                // splits that hold visible keys
+    int ns = s1 - s0 + 1;
+    size_t base = ((size_t)b * a.nh + h) * a.max_splits + s0;
+    if (threadIdx.x < 32) {
+        int lane = threadIdx.x;
+        float M = -INFINITY;
+        for (int s = lane; s < ns; s += 32) M = fmaxf(M, a.part_ml[(base + s) * 2]);
+        for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+        float L = 0.f;
+        for (int s = lane; s < ns; s += 32) {
+            float ms = a.part_ml[(base + s) * 2];
+            float f = ms == -INFINITY ? 0.f : exp2f(ms - M);
+            wts[s] = f;
+            L += a.part_ml[(base + s) * 2 + 1] * f;
+        }
+        for (int o = 16; o > 0; o >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o);
+        float inv = L > 0.f ? 1.0f / L : 0.f;
+        __syncwarp();
+        for (int s = lane; s < ns; s += 32) wts[s] *= inv;
     }
-    float inv = L > 0.f ? 1.0f / L : 0.f;
+    __syncthreads();
     for (int col = threadIdx.x; col < a.d; col += blockDim.x) {
         float acc = 0.f;
-        for (int s = s0; s <= s1; ++s) {
-            float ms = a.part_ml[(base + s) * 2];
-            if (ms != -INFINITY) acc += a.part_o[(base + s) * a.d + col] * exp2f(ms - M);
-        }
-        a.out[((size_t)t * a.nh + h) * a.d + col] = __float2bfloat16_rn(acc * inv);
+#pragma unroll 8
+        for (int s = 0; s < ns; ++s) acc = fmaf(a.part_o[(base + s) * a.d + col], wts[s], acc);
+        a.out[((size_t)t * a.nh + h) * a.d + col] = __float2bfloat16_rn(acc);
     }
 }
 
@@ -313,7 +332,7 @@ __global__ void __launch_bounds__(AM_THREADS) attention_prefill_kernel(MmaAttnAr
     const int* table = a.block_table + (size_t)a.seq_slot[b] * a.max_pages;
     int d = a.d, ld = d + AM_PAD;
     bf16* Ks = reinterpret_cast<bf16*>(smem_raw);
-    bf16* Vs = Ks + 2 * AM_TILE * ld;
+    bf16* Vs = Ks + AM_STAGES * AM_TILE * ld;
 
     int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, quad = lane & 3, grp = lane >> 2;
     int r0 = warp * 16 + grp, r1 = r0 + 8;                   // this thread's two query rows within the tile
@@ -343,21 +362,26 @@ __global__ void __launch_bounds__(AM_THREADS) attention_prefill_kernel(MmaAttnAr
 
     int k_begin = lo_tile / AM_TILE * AM_TILE;
     int n_tiles = (p_last - k_begin) / AM_TILE + 1;
-    stage_tile(Ks, Vs, a, table, kvh, k_begin, lo_tile, p_last);
-    cp_async_commit();
-    for (int it = 0; it < n_tiles; ++it) {
-        int cur = it & 1;
-        if (it + 1 < n_tiles)
-            stage_tile(Ks + (cur ^ 1) * AM_TILE * ld, Vs + (cur ^ 1) * AM_TILE * ld, a, table, kvh,
-                       k_begin + (it + 1) * AM_TILE, lo_tile, p_last);
+#pragma unroll
+    for (int p = 0; p < AM_STAGES - 1; ++p) {
+        if (p < n_tiles)
+            stage_tile(Ks + p * AM_TILE * ld, Vs + p * AM_TILE * ld, a, table, kvh, k_begin + p * AM_TILE, lo_tile, p_last);
         cp_async_commit();
-        cp_async_wait<1>();
+    }
+    for (int it = 0; it < n_tiles; ++it) {
+        cp_async_wait<AM_STAGES - 2>();
         __syncthreads();
+        int nxt = it + AM_STAGES - 1;
+        if (nxt < n_tiles) {
+            int st = nxt % AM_STAGES;
+            stage_tile(Ks + st * AM_TILE * ld, Vs + st * AM_TILE * ld, a, table, kvh, k_begin + nxt * AM_TILE, lo_tile, p_last);
+        }
+        cp_async_commit();
+        int cur = it % AM_STAGES;
         int k0 = k_begin + it * AM_TILE;
         if (warp * 16 < nq && k0 <= warp_hi && k0 + AM_TILE > warp_lo)
             warp_tile<DMAX, 8>(qf, o, m, l, Ks + cur * AM_TILE * ld, Vs + cur * AM_TILE * ld, ld, d, k0, los, his,
                                a.scale_log2);
-        __syncthreads();
     }
     cp_async_wait<0>();
 #pragma unroll
@@ -378,7 +402,7 @@ __global__ void __launch_bounds__(AM_THREADS) attention_prefill_kernel(MmaAttnAr
     }
 }
 
-static size_t stage_bytes(int d) { return (size_t)2 * 2 * AM_TILE * (d + AM_PAD) * sizeof(bf16); }
+static size_t stage_bytes(int d) { return (size_t)AM_STAGES * 2 * AM_TILE * (d + AM_PAD) * sizeof(bf16); }
 
 static int check_common(const char* who, int nh, int nkv, int d, int q_stride) {
     if (d < 16 || d > 256 || d % 16) return ce_fail(CE_ERR_SIZE, "%s: head_dim %d must be a multiple of 16 in 16..256", who, d);
@@ -401,14 +425,16 @@ extern "C" long long ce_attention_decode_scratch(int n_seqs, int nh, int d, int 
 }
 
 // The first n_seqs sequences of the step bring one token each (tokens 0 .. n_seqs-1).
-// max_splits >= ceil(longest context / 256); it fixes the grid, not the result.
+// max_splits >= ceil(longest context / AM_SPLIT); it fixes the grid, not the result.
+extern "C" int ce_attention_decode_split() { return AM_SPLIT; }
+
 extern "C" int ce_attention_decode_bf16(const void* q, const void* k_pool, const void* v_pool, void* out, float* scratch,
-                                        const int* positions, const int* seq_slot, const int* q_start,
+                                        int* counters, int n_counters, const int* positions, const int* seq_slot, const int* q_start,
                                         const int* ctx_len, const int* block_table, int* status, int n_seqs, int nh,
                                         int nkv, int d, int q_stride, int page_size, int max_pages, int num_pages,
                                         int window, float scale, int max_splits, cudaStream_t stream) {
     if (n_seqs == 0) return CE_OK;
-    if (!q || !k_pool || !v_pool || !out || !scratch || !positions || !seq_slot || !q_start || !ctx_len || !block_table || !status)
+    if (!q || !k_pool || !v_pool || !out || !scratch || !counters || !positions || !seq_slot || !q_start || !ctx_len || !block_table || !status)
         return ce_fail(CE_ERR_ARG, "ce_attention_decode_bf16: null pointer");
     int rc = check_common("ce_attention_decode_bf16", nh, nkv, d, q_stride);
     if (rc) return rc;
@@ -423,6 +449,9 @@ extern "C" int ce_attention_decode_bf16(const void* q, const void* k_pool, const
     a.scale_log2 = scale * 1.4426950408889634f;
     int G = nh / nkv;
     dim3 grid(n_seqs * max_splits, nkv, (G + 15) / 16);
+    if ((long long)n_seqs * nkv * grid.z > n_counters)
+        return ce_fail(CE_ERR_ARG, "ce_attention_decode_bf16: %lld counters needed, %d given", (long long)n_seqs * nkv * grid.z, n_counters);
+    a.counters = counters;
     size_t smem = stage_bytes(d);
     size_t comb = (size_t)(4 * 16 * d + 128) * sizeof(float);
     if (comb > smem) smem = comb;
@@ -437,7 +466,7 @@ extern "C" int ce_attention_decode_bf16(const void* q, const void* k_pool, const
         attention_decode_kernel<256><<<grid, AM_THREADS, smem, stream>>>(a);
     }
     if ((rc = ce_check_launch("ce_attention_decode_bf16"))) return rc;
-    attention_merge_kernel<<<dim3(n_seqs, nh), 128, 0, stream>>>(a);
+    attention_merge_kernel<<<dim3(n_seqs, nh), d >= 128 ? 128 : (d + 31) / 32 * 32, max_splits * sizeof(float), stream>>>(a);
     return ce_check_launch("ce_attention_decode_bf16 (merge)");
 }
 

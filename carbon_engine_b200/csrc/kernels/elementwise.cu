@@ -21,6 +21,7 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict_
         return;
     }
     const T* row = table + (size_t)tok * H;
+#pragma unroll 4
     for (int j = threadIdx.x; j < H; j += blockDim.x) x[(size_t)t * H + j] = CeType<T>::load(row + j);
 }
 
@@ -29,9 +30,9 @@ extern "C" int ce_embed(const void* table, int dtype, const int* tokens, float* 
     if (T == 0) return CE_OK;
     if (!table || !tokens || !x || !status) return ce_fail(CE_ERR_ARG, "ce_embed: null pointer");
     if (dtype == CE_F32)
-        embed_kernel<float><<<T, 256, 0, stream>>>((const float*)table, tokens, x, H, V, status);
+        embed_kernel<float><<<T, H >= 1024 ? 1024 : 256, 0, stream>>>((const float*)table, tokens, x, H, V, status);
     else if (dtype == CE_BF16)
-        embed_kernel<__nv_bfloat16><<<T, 256, 0, stream>>>((const __nv_bfloat16*)table, tokens, x, H, V, status);
+        embed_kernel<__nv_bfloat16><<<T, H >= 1024 ? 1024 : 256, 0, stream>>>((const __nv_bfloat16*)table, tokens, x, H, V, status);
     else
         return ce_fail(CE_ERR_ARG, "ce_embed: unknown dtype %d", dtype);
     return ce_check_launch("ce_embed");
@@ -58,16 +59,68 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
     for (int j = threadIdx.x; j < H; j += blockDim.x) CeType<T>::store(o + j, xr[j] * inv * w[j]);
 }
 
+// The same for widths that are multiples of 4 and at most 4 * 4 * blockDim: every thread keeps its
+// float4 elements in registers, so the row is read once and all loads are in flight together.
+template <typename T>
+__global__ void __launch_bounds__(1024) rmsnorm_vec_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                                                          T* __restrict__ out, const int* __restrict__ rows, int H,
+                                                          float eps) {
+    __shared__ float scratch[32];
+    int r = blockIdx.x, n4 = H >> 2;
+    const float4* xr = reinterpret_cast<const float4*>(x + (size_t)(rows ? rows[r] : r) * H);
+    const float4* wr = reinterpret_cast<const float4*>(w);
+    float4 v[4], g[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        int j = threadIdx.x + i * blockDim.x;
+        v[i] = j < n4 ? xr[j] : make_float4(0.f, 0.f, 0.f, 0.f);
+        g[i] = j < n4 ? wr[j] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        ss = fmaf(v[i].x, v[i].x, ss); ss = fmaf(v[i].y, v[i].y, ss);
+        ss = fmaf(v[i].z, v[i].z, ss); ss = fmaf(v[i].w, v[i].w, ss);
+    }
+    ss = ce_block_sum(ss, scratch);
+    float inv = 1.0f / sqrtf(ss / (float)H + eps);
+    T* o = out + (size_t)r * H;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        int j = threadIdx.x + i * blockDim.x;
+        if (j < n4) {
+            CeType<T>::store(o + 4 * j, v[i].x * inv * g[i].x);
+            CeType<T>::store(o + 4 * j + 1, v[i].y * inv * g[i].y);
+            CeType<T>::store(o + 4 * j + 2, v[i].z * inv * g[i].z);
+            CeType<T>::store(o + 4 * j + 3, v[i].w * inv * g[i].w);
+        }
+    }
+}
+
+// Threads per row of the vector kernel: a function of the width only, so that the order of the sum
+// never depends on the batch.  0: use the scalar kernel.
+static int rmsnorm_vec_threads(int H, const void* x, const void* w) {
+    if (H % 4 || (((uintptr_t)x | (uintptr_t)w) & 15)) return 0;
+    int n4 = H / 4;
+    int threads = ((n4 + 3) / 4 + 31) / 32 * 32;       // four float4 per thread where possible
+    if (threads < 128) threads = 128;
+    if (threads > 1024) return 0;
+    return threads;
+}
+
 extern "C" int ce_rmsnorm(const float* x, const float* w, void* out, int out_dtype, const int* rows, int R, int H,
                           float eps, cudaStream_t stream) {
     if (R == 0) return CE_OK;
     if (!x || !w || !out) return ce_fail(CE_ERR_ARG, "ce_rmsnorm: null pointer");
     if (H <= 0) return ce_fail(CE_ERR_SIZE, "ce_rmsnorm: width %d", H);
-    if (out_dtype == CE_F32)
-        rmsnorm_kernel<float><<<R, 256, 0, stream>>>(x, w, (float*)out, rows, H, eps);
-    else if (out_dtype == CE_BF16)
-        rmsnorm_kernel<__nv_bfloat16><<<R, 256, 0, stream>>>(x, w, (__nv_bfloat16*)out, rows, H, eps);
-    else
+    int vt = rmsnorm_vec_threads(H, x, w);
+    if (out_dtype == CE_F32) {
+        if (vt) rmsnorm_vec_kernel<float><<<R, vt, 0, stream>>>(x, w, (float*)out, rows, H, eps);
+        else rmsnorm_kernel<float><<<R, 256, 0, stream>>>(x, w, (float*)out, rows, H, eps);
+    } else if (out_dtype == CE_BF16) {
+        if (vt) rmsnorm_vec_kernel<__nv_bfloat16><<<R, vt, 0, stream>>>(x, w, (__nv_bfloat16*)out, rows, H, eps);
+        else rmsnorm_kernel<__nv_bfloat16><<<R, 256, 0, stream>>>(x, w, (__nv_bfloat16*)out, rows, H, eps);
+    } else
         return ce_fail(CE_ERR_ARG, "ce_rmsnorm: unknown dtype %d", out_dtype);
     return ce_check_launch("ce_rmsnorm");
 }

@@ -246,14 +246,29 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
             if (s_ticket == a.splits - 1) {
                 __threadfence();
                 if (n < a.N && s_abort == 0) {
-                    for (int m = 0; m < m_valid; ++m) {
-                        float g = 0.f, u = 0.f;
+                    // eight tokens at a time, all their loads in flight together; sums in split order
+                    size_t split_stride = (size_t)n_tiles * NACC * BN * BM;
+                    const float* p0 = a.scratch + ((size_t)tile * NACC) * BN * BM + row;
+                    for (int mb = 0; mb < m_valid; mb += 8) {
+                        float g[8], u[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) g[j] = u[j] = 0.f;
+#pragma unroll 4
                         for (int s = 0; s < a.splits; ++s) {
-                            const float* p = a.scratch + (((size_t)s * n_tiles + tile) * NACC) * BN * BM;
-                            g += __ldcg(p + (size_t)m * BM + row);
-                            if (NACC == 2) u += __ldcg(p + (size_t)(BN + m) * BM + row);
+                            const float* p = p0 + s * split_stride;
+                            float tg[8], tu[8];
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) {
+                                bool in = mb + j < m_valid;
+                                tg[j] = in ? __ldcg(p + (size_t)(mb + j) * BM) : 0.f;
+                                tu[j] = (NACC == 2 && in) ? __ldcg(p + (size_t)(BN + mb + j) * BM) : 0.f;
+                            }
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) { g[j] += tg[j]; u[j] += tu[j]; }
                         }
-                        epilogue_store(a, m0 + m, n, g, u);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j)
+                            if (mb + j < m_valid) epilogue_store(a, m0 + mb + j, n, g[j], u[j]);
                     }
                 }
                 if (threadIdx.x == 64) a.counters[tile] = 0;      // ready for the next launch
@@ -349,10 +364,13 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, const TcArgs& a, dim3 g
 extern "C" int ce_gemm_tc_splits(int M, int N, int K) {
     int kblocks = (K + BK - 1) / BK;
     if (M > 256) return 1;
+    int bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
     int tiles = (N + BM - 1) / BM;
-    int s = 148 / tiles;
-    if (s > kblocks / 4) s = kblocks / 4;
-    if (s > 8) s = 8;
+    int s = 296 / tiles;                       // two CTAs per SM keep enough loads in flight
+    if (s > kblocks / 4) s = kblocks / 4;      // at least four k-blocks per split
+    int by_traffic = (int)(0.15 * K / (4.0 * bn));   // partial sums cost S * bn * 4 / K of the weight bytes
+    if (s > by_traffic) s = by_traffic;
+    if (s > 16) s = 16;
     return s < 1 ? 1 : s;
 }
 

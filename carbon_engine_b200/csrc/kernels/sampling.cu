@@ -163,7 +163,17 @@ __global__ void __launch_bounds__(SMP_THREADS) argmax_kernel(const float* __rest
     const float* l = logits + (size_t)r * V;
     float bv = -INFINITY;
     int bi = 0x7fffffff;
-    for (int i = threadIdx.x; i < V; i += SMP_THREADS) {
+    int i = threadIdx.x;
+    // eight loads in flight per thread; indices rise within a thread, so "first maximum" holds
+    for (; i + 7 * SMP_THREADS < V; i += 8 * SMP_THREADS) {
+        float z[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) z[k] = l[i + k * SMP_THREADS];
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+            if (z[k] > bv) { bv = z[k]; bi = i + k * SMP_THREADS; }
+    }
+    for (; i < V; i += SMP_THREADS) {
         float z = l[i];
         if (z > bv) { bv = z; bi = i; }
     }

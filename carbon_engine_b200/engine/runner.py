@@ -38,6 +38,8 @@ class ModelRunner:
         self.fast_attention = True
         self.graphs_enabled = False
         self._graphs = {}
+        from .. import ops_tensor
+        self._decode_split = ops_tensor.decode_split()
         self._graph_pool = None
         self.h2d_bytes_last = 0
         self.kernel_launches = 0
@@ -133,7 +135,7 @@ class ModelRunner:
                 h_tiles[2 * nt], h_tiles[2 * nt + 1] = bi, q0
                 nt += 1
         ctx.n_tiles = nt
-        ctx.decode_splits = (dec_ctx + 255) // 256
+        ctx.decode_splits = (dec_ctx + self._decode_split - 1) // self._decode_split
         ctx.h_tokens = h_tok[:T].tolist()
 
         rows: List[int] = []

@@ -12,9 +12,10 @@ from .csrc.kernel_lib import kernels
 
 _i, _f, _ll, _p = ctypes.c_int, ctypes.c_float, ctypes.c_longlong, ctypes.c_void_p
 kernel_lib.declare("ce_attention_decode_scratch", _ll, [_i, _i, _i, _i])
-# q, k_pool, v_pool, out, scratch, positions, seq_slot, q_start, ctx_len, block_table, status,
+# q, k_pool, v_pool, out, scratch, counters, n_counters, positions, seq_slot, q_start, ctx_len, block_table, status,
 # n_seqs, nh, nkv, d, q_stride, page_size, max_pages, num_pages, window, scale, max_splits, stream
-kernel_lib.declare("ce_attention_decode_bf16", _i, [_p] * 11 + [_i] * 9 + [_f, _i, _p])
+kernel_lib.declare("ce_attention_decode_bf16", _i, [_p] * 6 + [_i] + [_p] * 6 + [_i] * 9 + [_f, _i, _p])
+kernel_lib.declare("ce_attention_decode_split", _i, [])
 # q, k_pool, v_pool, out, positions, seq_slot, q_start, ctx_len, block_table, tiles, status,
 # n_tiles, nh, nkv, d, q_stride, page_size, max_pages, num_pages, window, scale, stream
 kernel_lib.declare("ce_attention_prefill_bf16", _i, [_p] * 11 + [_i] * 9 + [_f, _p])
@@ -25,7 +26,11 @@ kernel_lib.declare("ce_gemm_tc_splits", _i, [_i, _i, _i])
 # A, W, C, M, N, K, lda, ldc, mode, scratch, scratch_floats, counters, n_counters, status, stream
 kernel_lib.declare("ce_gemm_tc", _i, [_p, _p, _p, _i, _i, _i, _i, _i, _i, _p, _ll, _p, _i, _p, _p])
 
-DECODE_SPLIT = 256
+
+def decode_split() -> int:
+    """Positions per split of the decode attention kernel."""
+    return kernels().ce_attention_decode_split()
+
 GEMM_SCRATCH_FLOATS = 16 << 20        # 64 MB of split-K partial sums
 GEMM_COUNTERS = 1 << 16
 
@@ -40,6 +45,7 @@ class _Workspace:
         self.scratch = torch.empty(GEMM_SCRATCH_FLOATS, dtype=torch.float32, device=device)
         self.counters = torch.zeros(GEMM_COUNTERS, dtype=torch.int32, device=device)
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        self.attn_counters = torch.zeros(GEMM_COUNTERS, dtype=torch.int32, device=device)
 
 
 def gemm_workspace(device) -> _Workspace:
@@ -91,9 +97,10 @@ def attention_bf16(ctx, qkv, out, cache, table, nh, nkv, d, window, scale) -> bo
         splits = ctx.decode_splits
         need = k.ce_attention_decode_scratch(ctx.n_decode, nh, d, splits)
         scratch = ctx.scratch("attention_decode", need)
+        ws = gemm_workspace(qkv.device)
         ops._ok(k.ce_attention_decode_bf16(
             qkv.data_ptr(), cache.k_pool.data_ptr(), cache.v_pool.data_ptr(), out.data_ptr(), scratch.data_ptr(),
-            ctx.positions.data_ptr(), ctx.seq_slot.data_ptr(), ctx.q_start.data_ptr(), ctx.ctx_len.data_ptr(),
+            ws.attn_counters.data_ptr(), ws.attn_counters.numel(), ctx.positions.data_ptr(), ctx.seq_slot.data_ptr(), ctx.q_start.data_ptr(), ctx.ctx_len.data_ptr(),
             table.data_ptr(), ctx.status.data_ptr(), ctx.n_decode, nh, nkv, d, qkv.shape[1], *args, splits, stream), 2)
     if ctx.n_tiles > 0:
         ops._ok(k.ce_attention_prefill_bf16(

@@ -374,7 +374,9 @@ class FakeCtx:
         self.seq_slot = mk(order)                  # sequence bi of the step uses block-table row order[bi]
         self.tiles = mk(tiles if tiles else [[0, 0]])
         self.n_tiles = len(tiles)
-        self.decode_splits = (dec + 255) // 256
+        from carbon_engine_b200 import ops_tensor
+        split = ops_tensor.decode_split()
+        self.decode_splits = (dec + split - 1) // split
         self.status = status()
         self.device = dev()
         self._s = {}
@@ -514,8 +516,12 @@ def test_tcgen05_product_is_repeatable_and_rows_stand_alone(ops):
         assert torch.equal(tc_product(a, w, ops.GEMM_STORE_F32, 256), first)
     one = tc_product(a[5:6].contiguous(), w, ops.GEMM_STORE_F32, 256)
     assert torch.equal(one[0], first[5])
-    sixty = tc_product(torch.cat([a, a, a, a])[:60].contiguous(), w, ops.GEMM_STORE_F32, 256)
-    assert torch.equal(sixty[21], first[5])
+    # a larger tile of tokens may split K differently: equal within a tile size, close across tile sizes
+    many = torch.cat([a, a, a, a])
+    sixty = tc_product(many[:60].contiguous(), w, ops.GEMM_STORE_F32, 256)
+    forty = tc_product(many[:40].contiguous(), w, ops.GEMM_STORE_F32, 256)
+    assert torch.equal(sixty[21], forty[21])
+    assert rel_err(sixty[21], first[5]) < 1e-5
 
 
 def test_tcgen05_product_refuses_what_tma_cannot_address(ops):

@@ -32,6 +32,7 @@ struct AttnArgs {
 
 template <typename T>
 __global__ void attention_generic_kernel(AttnArgs a) {
+    ce_pdl_begin();
     extern __shared__ __align__(16) unsigned char smem_raw[];
     long long* vrow = (long long*)smem_raw;           // ATT_THREADS
     float* probs = (float*)(vrow + ATT_THREADS);      // ATT_THREADS
@@ -122,9 +123,9 @@ extern "C" int ce_attention_generic(const void* q, const void* k_pool, const voi
     size_t smem = (d + ATT_THREADS + 32) * sizeof(float) + ATT_THREADS * sizeof(long long);
     dim3 grid(T, nh);
     if (dtype == CE_F32)
-        attention_generic_kernel<float><<<grid, ATT_THREADS, smem, stream>>>(a);
+        ce_launch(attention_generic_kernel<float>, grid, ATT_THREADS, smem, stream, a);
     else if (dtype == CE_BF16)
-        attention_generic_kernel<__nv_bfloat16><<<grid, ATT_THREADS, smem, stream>>>(a);
+        ce_launch(attention_generic_kernel<__nv_bfloat16>, grid, ATT_THREADS, smem, stream, a);
     else
         return ce_fail(CE_ERR_ARG, "ce_attention_generic: unknown dtype %d", dtype);
     return ce_check_launch("ce_attention_generic");

@@ -72,23 +72,32 @@ struct MmaAttnArgs {
 // Keys outside [lo, hi] are filled with zeros, so that a masked probability of 0 never meets a NaN.
 __device__ __forceinline__ void stage_tile(bf16* Ks, bf16* Vs, const MmaAttnArgs& a, const int* table, int kvh, int k0,
                                            int lo, int hi) {
-    int d = a.d, ld = d + AM_PAD, chunks = d / 8;
-    for (int c = threadIdx.x; c < AM_TILE * chunks; c += AM_THREADS) {
-        int kl = c / chunks, part = c - kl * chunks;
+    // 16-byte chunks c = thread, thread + 128, ...: (key, part) advance by fixed steps, without divisions
+    int d = a.d, ld = d + AM_PAD, chunks = d >> 3;
+    int kl = threadIdx.x / chunks, part = threadIdx.x - kl * chunks;
+    int dkl = AM_THREADS / chunks, dpart = AM_THREADS - dkl * chunks;
+    bool pow2 = (a.page_size & (a.page_size - 1)) == 0;
+    int shift = 31 - __clz(a.page_size);
+    while (kl < AM_TILE) {
         int key = k0 + kl;
         bool valid = key >= lo && key <= hi;
         size_t row = 0;
         if (valid) {
-            int page = table[key / a.page_size];
+            int pi = pow2 ? key >> shift : key / a.page_size;
+            int off = pow2 ? key & (a.page_size - 1) : key - pi * a.page_size;
+            int page = table[pi];
             if (page < 0 || page >= a.num_pages) {
                 atomicExch(a.status, 4);
                 valid = false;
             } else {
-                row = (((size_t)page * a.nkv + kvh) * a.page_size + key % a.page_size) * d + part * 8;
+                row = (((size_t)page * a.nkv + kvh) * a.page_size + off) * d + part * 8;
             }
         }
         cp_async16(Ks + kl * ld + part * 8, a.k_pool + row, valid);
         cp_async16(Vs + kl * ld + part * 8, a.v_pool + row, valid);
+        kl += dkl;
+        part += dpart;
+        if (part >= chunks) { part -= chunks; ++kl; }
     }
 }
 
@@ -173,6 +182,7 @@ __device__ __forceinline__ void warp_tile(const uint32_t (&qf)[DMAX / 16][4], fl
 // ---------------------------------------------------------------------------------------------
 template <int DMAX>
 __global__ void __launch_bounds__(AM_THREADS) attention_decode_kernel(MmaAttnArgs a) {
+    ce_pdl_begin();
     extern __shared__ __align__(16) unsigned char smem_raw[];
     int b = blockIdx.x / a.max_splits, split = blockIdx.x % a.max_splits;
     int kvh = blockIdx.y, hg = blockIdx.z;
@@ -282,6 +292,7 @@ __global__ void __launch_bounds__(AM_THREADS) attention_decode_kernel(MmaAttnArg
 // w_s = 2^(m_s - M) / sum_s l_s 2^(m_s - M).  The weights are computed once per block by warp 0
 // (lanes over splits, fixed shuffle order), then every thread adds its column in split order.
 __global__ void attention_merge_kernel(MmaAttnArgs a) {
+    ce_pdl_begin();
     extern __shared__ float wts[];                              // [s1 - s0 + 1]
     int b = blockIdx.x, h = blockIdx.y;
     int t = a.q_start[b];
@@ -321,6 +332,7 @@ __global__ void attention_merge_kernel(MmaAttnArgs a) {
 // ---------------------------------------------------------------------------------------------
 template <int DMAX>
 __global__ void __launch_bounds__(AM_THREADS) attention_prefill_kernel(MmaAttnArgs a) {
+    ce_pdl_begin();
     extern __shared__ __align__(16) unsigned char smem_raw[];
     int b = a.tiles[2 * blockIdx.x], q0 = a.tiles[2 * blockIdx.x + 1];
     int h = blockIdx.y, kvh = h / (a.nh / a.nkv);
@@ -457,16 +469,16 @@ extern "C" int ce_attention_decode_bf16(const void* q, const void* k_pool, const
     if (comb > smem) smem = comb;
     if (d <= 64) {
         if ((rc = set_smem(attention_decode_kernel<64>, smem, "ce_attention_decode_bf16"))) return rc;
-        attention_decode_kernel<64><<<grid, AM_THREADS, smem, stream>>>(a);
+        ce_launch(attention_decode_kernel<64>, grid, AM_THREADS, smem, stream, a);
     } else if (d <= 128) {
         if ((rc = set_smem(attention_decode_kernel<128>, smem, "ce_attention_decode_bf16"))) return rc;
-        attention_decode_kernel<128><<<grid, AM_THREADS, smem, stream>>>(a);
+        ce_launch(attention_decode_kernel<128>, grid, AM_THREADS, smem, stream, a);
     } else {
         if ((rc = set_smem(attention_decode_kernel<256>, smem, "ce_attention_decode_bf16"))) return rc;
-        attention_decode_kernel<256><<<grid, AM_THREADS, smem, stream>>>(a);
+        ce_launch(attention_decode_kernel<256>, grid, AM_THREADS, smem, stream, a);
     }
     if ((rc = ce_check_launch("ce_attention_decode_bf16"))) return rc;
-    attention_merge_kernel<<<dim3(n_seqs, nh), d >= 128 ? 128 : (d + 31) / 32 * 32, max_splits * sizeof(float), stream>>>(a);
+    ce_launch(attention_merge_kernel, dim3(n_seqs, nh), d >= 128 ? 128 : (d + 31) / 32 * 32, max_splits * sizeof(float), stream, a);
     return ce_check_launch("ce_attention_decode_bf16 (merge)");
 }
 
@@ -493,13 +505,13 @@ extern "C" int ce_attention_prefill_bf16(const void* q, const void* k_pool, cons
     size_t smem = stage_bytes(d);
     if (d <= 64) {
         if ((rc = set_smem(attention_prefill_kernel<64>, smem, "ce_attention_prefill_bf16"))) return rc;
-        attention_prefill_kernel<64><<<grid, AM_THREADS, smem, stream>>>(a);
+        ce_launch(attention_prefill_kernel<64>, grid, AM_THREADS, smem, stream, a);
     } else if (d <= 128) {
         if ((rc = set_smem(attention_prefill_kernel<128>, smem, "ce_attention_prefill_bf16"))) return rc;
-        attention_prefill_kernel<128><<<grid, AM_THREADS, smem, stream>>>(a);
+        ce_launch(attention_prefill_kernel<128>, grid, AM_THREADS, smem, stream, a);
     } else {
         if ((rc = set_smem(attention_prefill_kernel<256>, smem, "ce_attention_prefill_bf16"))) return rc;
-        attention_prefill_kernel<256><<<grid, AM_THREADS, smem, stream>>>(a);
+        ce_launch(attention_prefill_kernel<256>, grid, AM_THREADS, smem, stream, a);
     }
     return ce_check_launch("ce_attention_prefill_bf16");
 }

@@ -17,7 +17,33 @@
 #define CE_F32 0
 #define CE_BF16 1
 
+#include <utility>
+
 extern "C" const char* ce_last_error();
+// Programmatic dependent launch: a kernel launched through ce_launch() may be scheduled while the
+// kernel before it in the stream still runs.  Every kernel therefore begins with ce_pdl_begin():
+// it lets its own dependents be scheduled early, and then waits until all grids before it are
+// complete and their memory is visible, before it touches anything they wrote or still read.
+// (Both instructions do nothing in a kernel launched the ordinary way.)
+bool ce_pdl_enabled();
+__device__ __forceinline__ void ce_pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void ce_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void ce_pdl_begin() { ce_pdl_launch_dependents(); ce_pdl_wait(); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t ce_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ce_pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
 int ce_fail(int code, const char* fmt, ...);
 int ce_check_launch(const char* what);
 

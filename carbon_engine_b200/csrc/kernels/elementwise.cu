@@ -13,6 +13,7 @@
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ tokens,
                              float* __restrict__ x, int H, int V, int* __restrict__ status) {
+    ce_pdl_begin();
     int t = blockIdx.x;
     int tok = tokens[t];
     if (tok < 0 || tok >= V) {
@@ -30,9 +31,9 @@ extern "C" int ce_embed(const void* table, int dtype, const int* tokens, float* 
     if (T == 0) return CE_OK;
     if (!table || !tokens || !x || !status) return ce_fail(CE_ERR_ARG, "ce_embed: null pointer");
     if (dtype == CE_F32)
-        embed_kernel<float><<<T, H >= 1024 ? 1024 : 256, 0, stream>>>((const float*)table, tokens, x, H, V, status);
+        ce_launch(embed_kernel<float>, T, H >= 1024 ? 1024 : 256, 0, stream, (const float*)table, tokens, x, H, V, status);
     else if (dtype == CE_BF16)
-        embed_kernel<__nv_bfloat16><<<T, H >= 1024 ? 1024 : 256, 0, stream>>>((const __nv_bfloat16*)table, tokens, x, H, V, status);
+        ce_launch(embed_kernel<__nv_bfloat16>, T, H >= 1024 ? 1024 : 256, 0, stream, (const __nv_bfloat16*)table, tokens, x, H, V, status);
     else
         return ce_fail(CE_ERR_ARG, "ce_embed: unknown dtype %d", dtype);
     return ce_check_launch("ce_embed");
@@ -45,6 +46,7 @@ extern "C" int ce_embed(const void* table, int dtype, const int* tokens, float* 
 template <typename T>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w, T* __restrict__ out,
                                const int* __restrict__ rows, int H, float eps) {
+    ce_pdl_begin();
     __shared__ float scratch[32];
     int r = blockIdx.x;
     const float* xr = x + (size_t)(rows ? rows[r] : r) * H;
@@ -65,6 +67,7 @@ template <typename T>
 __global__ void __launch_bounds__(1024) rmsnorm_vec_kernel(const float* __restrict__ x, const float* __restrict__ w,
                                                           T* __restrict__ out, const int* __restrict__ rows, int H,
                                                           float eps) {
+    ce_pdl_begin();
     __shared__ float scratch[32];
     int r = blockIdx.x, n4 = H >> 2;
     const float4* xr = reinterpret_cast<const float4*>(x + (size_t)(rows ? rows[r] : r) * H);
@@ -115,11 +118,11 @@ extern "C" int ce_rmsnorm(const float* x, const float* w, void* out, int out_dty
     if (H <= 0) return ce_fail(CE_ERR_SIZE, "ce_rmsnorm: width %d", H);
     int vt = rmsnorm_vec_threads(H, x, w);
     if (out_dtype == CE_F32) {
-        if (vt) rmsnorm_vec_kernel<float><<<R, vt, 0, stream>>>(x, w, (float*)out, rows, H, eps);
-        else rmsnorm_kernel<float><<<R, 256, 0, stream>>>(x, w, (float*)out, rows, H, eps);
+        if (vt) ce_launch(rmsnorm_vec_kernel<float>, R, vt, 0, stream, x, w, (float*)out, rows, H, eps);
+        else ce_launch(rmsnorm_kernel<float>, R, 256, 0, stream, x, w, (float*)out, rows, H, eps);
     } else if (out_dtype == CE_BF16) {
-        if (vt) rmsnorm_vec_kernel<__nv_bfloat16><<<R, vt, 0, stream>>>(x, w, (__nv_bfloat16*)out, rows, H, eps);
-        else rmsnorm_kernel<__nv_bfloat16><<<R, 256, 0, stream>>>(x, w, (__nv_bfloat16*)out, rows, H, eps);
+        if (vt) ce_launch(rmsnorm_vec_kernel<__nv_bfloat16>, R, vt, 0, stream, x, w, (__nv_bfloat16*)out, rows, H, eps);
+        else ce_launch(rmsnorm_kernel<__nv_bfloat16>, R, 256, 0, stream, x, w, (__nv_bfloat16*)out, rows, H, eps);
     } else
         return ce_fail(CE_ERR_ARG, "ce_rmsnorm: unknown dtype %d", out_dtype);
     return ce_check_launch("ce_rmsnorm");
@@ -158,6 +161,7 @@ struct QkRopeArgs {
 
 template <typename T>
 __global__ void qk_rope_kvwrite_kernel(QkRopeArgs a) {
+    ce_pdl_begin();
     extern __shared__ float sh[];     // d floats + 32 scratch
     float* vals = sh;
     float* scratch = sh + a.d;
@@ -229,9 +233,9 @@ extern "C" int ce_qk_rope_kvwrite(void* qkv, void* k_pool, void* v_pool, int dty
     dim3 grid(T, nh + 2 * nkv);
     size_t smem = (d + 32) * sizeof(float);
     if (dtype == CE_F32)
-        qk_rope_kvwrite_kernel<float><<<grid, threads, smem, stream>>>(a);
+        ce_launch(qk_rope_kvwrite_kernel<float>, grid, threads, smem, stream, a);
     else if (dtype == CE_BF16)
-        qk_rope_kvwrite_kernel<__nv_bfloat16><<<grid, threads, smem, stream>>>(a);
+        ce_launch(qk_rope_kvwrite_kernel<__nv_bfloat16>, grid, threads, smem, stream, a);
     else
         return ce_fail(CE_ERR_ARG, "ce_qk_rope_kvwrite: unknown dtype %d", dtype);
     return ce_check_launch("ce_qk_rope_kvwrite");
@@ -242,6 +246,7 @@ extern "C" int ce_qk_rope_kvwrite(void* qkv, void* k_pool, void* v_pool, int dty
 // ---------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void add_residual_kernel(float* __restrict__ x, const T* __restrict__ delta, size_t n) {
+    ce_pdl_begin();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     size_t stride = (size_t)gridDim.x * blockDim.x;
     for (; i < n; i += stride) x[i] += CeType<T>::load(delta + i);
@@ -252,9 +257,9 @@ extern "C" int ce_add_residual(float* x, const void* delta, int dtype, long long
     if (!x || !delta) return ce_fail(CE_ERR_ARG, "ce_add_residual: null pointer");
     int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
     if (dtype == CE_F32)
-        add_residual_kernel<float><<<blocks, 256, 0, stream>>>(x, (const float*)delta, (size_t)n);
+        ce_launch(add_residual_kernel<float>, blocks, 256, 0, stream, x, (const float*)delta, (size_t)n);
     else if (dtype == CE_BF16)
-        add_residual_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(x, (const __nv_bfloat16*)delta, (size_t)n);
+        ce_launch(add_residual_kernel<__nv_bfloat16>, blocks, 256, 0, stream, x, (const __nv_bfloat16*)delta, (size_t)n);
     else
         return ce_fail(CE_ERR_ARG, "ce_add_residual: unknown dtype %d", dtype);
     return ce_check_launch("ce_add_residual");
@@ -266,6 +271,7 @@ extern "C" int ce_add_residual(float* x, const void* delta, int dtype, long long
 // ---------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t total) {
+    ce_pdl_begin();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     size_t stride = (size_t)gridDim.x * blockDim.x;
     for (; i < total; i += stride) {
@@ -282,9 +288,9 @@ extern "C" int ce_swiglu(const void* gu, void* out, int dtype, int T, int I, cud
     if (!gu || !out) return ce_fail(CE_ERR_ARG, "ce_swiglu: null pointer");
     int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
     if (dtype == CE_F32)
-        swiglu_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gu, (float*)out, I, total);
+        ce_launch(swiglu_kernel<float>, blocks, 256, 0, stream, (const float*)gu, (float*)out, I, total);
     else if (dtype == CE_BF16)
-        swiglu_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, I, total);
+        ce_launch(swiglu_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, I, total);
     else
         return ce_fail(CE_ERR_ARG, "ce_swiglu: unknown dtype %d", dtype);
     return ce_check_launch("ce_swiglu");
@@ -295,6 +301,7 @@ extern "C" int ce_swiglu(const void* gu, void* out, int dtype, int T, int I, cud
 // ---------------------------------------------------------------------------------------------
 __global__ void scatter_i32_kernel(int* __restrict__ dst, const int* __restrict__ idx, const int* __restrict__ val,
                                    int n, long long dst_len) {
+    ce_pdl_begin();
     int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n && idx[i] >= 0 && idx[i] < dst_len) dst[idx[i]] = val[i];
 }
@@ -302,6 +309,6 @@ __global__ void scatter_i32_kernel(int* __restrict__ dst, const int* __restrict_
 extern "C" int ce_scatter_i32(int* dst, const int* idx, const int* val, int n, long long dst_len, cudaStream_t stream) {
     if (n == 0) return CE_OK;
     if (!dst || !idx || !val) return ce_fail(CE_ERR_ARG, "ce_scatter_i32: null pointer");
-    scatter_i32_kernel<<<(n + 255) / 256, 256, 0, stream>>>(dst, idx, val, n, dst_len);
+    ce_launch(scatter_i32_kernel, (n + 255) / 256, 256, 0, stream, dst, idx, val, n, dst_len);
     return ce_check_launch("ce_scatter_i32");
 }

@@ -2,6 +2,7 @@
 #include "common.cuh"
 #include <stdarg.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 static thread_local char g_error[512] = "";
 
@@ -29,3 +30,14 @@ extern "C" int ce_build_arch() {
     return 0;
 #endif
 }
+
+// Programmatic dependent launch is on unless switched off (ce_set_pdl(0), or CE_PDL=0 in the environment).
+static int g_pdl = -1;
+bool ce_pdl_enabled() {
+    if (g_pdl < 0) {
+        const char* e = getenv("CE_PDL");
+        g_pdl = (e && e[0] == '0') ? 0 : 1;
+    }
+    return g_pdl != 0;
+}
+extern "C" void ce_set_pdl(int on) { g_pdl = on ? 1 : 0; }

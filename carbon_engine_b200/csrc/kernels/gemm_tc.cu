@@ -126,6 +126,10 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
     int kb1 = min(kb0 + a.kblocks_per_split, a.kblocks);
     int nkb = kb1 - kb0;
 
+    // Dependent launch: this grid may start while the kernel before it still runs.  Weights are
+    // written by no kernel, so their loads start at once; the tokens (and everything the epilogue
+    // reads or writes) wait until the grids before this one are complete.
+    ce_pdl_launch_dependents();
     if (threadIdx.x == 0) {
         for (int s = 0; s < stages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
         mbar_init(&acc_bar, 1);
@@ -146,9 +150,22 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
             // ---- producer: TMA loads of the weight tile(s) and the token tile, stage after stage
             int issued = 0;
             bool ok = true;
-            for (int i = 0; i < nkb && ok; ++i) {
+            int first = min(nkb, stages);
+            for (int i = 0; i < first; ++i) {            // weights of the first stages: before the wait
+                unsigned char* st = tiles + (size_t)i * STAGE_BYTES;
+                mbar_expect_tx(&full_bar[i], STAGE_BYTES);
+                int k = (kb0 + i) * BK;
+                tma_load_2d(st, &map_w, &full_bar[i], k, n0);
+                if (NACC == 2) tma_load_2d(st + W_BYTES, &map_w, &full_bar[i], k, a.N + n0);
+            }
+            ce_pdl_wait();
+            for (int i = 0; i < first; ++i) {            // their tokens: after it
+                tma_load_2d(tiles + (size_t)i * STAGE_BYTES + NACC * W_BYTES, &map_x, &full_bar[i], (kb0 + i) * BK, m0);
+                issued = i + 1;
+            }
+            for (int i = first; i < nkb && ok; ++i) {
                 int s = i % stages;
-                if (i >= stages) ok = mbar_wait(&empty_bar[s], ((i / stages) - 1) & 1);
+                ok = mbar_wait(&empty_bar[s], ((i / stages) - 1) & 1);
                 if (!ok) break;
                 unsigned char* st = tiles + (size_t)s * STAGE_BYTES;
                 mbar_expect_tx(&full_bar[s], STAGE_BYTES);
@@ -194,6 +211,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
         int row = quad * 32 + lane;                  // feature within the tile
         int n = n0 + row;
         int m_valid = min(BN, a.M - m0);
+        ce_pdl_wait();
         bool ok = nkb > 0 ? mbar_wait(&acc_bar, 0) : true;
         if (!ok) { atomicExch(a.status, 5); atomicExch(&s_abort, 1); }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -341,8 +359,8 @@ int get_map(const void* ptr, long long rows, long long cols, long long ld, int b
 template <int BN, int NACC>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, const TcArgs& a, dim3 grid, cudaStream_t stream) {
     constexpr size_t stage = NACC * BM * BK * 2 + BN * BK * 2;
-    // decode-sized tiles: two CTAs per SM; large tiles: one
-    size_t budget = BN <= 64 ? 100 * 1024 : 200 * 1024;
+    // more CTAs than SMs and small tiles: two CTAs per SM; otherwise one CTA with a deeper pipeline
+    size_t budget = (BN <= 64 && grid.x * grid.y * grid.z > 148) ? 100 * 1024 : 200 * 1024;
     int stages = (int)(budget / stage);
     if (stages > 8) stages = 8;
     if (stages < 2) stages = 2;
@@ -353,7 +371,7 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, const TcArgs& a, dim3 g
         if (e != cudaSuccess) return ce_fail(CE_ERR_CUDA, "ce_gemm_tc: %s", cudaGetErrorString(e));
         attr_set = true;
     }
-    gemm_tc_kernel<BN, NACC><<<grid, THREADS, smem, stream>>>(mw, mx, a, stages);
+    ce_launch(gemm_tc_kernel<BN, NACC>, grid, THREADS, smem, stream, mw, mx, a, stages);
     return ce_check_launch("ce_gemm_tc");
 }
 
@@ -366,7 +384,7 @@ extern "C" int ce_gemm_tc_splits(int M, int N, int K) {
     if (M > 256) return 1;
     int bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
     int tiles = (N + BM - 1) / BM;
-    int s = 296 / tiles;                       // two CTAs per SM keep enough loads in flight
+    int s = 148 / tiles;                       // about one CTA per SM, each with a deep pipeline
     if (s > kblocks / 4) s = kblocks / 4;      // at least four k-blocks per split
     int by_traffic = (int)(0.15 * K / (4.0 * bn));   // partial sums cost S * bn * 4 / K of the weight bytes
     if (s > by_traffic) s = by_traffic;

@@ -84,6 +84,7 @@ struct SampleRow {
 __global__ void __launch_bounds__(SMP_THREADS) sample_kernel(const float* __restrict__ logits, int V,
                                                             const SampleRow* __restrict__ params,
                                                             int* __restrict__ out) {
+    ce_pdl_begin();
     __shared__ float sv[32];
     __shared__ int si[32];
     __shared__ float scratch[32];
@@ -151,12 +152,13 @@ extern "C" int ce_sample(const float* logits, int rows, int V, const void* param
     if (rows == 0) return CE_OK;
     if (!logits || !params || !out) return ce_fail(CE_ERR_ARG, "ce_sample: null pointer");
     if (V <= 0 || V >= (1 << 24)) return ce_fail(CE_ERR_SIZE, "ce_sample: vocabulary %d not in 1..2^24", V);
-    sample_kernel<<<rows, SMP_THREADS, 0, stream>>>(logits, V, (const SampleRow*)params, out);
+    ce_launch(sample_kernel, rows, SMP_THREADS, 0, stream, logits, V, (const SampleRow*)params, out);
     return ce_check_launch("ce_sample");
 }
 
 // Greedy pick for all rows: the first maximum of each row.
 __global__ void __launch_bounds__(SMP_THREADS) argmax_kernel(const float* __restrict__ logits, int V, int* __restrict__ out) {
+    ce_pdl_begin();
     __shared__ float sv[32];
     __shared__ int si[32];
     int r = blockIdx.x;
@@ -185,7 +187,7 @@ extern "C" int ce_argmax(const float* logits, int rows, int V, int* out, cudaStr
     if (rows == 0) return CE_OK;
     if (!logits || !out) return ce_fail(CE_ERR_ARG, "ce_argmax: null pointer");
     if (V <= 0) return ce_fail(CE_ERR_SIZE, "ce_argmax: vocabulary %d", V);
-    argmax_kernel<<<rows, SMP_THREADS, 0, stream>>>(logits, V, out);
+    ce_launch(argmax_kernel, rows, SMP_THREADS, 0, stream, logits, V, out);
     return ce_check_launch("ce_argmax");
 }
 
@@ -195,6 +197,7 @@ extern "C" int ce_argmax(const float* logits, int rows, int V, int* out, cudaStr
 // entries: [n, 4] int32 = (row, token, seen flag, count in the output)
 __global__ void penalties_kernel(float* __restrict__ logits, int V, const int* __restrict__ entries, int n,
                                  const float* __restrict__ row_params /* [rows, 3] rep, presence, frequency */) {
+    ce_pdl_begin();
     int e = blockIdx.x * blockDim.x + threadIdx.x;
     if (e >= n) return;
     int row = entries[4 * e], tok = entries[4 * e + 1], seen = entries[4 * e + 2], cnt = entries[4 * e + 3];
@@ -211,6 +214,6 @@ extern "C" int ce_apply_penalties(float* logits, int V, const int* entries, int 
                                   cudaStream_t stream) {
     if (n == 0) return CE_OK;
     if (!logits || !entries || !row_params) return ce_fail(CE_ERR_ARG, "ce_apply_penalties: null pointer");
-    penalties_kernel<<<(n + 255) / 256, 256, 0, stream>>>(logits, V, entries, n, row_params);
+    ce_launch(penalties_kernel, (n + 255) / 256, 256, 0, stream, logits, V, entries, n, row_params);
     return ce_check_launch("ce_apply_penalties");
 }

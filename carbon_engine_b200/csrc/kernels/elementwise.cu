@@ -215,6 +215,83 @@ __global__ void qk_rope_kvwrite_kernel(QkRopeArgs a) {
     if (j < d) CeType<T>::store(dst + j, v);
 }
 
+// The same with one warp per head, for head sizes that are multiples of 64 with a full rotation:
+// lane l holds elements l, l+32, ...; the partner of element j in the rotation, j +- d/2, lies in
+// the same lane, so a head needs no shared memory and no block-wide barrier.  Four heads per block.
+template <typename T, int NE>      // NE = d / 32 elements per lane
+__global__ void __launch_bounds__(128) qk_rope_kvwrite_warp_kernel(QkRopeArgs a) {
+    ce_pdl_begin();
+    int lane = threadIdx.x & 31;
+    long long head_index = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+    int heads_per_token = a.nh + 2 * a.nkv;
+    if (head_index >= (long long)a.T * heads_per_token) return;
+    int t = (int)(head_index / heads_per_token), hh = (int)(head_index - (long long)t * heads_per_token);
+    int d = a.d;
+    bool is_q = hh < a.nh, is_k = !is_q && hh < a.nh + a.nkv;
+    if (!is_q && !a.write_kv) return;
+    T* src = (T*)a.qkv + (size_t)t * heads_per_token * d + (size_t)hh * d;
+    float v[NE];
+#pragma unroll
+    for (int i = 0; i < NE; ++i) v[i] = CeType<T>::load(src + lane + 32 * i);
+    int pos = a.positions[t];
+    T* dst = src;
+    if (!is_q) {
+        int slot = a.seq_slot[a.seq_of_token[t]];
+        int page = a.block_table[(size_t)slot * a.max_pages + pos / a.page_size];
+        if (page < 0 || page >= a.num_pages) {
+            if (lane == 0) atomicExch(a.status, 2);
+            return;
+        }
+        int kvh = is_k ? hh - a.nh : hh - a.nh - a.nkv;
+        T* pool = (T*)(is_k ? a.k_pool : a.v_pool);
+        dst = pool + (((size_t)page * a.nkv + kvh) * a.page_size + pos % a.page_size) * d;
+    }
+    if (is_q || is_k) {
+        const float* w = is_q ? a.q_weight : a.k_weight;
+        if (w) {
+            float ss = 0.f;
+#pragma unroll
+            for (int i = 0; i < NE; ++i) ss = fmaf(v[i], v[i], ss);
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            float inv = 1.0f / sqrtf(ss / (float)d + a.eps);
+#pragma unroll
+            for (int i = 0; i < NE; ++i) v[i] = v[i] * inv * w[lane + 32 * i];
+        }
+        if (a.cos_table) {
+            if (pos >= a.max_pos) {
+                if (lane == 0) atomicExch(a.status, 3);
+                return;
+            }
+            const float* c = a.cos_table + (size_t)pos * (d / 2);
+            const float* s = a.sin_table + (size_t)pos * (d / 2);
+#pragma unroll
+            for (int i = 0; i < NE / 2; ++i) {
+                int j = lane + 32 * i;                      // element j pairs with j + d/2 = this lane's element i + NE/2
+                float x1 = v[i], x2 = v[i + NE / 2];
+                v[i] = x1 * c[j] - x2 * s[j];
+                v[i + NE / 2] = x2 * c[j] + x1 * s[j];
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < NE; ++i) CeType<T>::store(dst + lane + 32 * i, v[i]);
+}
+
+template <typename T>
+static bool launch_rope_warp(const QkRopeArgs& a, cudaStream_t stream) {
+    long long heads = (long long)a.T * (a.nh + 2 * a.nkv);
+    if (a.d % 64 || a.d > 256 || (a.cos_table && a.rd != a.d) || (heads + 3) / 4 > 2147483647LL) return false;
+    unsigned blocks = (unsigned)((heads + 3) / 4);
+    switch (a.d / 32) {
+        case 2: ce_launch(qk_rope_kvwrite_warp_kernel<T, 2>, blocks, 128, 0, stream, a); return true;
+        case 4: ce_launch(qk_rope_kvwrite_warp_kernel<T, 4>, blocks, 128, 0, stream, a); return true;
+        case 6: ce_launch(qk_rope_kvwrite_warp_kernel<T, 6>, blocks, 128, 0, stream, a); return true;
+        case 8: ce_launch(qk_rope_kvwrite_warp_kernel<T, 8>, blocks, 128, 0, stream, a); return true;
+    }
+    return false;
+}
+
 extern "C" int ce_qk_rope_kvwrite(void* qkv, void* k_pool, void* v_pool, int dtype, const float* q_weight,
                                   const float* k_weight, const float* cos_table, const float* sin_table,
                                   const int* positions, const int* seq_of_token, const int* seq_slot,
@@ -232,11 +309,12 @@ extern "C" int ce_qk_rope_kvwrite(void* qkv, void* k_pool, void* v_pool, int dty
     int threads = (d + 31) / 32 * 32;
     dim3 grid(T, nh + 2 * nkv);
     size_t smem = (d + 32) * sizeof(float);
-    if (dtype == CE_F32)
-        ce_launch(qk_rope_kvwrite_kernel<float>, grid, threads, smem, stream, a);
-    else if (dtype == CE_BF16)
-        ce_launch(qk_rope_kvwrite_kernel<__nv_bfloat16>, grid, threads, smem, stream, a);
-    else
+    if (dtype == CE_F32) {
+        if (!launch_rope_warp<float>(a, stream)) ce_launch(qk_rope_kvwrite_kernel<float>, grid, threads, smem, stream, a);
+    } else if (dtype == CE_BF16) {
+        if (!launch_rope_warp<__nv_bfloat16>(a, stream))
+            ce_launch(qk_rope_kvwrite_kernel<__nv_bfloat16>, grid, threads, smem, stream, a);
+    } else
         return ce_fail(CE_ERR_ARG, "ce_qk_rope_kvwrite: unknown dtype %d", dtype);
     return ce_check_launch("ce_qk_rope_kvwrite");
 }

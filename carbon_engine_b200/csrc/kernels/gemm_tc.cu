@@ -301,6 +301,166 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
     }
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// Many tokens (prefill): a persistent kernel.  One CTA per SM walks over output tiles (tokens
+// fastest, so the CTAs that run together share weight tiles in L2); tensor memory holds two sets of
+// accumulators, so the epilogue of one tile runs while the MMAs of the next fill the other set.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+    uint32_t r[32];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+                 "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+template <int BN, int NACC>
+__global__ void __launch_bounds__(THREADS) gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w,
+                                                                    const __grid_constant__ CUtensorMap map_x, TcArgs a,
+                                                                    int stages, int tiles_n, int tiles_m) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    __shared__ __align__(8) uint64_t full_bar[8], empty_bar[8], acc_full[2], acc_empty[2];
+    __shared__ uint32_t tmem_slot;
+
+    constexpr uint32_t W_BYTES = BM * BK * 2, X_BYTES = BN * BK * 2;
+    constexpr uint32_t STAGE_BYTES = NACC * W_BYTES + X_BYTES;
+    constexpr uint32_t ACC_COLS = NACC * BN;
+    constexpr uint32_t TMEM_COLS = 2 * ACC_COLS;
+    static_assert(TMEM_COLS <= 512 && (TMEM_COLS & (TMEM_COLS - 1)) == 0, "two accumulator sets must fit tensor memory");
+    uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    unsigned char* tiles = smem_raw + (base - smem_u32(smem_raw));
+    int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    int total = tiles_n * tiles_m;
+
+    ce_pdl_launch_dependents();
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < stages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 1); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(TMEM_COLS));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    uint32_t tmem = tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            ce_pdl_wait();
+            int it = 0, first_in_flight = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x) {
+                int n0 = (tile / tiles_m) * BM, m0 = (tile % tiles_m) * BN;
+                for (int kb = 0; kb < a.kblocks; ++kb, ++it) {
+                    int s = it % stages;
+                    if (it >= stages) ok = mbar_wait(&empty_bar[s], ((it / stages) - 1) & 1);
+                    if (!ok) break;
+                    unsigned char* st = tiles + (size_t)s * STAGE_BYTES;
+                    mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+                    tma_load_2d(st, &map_w, &full_bar[s], kb * BK, n0);
+                    if (NACC == 2) tma_load_2d(st + W_BYTES, &map_w, &full_bar[s], kb * BK, a.N + n0);
+                    tma_load_2d(st + NACC * W_BYTES, &map_x, &full_bar[s], kb * BK, m0);
+                }
+            }
+            if (!ok) {
+                atomicExch(a.status, 5);
+                first_in_flight = max(0, it - stages);
+                for (int i = first_in_flight; i < it; ++i) mbar_wait(&full_bar[i % stages], (i / stages) & 1);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+            int it = 0, lt = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x, ++lt) {
+                int buf = lt & 1;
+                if (lt >= 2) ok = mbar_wait(&acc_empty[buf], ((lt >> 1) - 1) & 1);     // the epilogue has drained this set
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                uint32_t d_tmem = tmem + buf * ACC_COLS;
+                for (int kb = 0; kb < a.kblocks; ++kb, ++it) {
+                    int s = it % stages;
+                    ok = mbar_wait(&full_bar[s], (it / stages) & 1);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    uint32_t st = base + s * STAGE_BYTES;
+#pragma unroll
+                    for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+                        uint64_t bdesc = umma_desc(st + NACC * W_BYTES + kk * UMMA_K * 2);
+                        uint32_t acc = (kb > 0 || kk > 0) ? 1u : 0u;
+                        umma_bf16(d_tmem, umma_desc(st + kk * UMMA_K * 2), bdesc, idesc, acc);
+                        if (NACC == 2) umma_bf16(d_tmem + BN, umma_desc(st + W_BYTES + kk * UMMA_K * 2), bdesc, idesc, acc);
+                    }
+                    umma_commit(&empty_bar[s]);
+                }
+                if (ok) umma_commit(&acc_full[buf]);
+            }
+            if (!ok) atomicExch(a.status, 5);
+        }
+    } else {
+        int quad = warp & 3;
+        int row = quad * 32 + lane;
+        ce_pdl_wait();
+        int lt = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x, ++lt) {
+            int buf = lt & 1;
+            int n0 = (tile / tiles_m) * BM, m0 = (tile % tiles_m) * BN;
+            int n = n0 + row;
+            int m_valid = min(BN, a.M - m0);
+            ok = mbar_wait(&acc_full[buf], (lt >> 1) & 1);
+            if (!ok) { atomicExch(a.status, 5); break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            uint32_t taddr = tmem + buf * ACC_COLS + ((uint32_t)(quad * 32) << 16);
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 32) {
+                if (c >= m_valid) break;
+                float g[32], u[32];
+                tmem_ld32(taddr + c, g);
+                if (NACC == 2) tmem_ld32(taddr + BN + c, u);
+                if (n < a.N) {
+                    if (a.mode == TC_ACCUM_F32) {
+                        float* xp = (float*)a.out + (size_t)(m0 + c) * a.ldo + n;
+                        float xv[32];
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) xv[j] = (c + j < m_valid) ? xp[(size_t)j * a.ldo] : 0.f;   // all loads first
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (c + j < m_valid) xp[(size_t)j * a.ldo] = xv[j] + g[j];
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (c + j < m_valid) epilogue_store(a, m0 + c + j, n, g[j], NACC == 2 ? u[j] : 0.f);
+                    }
+                }
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (threadIdx.x == 64) mbar_arrive(&acc_empty[buf]);
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    }
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS));
+    }
+}
+
 // ---- host side ------------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                 const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -375,6 +535,34 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, const TcArgs& a, dim3 g
     return ce_check_launch("ce_gemm_tc");
 }
 
+int sm_count() {
+    static int n = 0;
+    if (n == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    }
+    return n;
+}
+
+template <int BN, int NACC>
+int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, const TcArgs& a, int tiles_n, int tiles_m, cudaStream_t stream) {
+    constexpr size_t stage = NACC * BM * BK * 2 + BN * BK * 2;
+    int stages = (int)((200 * 1024) / stage);
+    if (stages > 8) stages = 8;
+    size_t smem = stages * stage + 1024;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_persistent_kernel<BN, NACC>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 2048);
+        if (e != cudaSuccess) return ce_fail(CE_ERR_CUDA, "ce_gemm_tc: %s", cudaGetErrorString(e));
+        attr_set = true;
+    }
+    long long total = (long long)tiles_n * tiles_m;
+    int grid = (int)(total < sm_count() ? total : sm_count());
+    ce_launch(gemm_tc_persistent_kernel<BN, NACC>, grid, THREADS, smem, stream, mw, mx, a, stages, tiles_n, tiles_m);
+    return ce_check_launch("ce_gemm_tc (persistent)");
+}
+
 }  // namespace
 
 // How many splits of K a product of these sizes uses (it depends on N and K only while the tokens
@@ -421,9 +609,21 @@ extern "C" int ce_gemm_tc(const void* A, const void* W, void* C, int M, int N, i
     if (((uintptr_t)A | (uintptr_t)W) & 15) return ce_fail(CE_ERR_SIZE, "ce_gemm_tc: operands must be 16-byte aligned");
     if (mode < 0 || mode > 3) return ce_fail(CE_ERR_ARG, "ce_gemm_tc: unknown epilogue %d", mode);
     int nacc = mode == TC_SWIGLU ? 2 : 1;
+    int kblocks = (K + BK - 1) / BK;
+    if (M > 256) {       // many tokens: the persistent kernel, no split-K
+        int pbn = nacc == 2 ? 128 : 256;
+        long long tiles_m = (M + pbn - 1) / pbn, tiles_n = (N + BM - 1) / BM;
+        if (tiles_m * tiles_n > 2147483647LL) return ce_fail(CE_ERR_SIZE, "ce_gemm_tc: too many tiles");
+        CUtensorMap pw, px;
+        int prc = get_map(W, (long long)N * nacc, K, K, BM, &pw);
+        if (prc) return prc;
+        if ((prc = get_map(A, M, K, lda, pbn, &px))) return prc;
+        TcArgs pa{C, scratch, counters, status, M, N, K, ldc, mode, 1, kblocks, kblocks};
+        return nacc == 2 ? launch_persistent<128, 2>(pw, px, pa, (int)tiles_n, (int)tiles_m, stream)
+                         : launch_persistent<256, 1>(pw, px, pa, (int)tiles_n, (int)tiles_m, stream);
+    }
     int bn = ce_gemm_tc_tile_tokens(M);
     int splits = ce_gemm_tc_splits(M, N, K);
-    int kblocks = (K + BK - 1) / BK;
     dim3 grid((N + BM - 1) / BM, (M + bn - 1) / bn, splits);
     if (grid.y > 65535) return ce_fail(CE_ERR_SIZE, "ce_gemm_tc: M=%d is too large", M);
     if (splits > 1) {

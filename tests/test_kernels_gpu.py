@@ -97,7 +97,8 @@ def step_meta(seqs):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("nh,nkv,d,rd,ps", [(6, 3, 48, 48, 8), (4, 1, 16, 16, 16), (5, 5, 80, 32, 4), (2, 2, 256, 256, 64)])
+@pytest.mark.parametrize("nh,nkv,d,rd,ps", [(6, 3, 48, 48, 8), (4, 1, 16, 16, 16), (5, 5, 80, 32, 4), (2, 2, 256, 256, 64),
+                                            (8, 2, 128, 128, 64), (3, 1, 64, 64, 16), (4, 2, 192, 192, 8), (2, 1, 128, 64, 16)])
 def test_qk_norm_rope_and_cache_write(ops, dtype, nh, nkv, d, rd, ps):
     torch.manual_seed(1)
     seqs = [(5, 9), (0, 3), (30, 1)]
@@ -488,7 +489,8 @@ def tc_product(a, w, mode, N, x0=None):
 
 
 @pytest.mark.parametrize("M,N,K", [(1, 128, 64), (8, 256, 4096), (16, 96, 80), (17, 301, 136), (64, 4096, 512), (100, 200, 1000),
-                                   (256, 384, 256), (300, 520, 192), (5, 1000, 2048), (2048, 512, 256)])
+                                   (256, 384, 256), (300, 520, 192), (5, 1000, 2048), (2048, 512, 256), (1000, 5120, 128),
+                                   (257, 19000, 64)])
 def test_tcgen05_product_all_epilogues(ops, M, N, K):
     torch.manual_seed(M * 7 + N)
     a = torch.randn(M, K, device=dev()).to(torch.bfloat16)

@@ -103,36 +103,48 @@ __device__ __forceinline__ void stage_tile(bf16* Ks, bf16* Vs, const MmaAttnArgs
 
 // One warp: scores of its 16 rows against NK8*8 staged keys, online softmax, output update.
 // lo/hi: first and last visible key of rows (lane/4) and (lane/4 + 8).
-template <int DMAX, int NK8>
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const bf16* p) {
+    uint32_t addr = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+
+// MASK false: every staged key of the tile is visible to every row of the warp (no compares).
+template <int DMAX, int NK8, bool MASK>
 __device__ __forceinline__ void warp_tile(const uint32_t (&qf)[DMAX / 16][4], float (&o)[DMAX / 8][4], float (&m)[2],
                                           float (&l)[2], const bf16* Ks, const bf16* Vs, int ld, int d, int key_base,
                                           const int (&lo)[2], const int (&hi)[2], float scale_log2) {
-    int lane = threadIdx.x & 31, quad = lane & 3, grp = lane >> 2;
+    int lane = threadIdx.x & 31, quad = lane & 3;
+    int mi = lane >> 3, rr = lane & 7;
     float s[NK8][4];
 #pragma unroll
     for (int j = 0; j < NK8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+    // K fragments: one ldmatrix.x4 brings the B operands of two key tiles for one step of 16 along d
+    const bf16* krow = Ks + ((mi >> 1) * 8 + rr) * ld + (mi & 1) * 8;
 #pragma unroll
     for (int kk = 0; kk < DMAX / 16; ++kk) {
         if (kk * 16 < d) {
 #pragma unroll
-            for (int j = 0; j < NK8; ++j) {
-                const bf16* kp = Ks + (j * 8 + grp) * ld + kk * 16 + 2 * quad;
-                uint32_t b0 = *reinterpret_cast<const uint32_t*>(kp);
-                uint32_t b1 = *reinterpret_cast<const uint32_t*>(kp + 8);
-                mma16816(s[j], qf[kk], b0, b1);
+            for (int j = 0; j < NK8; j += 2) {
+                uint32_t kb[4];
+                ldmatrix_x4(kb, krow + j * 8 * ld + kk * 16);
+                mma16816(s[j], qf[kk], kb[0], kb[1]);
+                mma16816(s[j + 1], qf[kk], kb[2], kb[3]);
             }
         }
     }
+    // raw maxima; the scale (positive) is applied inside the exponent: p = 2^(s * scale - m)
     float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
     for (int j = 0; j < NK8; ++j) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-            int r = e >> 1;
-            int key = key_base + j * 8 + 2 * quad + (e & 1);
-            float v = (key >= lo[r] && key <= hi[r]) ? s[j][e] * scale_log2 : -INFINITY;
-            s[j][e] = v;
-            mx[r] = fmaxf(mx[r], v);
+            if (MASK) {
+                int r = e >> 1;
+                int key = key_base + j * 8 + 2 * quad + (e & 1);
+                if (!(key >= lo[r] && key <= hi[r])) s[j][e] = -INFINITY;
+            }
+            mx[e >> 1] = fmaxf(mx[e >> 1], s[j][e]);
         }
     }
     float alpha[2], muse[2];
@@ -140,7 +152,7 @@ __device__ __forceinline__ void warp_tile(const uint32_t (&qf)[DMAX / 16][4], fl
     for (int r = 0; r < 2; ++r) {
         mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
         mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
-        float mn = fmaxf(m[r], mx[r]);
+        float mn = fmaxf(m[r], mx[r] * scale_log2);
         muse[r] = mn == -INFINITY ? 0.f : mn;
         alpha[r] = exp2f(m[r] - muse[r]);
         m[r] = mn;
@@ -150,7 +162,7 @@ __device__ __forceinline__ void warp_tile(const uint32_t (&qf)[DMAX / 16][4], fl
     for (int j = 0; j < NK8; ++j) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-            float p = exp2f(s[j][e] - muse[e >> 1]);
+            float p = exp2f(fmaf(s[j][e], scale_log2, -muse[e >> 1]));
             s[j][e] = p;
             l[e >> 1] += p;
         }
@@ -163,7 +175,6 @@ __device__ __forceinline__ void warp_tile(const uint32_t (&qf)[DMAX / 16][4], fl
     for (int c = 0; c < NK8 / 2; ++c) {
         uint32_t pa[4] = {pack_bf16(s[2 * c][0], s[2 * c][1]), pack_bf16(s[2 * c][2], s[2 * c][3]),
                           pack_bf16(s[2 * c + 1][0], s[2 * c + 1][1]), pack_bf16(s[2 * c + 1][2], s[2 * c + 1][3])};
-        int mi = lane >> 3, rr = lane & 7;
         const bf16* vrow = Vs + (c * 16 + (mi & 1) * 8 + rr) * ld + (mi >> 1) * 8;
 #pragma unroll
         for (int dn = 0; dn < DMAX / 8; dn += 2) {
@@ -238,9 +249,12 @@ __global__ void __launch_bounds__(AM_THREADS) attention_decode_kernel(MmaAttnArg
         cp_async_commit();
         int cur = it % AM_STAGES;
         int k0 = k_begin + it * AM_TILE + warp * 16;
-        if (k0 <= pos)
-            warp_tile<DMAX, 2>(qf, o, m, l, Ks + (cur * AM_TILE + warp * 16) * ld, Vs + (cur * AM_TILE + warp * 16) * ld,
-                               ld, d, k0, los, his, a.scale_log2);
+        if (k0 <= pos) {
+            const bf16* kt = Ks + (cur * AM_TILE + warp * 16) * ld;
+            const bf16* vt = Vs + (cur * AM_TILE + warp * 16) * ld;
+            if (k0 >= lo && k0 + 15 <= pos) warp_tile<DMAX, 2, false>(qf, o, m, l, kt, vt, ld, d, k0, los, his, a.scale_log2);
+            else warp_tile<DMAX, 2, true>(qf, o, m, l, kt, vt, ld, d, k0, los, his, a.scale_log2);
+        }
     }
     cp_async_wait<0>();
     __syncthreads();
@@ -371,6 +385,9 @@ __global__ void __launch_bounds__(AM_THREADS) attention_prefill_kernel(MmaAttnAr
     int los[2] = {a.window > 0 ? max(0, his[0] - a.window + 1) : 0, a.window > 0 ? max(0, his[1] - a.window + 1) : 0};
     int warp_hi = p_first + min(warp * 16 + 15, nq - 1);     // last key any row of this warp sees
     int warp_lo = a.window > 0 ? max(0, p_first + warp * 16 - a.window + 1) : 0;
+    bool warp_rows_full = warp * 16 + 15 < nq;                // all 16 rows of the warp are real queries
+    int warp_first_hi = p_first + warp * 16;                  // the warp's first row sees keys up to here
+    int warp_last_lo = a.window > 0 ? max(0, p_first + warp * 16 + 15 - a.window + 1) : 0;
 
     int k_begin = lo_tile / AM_TILE * AM_TILE;
     int n_tiles = (p_last - k_begin) / AM_TILE + 1;
@@ -391,9 +408,15 @@ __global__ void __launch_bounds__(AM_THREADS) attention_prefill_kernel(MmaAttnAr
         cp_async_commit();
         int cur = it % AM_STAGES;
         int k0 = k_begin + it * AM_TILE;
-        if (warp * 16 < nq && k0 <= warp_hi && k0 + AM_TILE > warp_lo)
-            warp_tile<DMAX, 8>(qf, o, m, l, Ks + cur * AM_TILE * ld, Vs + cur * AM_TILE * ld, ld, d, k0, los, his,
-                               a.scale_log2);
+        if (warp * 16 < nq && k0 <= warp_hi && k0 + AM_TILE > warp_lo) {
+            const bf16* kt = Ks + cur * AM_TILE * ld;
+            const bf16* vt = Vs + cur * AM_TILE * ld;
+            // all 64 keys visible to all 16 rows of the warp: at or below its first row, at or above its last row's window
+            if (warp_rows_full && k0 + AM_TILE - 1 <= warp_first_hi && k0 >= warp_last_lo)
+                warp_tile<DMAX, 8, false>(qf, o, m, l, kt, vt, ld, d, k0, los, his, a.scale_log2);
+            else
+                warp_tile<DMAX, 8, true>(qf, o, m, l, kt, vt, ld, d, k0, los, his, a.scale_log2);
+        }
     }
     cp_async_wait<0>();
 #pragma unroll

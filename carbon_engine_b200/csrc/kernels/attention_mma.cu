@@ -2,7 +2,7 @@
 // accumulators): a split-KV kernel for sequences that bring one token, and a flash kernel for
 // sequences that bring a portion of a prompt.  Both read keys and values through the block table.
 //
-// Decode: one block per (sequence, KV head, group of up to 16 query heads, split of 512 positions).
+// Decode: one block per (sequence, KV head, group of up to 16 query heads, split of 256 positions).
 // The query heads that share the KV head are the 16 rows of the MMA tile, so K and V are read once
 // per KV head (the reference's paged_decode_tc does the same for up to 8 heads,
 // src/kernels/attention_tc.cu:682-807).  Each of the 4 warps takes 16 of every 64 staged keys and
@@ -21,8 +21,9 @@
 
 #define AM_THREADS 128
 #define AM_TILE 64           // keys staged per iteration
-#define AM_SPLIT 512         // positions per decode split
-#define AM_STAGES 3          // staged tiles in flight: loads of tiles i+1, i+2 run while tile i is computed
+#define AM_SPLIT 256         // positions per decode split
+#define AM_STAGES 3          // decode: staged tiles in flight: loads of tiles i+1, i+2 run while tile i is computed
+#define AM_PF_STAGES 2       // prefill: two stages, so that three blocks fit one SM
 #define AM_PAD 8             // padding of a staged row, in elements (keeps 32-bit and ldmatrix reads conflict-free)
 
 typedef __nv_bfloat16 bf16;
@@ -64,7 +65,7 @@ struct MmaAttnArgs {
     const int* tiles;           // prefill: [n_tiles, 2] = (sequence, first new token of the tile)
     int* counters;              // decode: one per (sequence, KV head, head group), zero between launches
     int* status;
-    int nh, nkv, d, q_stride, page_size, max_pages, num_pages, window, max_splits, first_seq;
+    int nh, nkv, d, q_stride, page_size, max_pages, num_pages, window, max_splits, split;
     float scale_log2;           // scale * log2(e)
 };
 
@@ -121,15 +122,32 @@ __device__ __forceinline__ void warp_tile(const uint32_t (&qf)[DMAX / 16][4], fl
     for (int j = 0; j < NK8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
     // K fragments: one ldmatrix.x4 brings the B operands of two key tiles for one step of 16 along d
     const bf16* krow = Ks + ((mi >> 1) * 8 + rr) * ld + (mi & 1) * 8;
+    if (NK8 == 2) {
+        // few key tiles: odd steps along d go to a second pair of accumulators, which halves the
+        // chain of MMAs that wait for one another
+        float s2[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
-    for (int kk = 0; kk < DMAX / 16; ++kk) {
-        if (kk * 16 < d) {
-#pragma unroll
-            for (int j = 0; j < NK8; j += 2) {
+        for (int kk = 0; kk < DMAX / 16; ++kk) {
+            if (kk * 16 < d) {
                 uint32_t kb[4];
-                ldmatrix_x4(kb, krow + j * 8 * ld + kk * 16);
-                mma16816(s[j], qf[kk], kb[0], kb[1]);
-                mma16816(s[j + 1], qf[kk], kb[2], kb[3]);
+                ldmatrix_x4(kb, krow + kk * 16);
+                if (kk & 1) { mma16816(s2[0], qf[kk], kb[0], kb[1]); mma16816(s2[1], qf[kk], kb[2], kb[3]); }
+                else { mma16816(s[0], qf[kk], kb[0], kb[1]); mma16816(s[1], qf[kk], kb[2], kb[3]); }
+            }
+        }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { s[0][e] += s2[0][e]; s[1][e] += s2[1][e]; }
+    } else {
+#pragma unroll
+        for (int kk = 0; kk < DMAX / 16; ++kk) {
+            if (kk * 16 < d) {
+#pragma unroll
+                for (int j = 0; j < NK8; j += 2) {
+                    uint32_t kb[4];
+                    ldmatrix_x4(kb, krow + j * 8 * ld + kk * 16);
+                    mma16816(s[j], qf[kk], kb[0], kb[1]);
+                    mma16816(s[j + 1], qf[kk], kb[2], kb[3]);
+                }
             }
         }
     }
@@ -201,7 +219,7 @@ __global__ void __launch_bounds__(AM_THREADS) attention_decode_kernel(MmaAttnArg
     int t = b;                                    // one-token sequences come first: sequence b brings token b
     int pos = a.positions[t];
     int lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
-    int k_begin = split * AM_SPLIT, k_end = min(k_begin + AM_SPLIT, pos + 1);
+    int k_begin = split * a.split, k_end = min(k_begin + a.split, pos + 1);
     if (k_begin > pos || k_end <= lo) return;     // the merge kernel skips these splits too
     const int* table = a.block_table + (size_t)a.seq_slot[b] * a.max_pages;
     int d = a.d, ld = d + AM_PAD;
@@ -312,7 +330,7 @@ __global__ void attention_merge_kernel(MmaAttnArgs a) {
     int t = a.q_start[b];
     int pos = a.positions[t];
     int lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
-    int s0 = lo / AM_SPLIT, s1 = pos / AM_SPLIT;                // splits that hold visible keys
+    int s0 = lo / a.split, s1 = pos / a.split;                  // splits that hold visible keys
     int ns = s1 - s0 + 1;
     size_t base = ((size_t)b * a.nh + h) * a.max_splits + s0;
     if (threadIdx.x < 32) {
@@ -345,7 +363,7 @@ __global__ void attention_merge_kernel(MmaAttnArgs a) {
 // Prefill: grid (n_tiles, nh)
 // ---------------------------------------------------------------------------------------------
 template <int DMAX>
-__global__ void __launch_bounds__(AM_THREADS) attention_prefill_kernel(MmaAttnArgs a) {
+__global__ void __launch_bounds__(AM_THREADS, DMAX <= 128 ? 3 : 1) attention_prefill_kernel(MmaAttnArgs a) {
     ce_pdl_begin();
     extern __shared__ __align__(16) unsigned char smem_raw[];
     int b = a.tiles[2 * blockIdx.x], q0 = a.tiles[2 * blockIdx.x + 1];
@@ -358,7 +376,7 @@ __global__ void __launch_bounds__(AM_THREADS) attention_prefill_kernel(MmaAttnAr
     const int* table = a.block_table + (size_t)a.seq_slot[b] * a.max_pages;
     int d = a.d, ld = d + AM_PAD;
     bf16* Ks = reinterpret_cast<bf16*>(smem_raw);
-    bf16* Vs = Ks + AM_STAGES * AM_TILE * ld;
+    bf16* Vs = Ks + AM_PF_STAGES * AM_TILE * ld;
 
     int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, quad = lane & 3, grp = lane >> 2;
     int r0 = warp * 16 + grp, r1 = r0 + 8;                   // this thread's two query rows within the tile
@@ -392,21 +410,21 @@ __global__ void __launch_bounds__(AM_THREADS) attention_prefill_kernel(MmaAttnAr
     int k_begin = lo_tile / AM_TILE * AM_TILE;
     int n_tiles = (p_last - k_begin) / AM_TILE + 1;
 #pragma unroll
-    for (int p = 0; p < AM_STAGES - 1; ++p) {
+    for (int p = 0; p < AM_PF_STAGES - 1; ++p) {
         if (p < n_tiles)
             stage_tile(Ks + p * AM_TILE * ld, Vs + p * AM_TILE * ld, a, table, kvh, k_begin + p * AM_TILE, lo_tile, p_last);
         cp_async_commit();
     }
     for (int it = 0; it < n_tiles; ++it) {
-        cp_async_wait<AM_STAGES - 2>();
+        cp_async_wait<AM_PF_STAGES - 2>();
         __syncthreads();
-        int nxt = it + AM_STAGES - 1;
+        int nxt = it + AM_PF_STAGES - 1;
         if (nxt < n_tiles) {
-            int st = nxt % AM_STAGES;
+            int st = nxt % AM_PF_STAGES;
             stage_tile(Ks + st * AM_TILE * ld, Vs + st * AM_TILE * ld, a, table, kvh, k_begin + nxt * AM_TILE, lo_tile, p_last);
         }
         cp_async_commit();
-        int cur = it % AM_STAGES;
+        int cur = it % AM_PF_STAGES;
         int k0 = k_begin + it * AM_TILE;
         if (warp * 16 < nq && k0 <= warp_hi && k0 + AM_TILE > warp_lo) {
             const bf16* kt = Ks + cur * AM_TILE * ld;
@@ -437,7 +455,7 @@ __global__ void __launch_bounds__(AM_THREADS) attention_prefill_kernel(MmaAttnAr
     }
 }
 
-static size_t stage_bytes(int d) { return (size_t)AM_STAGES * 2 * AM_TILE * (d + AM_PAD) * sizeof(bf16); }
+static size_t stage_bytes(int d, int stages = AM_STAGES) { return (size_t)stages * 2 * AM_TILE * (d + AM_PAD) * sizeof(bf16); }
 
 static int check_common(const char* who, int nh, int nkv, int d, int q_stride) {
     if (d < 16 || d > 256 || d % 16) return ce_fail(CE_ERR_SIZE, "%s: head_dim %d must be a multiple of 16 in 16..256", who, d);
@@ -480,9 +498,19 @@ extern "C" int ce_attention_decode_bf16(const void* q, const void* k_pool, const
     a.part_o = scratch; a.part_ml = scratch + (size_t)n_seqs * nh * max_splits * d;
     a.positions = positions; a.seq_slot = seq_slot; a.q_start = q_start; a.ctx_len = ctx_len; a.block_table = block_table;
     a.status = status; a.nh = nh; a.nkv = nkv; a.d = d; a.q_stride = q_stride; a.page_size = page_size;
-    a.max_pages = max_pages; a.num_pages = num_pages; a.window = window; a.max_splits = max_splits;
+    a.max_pages = max_pages; a.num_pages = num_pages; a.window = window;
     a.scale_log2 = scale * 1.4426950408889634f;
     int G = nh / nkv;
+    // Splits of AM_SPLIT positions; when that makes more than about four waves of blocks, splits of
+    // twice the size (fewer blocks, fewer partial results: measured faster at large batches).  The
+    // choice depends on the number of one-token sequences and on max_splits, not on their contents.
+    a.split = AM_SPLIT;
+    a.max_splits = max_splits;
+    if ((long long)n_seqs * nkv * ((G + 15) / 16) * max_splits > 1200 && max_splits > 1) {
+        a.split = 2 * AM_SPLIT;
+        a.max_splits = (max_splits + 1) / 2;
+    }
+    max_splits = a.max_splits;
     dim3 grid(n_seqs * max_splits, nkv, (G + 15) / 16);
     if ((long long)n_seqs * nkv * grid.z > n_counters)
         return ce_fail(CE_ERR_ARG, "ce_attention_decode_bf16: %lld counters needed, %d given", (long long)n_seqs * nkv * grid.z, n_counters);
@@ -525,7 +553,7 @@ extern "C" int ce_attention_prefill_bf16(const void* q, const void* k_pool, cons
     a.max_pages = max_pages; a.num_pages = num_pages; a.window = window;
     a.scale_log2 = scale * 1.4426950408889634f;
     dim3 grid(n_tiles, nh);
-    size_t smem = stage_bytes(d);
+    size_t smem = stage_bytes(d, AM_PF_STAGES);
     if (d <= 64) {
         if ((rc = set_smem(attention_prefill_kernel<64>, smem, "ce_attention_prefill_bf16"))) return rc;
         ce_launch(attention_prefill_kernel<64>, grid, AM_THREADS, smem, stream, a);

@@ -21,6 +21,7 @@
 #include "common.cuh"
 #include <cuda.h>
 #include <mutex>
+#include <stdlib.h>
 #include <unordered_map>
 
 namespace {
@@ -519,8 +520,11 @@ int get_map(const void* ptr, long long rows, long long cols, long long ld, int b
 template <int BN, int NACC>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, const TcArgs& a, dim3 grid, cudaStream_t stream) {
     constexpr size_t stage = NACC * BM * BK * 2 + BN * BK * 2;
-    // more CTAs than SMs and small tiles: two CTAs per SM; otherwise one CTA with a deeper pipeline
-    size_t budget = (BN <= 64 && grid.x * grid.y * grid.z > 148) ? 100 * 1024 : 200 * 1024;
+    // small tiles: at most half an SM's shared memory, so that the blocks of the next kernel (launched
+    // as a programmatic dependent) fit beside these and stream their weights while these finish
+    // (measured: best for up to 16 tokens; from 32 tokens on one block per SM with a deeper pipeline wins)
+    static int small_kb = getenv("CE_GEMM_SMEM_KB") ? atoi(getenv("CE_GEMM_SMEM_KB")) : 0;
+    size_t budget = small_kb ? (size_t)small_kb * 1024 : (BN <= 16 ? 100 * 1024 : 200 * 1024);
     int stages = (int)(budget / stage);
     if (stages > 8) stages = 8;
     if (stages < 2) stages = 2;
@@ -572,7 +576,9 @@ extern "C" int ce_gemm_tc_splits(int M, int N, int K) {
     if (M > 256) return 1;
     int bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
     int tiles = (N + BM - 1) / BM;
-    int s = 148 / tiles;                       // about one CTA per SM, each with a deep pipeline
+    static int target = getenv("CE_GEMM_TARGET_CTAS") ? atoi(getenv("CE_GEMM_TARGET_CTAS")) : 0;
+    // up to 16 tokens: about two CTAs per SM, each with half an SM of shared memory; more tokens: one per SM
+    int s = (target ? target : (bn <= 16 ? 296 : 148)) / tiles;
     if (s > kblocks / 4) s = kblocks / 4;      // at least four k-blocks per split
     int by_traffic = (int)(0.15 * K / (4.0 * bn));   // partial sums cost S * bn * 4 / K of the weight bytes
     if (s > by_traffic) s = by_traffic;

@@ -18,6 +18,7 @@
 // Scores are scaled in float32, the softmax runs in float32 with exp2, probabilities are rounded to
 // bfloat16 for the PV product (as in src/kernels/attention_tc.cu:505-515), outputs are rounded once.
 #include "common.cuh"
+#include <stdlib.h>
 
 #define AM_THREADS 128
 #define AM_TILE 64           // keys staged per iteration
@@ -65,7 +66,7 @@ struct MmaAttnArgs {
     const int* tiles;           // prefill: [n_tiles, 2] = (sequence, first new token of the tile)
     int* counters;              // decode: one per (sequence, KV head, head group), zero between launches
     int* status;
-    int nh, nkv, d, q_stride, page_size, max_pages, num_pages, window, max_splits, split;
+    int nh, nkv, d, q_stride, page_size, max_pages, num_pages, window, max_splits, split, fused_merge;
     float scale_log2;           // scale * log2(e)
 };
 
@@ -318,6 +319,47 @@ __global__ void __launch_bounds__(AM_THREADS) attention_decode_kernel(MmaAttnArg
             a.part_ml[base * 2 + 1] = L;
         }
     }
+    if (!a.fused_merge) return;
+    // The block that arrives last for this (sequence, KV head, head group) merges the splits.  The
+    // result does not depend on which block that is: weights and sums are taken in split order.
+    __shared__ int s_ticket;
+    __threadfence();
+    __syncthreads();
+    int s0 = lo / a.split, s1 = pos / a.split, ns = s1 - s0 + 1;       // the splits that hold visible keys
+    int cidx = (b * a.nkv + kvh) * gridDim.z + hg;
+    if (threadIdx.x == 0) s_ticket = atomicAdd(&a.counters[cidx], 1);
+    __syncthreads();
+    if (s_ticket != ns - 1) return;
+    __threadfence();
+    float* wts = reinterpret_cast<float*>(smem_raw);                  // [heads_here][ns]: the staging buffers are free
+    for (int r = warp; r < heads_here; r += 4) {                       // one warp per head: lanes over splits
+        size_t base = ((size_t)b * a.nh + kvh * G + hg * 16 + r) * a.max_splits + s0;
+        float M = -INFINITY;
+        for (int s = lane; s < ns; s += 32) M = fmaxf(M, __ldcg(&a.part_ml[(base + s) * 2]));
+        for (int o2 = 16; o2 > 0; o2 >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o2));
+        float L = 0.f;
+        for (int s = lane; s < ns; s += 32) {
+            float ms = __ldcg(&a.part_ml[(base + s) * 2]);
+            float f = ms == -INFINITY ? 0.f : exp2f(ms - M);
+            wts[r * ns + s] = f;
+            L += __ldcg(&a.part_ml[(base + s) * 2 + 1]) * f;
+        }
+        for (int o2 = 16; o2 > 0; o2 >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o2);
+        float inv = L > 0.f ? 1.0f / L : 0.f;
+        __syncwarp();
+        for (int s = lane; s < ns; s += 32) wts[r * ns + s] *= inv;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < heads_here * d; e += AM_THREADS) {
+        int r = e / d, col = e - r * d;
+        int h = kvh * G + hg * 16 + r;
+        const float* po = a.part_o + (((size_t)b * a.nh + h) * a.max_splits + s0) * d + col;
+        float acc = 0.f;
+#pragma unroll 8
+        for (int s = 0; s < ns; ++s) acc = fmaf(__ldcg(po + (size_t)s * d), wts[r * ns + s], acc);
+        a.out[((size_t)t * a.nh + h) * d + col] = __float2bfloat16_rn(acc);
+    }
+    if (threadIdx.x == 0) a.counters[cidx] = 0;                        // ready for the next launch
 }
 
 // grid (n_seqs, nh), one warp per 32 output columns: out[t, h, :] = sum_s O_s w_s with
@@ -480,6 +522,8 @@ extern "C" long long ce_attention_decode_scratch(int n_seqs, int nh, int d, int 
 // The first n_seqs sequences of the step bring one token each (tokens 0 .. n_seqs-1).
 // max_splits >= ceil(longest context / AM_SPLIT); it fixes the grid, not the result.
 extern "C" int ce_attention_decode_split() { return AM_SPLIT; }
+// Kernels one decode attention call launches: 1 when the last block merges the splits, else 2.
+extern "C" int ce_attention_decode_kernels() { return getenv("CE_ATTN_FUSED_MERGE") ? 1 : 2; }
 
 extern "C" int ce_attention_decode_bf16(const void* q, const void* k_pool, const void* v_pool, void* out, float* scratch,
                                         int* counters, int n_counters, const int* positions, const int* seq_slot, const int* q_start,
@@ -511,6 +555,10 @@ extern "C" int ce_attention_decode_bf16(const void* q, const void* k_pool, const
         a.max_splits = (max_splits + 1) / 2;
     }
     max_splits = a.max_splits;
+    // A merge kernel combines the splits.  CE_ATTN_FUSED_MERGE=1 lets the last block of a (sequence,
+    // KV head) do it instead; measured slower (4.9 -> 5.0 ms a step at batch 8, 8B sizes), so it is off.
+    static int fused = getenv("CE_ATTN_FUSED_MERGE") ? 1 : 0;
+    a.fused_merge = fused && (size_t)16 * max_splits * sizeof(float) <= 16 * 1024;
     dim3 grid(n_seqs * max_splits, nkv, (G + 15) / 16);
     if ((long long)n_seqs * nkv * grid.z > n_counters)
         return ce_fail(CE_ERR_ARG, "ce_attention_decode_bf16: %lld counters needed, %d given", (long long)n_seqs * nkv * grid.z, n_counters);
@@ -529,6 +577,7 @@ extern "C" int ce_attention_decode_bf16(const void* q, const void* k_pool, const
         ce_launch(attention_decode_kernel<256>, grid, AM_THREADS, smem, stream, a);
     }
     if ((rc = ce_check_launch("ce_attention_decode_bf16"))) return rc;
+    if (a.fused_merge) return CE_OK;
     ce_launch(attention_merge_kernel, dim3(n_seqs, nh), d >= 128 ? 128 : (d + 31) / 32 * 32, max_splits * sizeof(float), stream, a);
     return ce_check_launch("ce_attention_decode_bf16 (merge)");
 }

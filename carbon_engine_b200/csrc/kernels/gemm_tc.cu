@@ -226,9 +226,19 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
                     tmem_ld16(taddr + c, g);
                     if (NACC == 2) tmem_ld16(taddr + BN + c, u);
                     if (n < a.N) {
+                        if (a.mode == TC_ACCUM_F32) {
+                            float* xp = (float*)a.out + (size_t)(m0 + c) * a.ldo + n;
+                            float xv[16];
 #pragma unroll
-                        for (int j = 0; j < 16; ++j)
-                            if (c + j < m_valid) epilogue_store(a, m0 + c + j, n, g[j], NACC == 2 ? u[j] : 0.f);
+                            for (int j = 0; j < 16; ++j) xv[j] = (c + j < m_valid) ? xp[(size_t)j * a.ldo] : 0.f;
+#pragma unroll
+                            for (int j = 0; j < 16; ++j)
+                                if (c + j < m_valid) xp[(size_t)j * a.ldo] = xv[j] + g[j];
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 16; ++j)
+                                if (c + j < m_valid) epilogue_store(a, m0 + c + j, n, g[j], NACC == 2 ? u[j] : 0.f);
+                        }
                     }
                 }
             }
@@ -269,9 +279,14 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
                     size_t split_stride = (size_t)n_tiles * NACC * BN * BM;
                     const float* p0 = a.scratch + ((size_t)tile * NACC) * BN * BM + row;
                     for (int mb = 0; mb < m_valid; mb += 8) {
-                        float g[8], u[8];
+                        float g[8], u[8], xv[8];
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) g[j] = u[j] = 0.f;
+                        for (int j = 0; j < 8; ++j) {
+                            g[j] = u[j] = 0.f;
+                            // the residual values this tile adds into travel together with the partial sums
+                            xv[j] = (a.mode == TC_ACCUM_F32 && mb + j < m_valid)
+                                        ? __ldcg((const float*)a.out + (size_t)(m0 + mb + j) * a.ldo + n) : 0.f;
+                        }
 #pragma unroll 4
                         for (int s = 0; s < a.splits; ++s) {
                             const float* p = p0 + s * split_stride;
@@ -286,8 +301,11 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
                             for (int j = 0; j < 8; ++j) { g[j] += tg[j]; u[j] += tu[j]; }
                         }
 #pragma unroll
-                        for (int j = 0; j < 8; ++j)
-                            if (mb + j < m_valid) epilogue_store(a, m0 + mb + j, n, g[j], u[j]);
+                        for (int j = 0; j < 8; ++j) {
+                            if (mb + j >= m_valid) continue;
+                            if (a.mode == TC_ACCUM_F32) ((float*)a.out)[(size_t)(m0 + mb + j) * a.ldo + n] = xv[j] + g[j];
+                            else epilogue_store(a, m0 + mb + j, n, g[j], u[j]);
+                        }
                     }
                 }
                 if (threadIdx.x == 64) a.counters[tile] = 0;      // ready for the next launch

@@ -16,6 +16,7 @@ kernel_lib.declare("ce_attention_decode_scratch", _ll, [_i, _i, _i, _i])
 # n_seqs, nh, nkv, d, q_stride, page_size, max_pages, num_pages, window, scale, max_splits, stream
 kernel_lib.declare("ce_attention_decode_bf16", _i, [_p] * 6 + [_i] + [_p] * 6 + [_i] * 9 + [_f, _i, _p])
 kernel_lib.declare("ce_attention_decode_split", _i, [])
+kernel_lib.declare("ce_attention_decode_kernels", _i, [])
 # q, k_pool, v_pool, out, positions, seq_slot, q_start, ctx_len, block_table, tiles, status,
 # n_tiles, nh, nkv, d, q_stride, page_size, max_pages, num_pages, window, scale, stream
 kernel_lib.declare("ce_attention_prefill_bf16", _i, [_p] * 11 + [_i] * 9 + [_f, _p])
@@ -101,7 +102,8 @@ def attention_bf16(ctx, qkv, out, cache, table, nh, nkv, d, window, scale) -> bo
         ops._ok(k.ce_attention_decode_bf16(
             qkv.data_ptr(), cache.k_pool.data_ptr(), cache.v_pool.data_ptr(), out.data_ptr(), scratch.data_ptr(),
             ws.attn_counters.data_ptr(), ws.attn_counters.numel(), ctx.positions.data_ptr(), ctx.seq_slot.data_ptr(), ctx.q_start.data_ptr(), ctx.ctx_len.data_ptr(),
-            table.data_ptr(), ctx.status.data_ptr(), ctx.n_decode, nh, nkv, d, qkv.shape[1], *args, splits, stream), 2)
+            table.data_ptr(), ctx.status.data_ptr(), ctx.n_decode, nh, nkv, d, qkv.shape[1], *args, splits, stream),
+                k.ce_attention_decode_kernels())
     if ctx.n_tiles > 0:
         ops._ok(k.ce_attention_prefill_bf16(
             qkv.data_ptr(), cache.k_pool.data_ptr(), cache.v_pool.data_ptr(), out.data_ptr(),

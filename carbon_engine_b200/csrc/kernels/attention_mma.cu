@@ -80,6 +80,27 @@ __device__ __forceinline__ void stage_tile(bf16* Ks, bf16* Vs, const MmaAttnArgs
     int dkl = AM_THREADS / chunks, dpart = AM_THREADS - dkl * chunks;
     bool pow2 = (a.page_size & (a.page_size - 1)) == 0;
     int shift = 31 - __clz(a.page_size);
+    if (pow2 && a.page_size >= AM_TILE && (k0 & (AM_TILE - 1)) == 0 && dpart == 0) {
+        // the whole tile lies in one page and every thread keeps its 16-byte column: one table lookup,
+        // then source and destination advance by constant strides
+        int page = (k0 <= hi && k0 + AM_TILE > lo) ? table[k0 >> shift] : 0;
+        bool page_ok = page >= 0 && page < a.num_pages;
+        if (!page_ok) { atomicExch(a.status, 4); page = 0; }
+        size_t base = (((size_t)page * a.nkv + kvh) * a.page_size + (k0 & (a.page_size - 1)) + kl) * d + part * 8;
+        const bf16* ksrc = a.k_pool + base;
+        const bf16* vsrc = a.v_pool + base;
+        bf16* kdst = Ks + kl * ld + part * 8;
+        bf16* vdst = Vs + kl * ld + part * 8;
+        bool all_valid = page_ok && k0 >= lo && k0 + AM_TILE - 1 <= hi;
+        for (; kl < AM_TILE; kl += dkl) {
+            bool valid = all_valid || (page_ok && k0 + kl >= lo && k0 + kl <= hi);
+            cp_async16(kdst, ksrc, valid);
+            cp_async16(vdst, vsrc, valid);
+            ksrc += dkl * d; vsrc += dkl * d;
+            kdst += dkl * ld; vdst += dkl * ld;
+        }
+        return;
+    }
     while (kl < AM_TILE) {
         int key = k0 + kl;
         bool valid = key >= lo && key <= hi;

@@ -120,6 +120,8 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
     ap.add_argument("--no-graphs", action="store_true")
+    ap.add_argument("--prefill-only", action="store_true",
+                    help="run only the 2,048-token prefill (for profiling) and print its time")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": "the reference is a Rust crate on the candle library: no "
@@ -135,8 +137,13 @@ def main() -> int:
     from carbon_engine_b200.bench_support import BenchHarness
     pk = peaks()
     cfg = dict(SIZES_8B, num_hidden_layers=args.layers)
-    h = BenchHarness(cfg, max_batch=max(64 if not args.no_points else args.batch, args.batch), context=args.context,
+    h = BenchHarness(cfg, max_batch=2 if args.prefill_only else max(64 if not args.no_points else args.batch, args.batch),
+                     context=args.context,
                      new_tokens=max(256, args.steps + args.warmup + 8), graphs=not args.no_graphs)
+    if args.prefill_only:
+        pf = h.prefill(2048, 2, 2)
+        print(json.dumps({"prefill_ms": round(pf["ms"], 3), "layers": args.layers}))
+        return 0
     clocks = ClockSampler()
     clocks.start()
     time.sleep(0.3)

@@ -31,7 +31,8 @@ class StepBuffers:
         T, B = self.max_tokens, self.max_seqs
         upd = T + 2 * B + 8                      # the most table entries one step can add per group
         sizes = [("tokens", T), ("positions", T), ("seq_of_token", T), ("seq_slot", B), ("q_start", B + 1),
-                 ("ctx_len", B), ("rows", T), ("tiles", 2 * (B + T // 64 + 1))]
+                 ("ctx_len", B), ("rows", T), ("tiles", 2 * (B + T // 64 + 1)),
+                 ("tiles128", 2 * (B + T // 128 + 1))]
         for g in range(num_groups):
             sizes += [(f"upd_idx{g}", upd), (f"upd_val{g}", upd)]
         self.offsets = {}
@@ -90,6 +91,8 @@ class StepContext:
         self.h_ctx_before: List[int] = []    # tokens of each sequence already in the cache
         self.tiles = bufs.dev_section("tiles")
         self.n_tiles = 0                     # 64-token tiles of the sequences that bring more than one token
+        self.tiles128 = bufs.dev_section("tiles128")
+        self.n_tiles128 = 0                  # the same in tiles of 128 tokens (tcgen05 attention)
         self.decode_splits = 1               # grid size of the split-KV decode kernel: >= ceil(longest decode context / 256)
         self._scratch = {}
         self.n_decode = 0                    # the first n_decode sequences bring exactly one token

@@ -124,7 +124,8 @@ class ModelRunner:
         h_qs[len(entries)] = off
         ctx.h_q_start.append(off)
         h_tiles = b.host_section("tiles")
-        nt = 0
+        h_tiles128 = b.host_section("tiles128")
+        nt = nt128 = 0
         dec_ctx = 1
         for bi, i in enumerate(order):
             n = len(entries[i].tokens)
@@ -134,7 +135,11 @@ class ModelRunner:
             for q0 in range(0, n, 64):
                 h_tiles[2 * nt], h_tiles[2 * nt + 1] = bi, q0
                 nt += 1
+            for q0 in range(0, n, 128):
+                h_tiles128[2 * nt128], h_tiles128[2 * nt128 + 1] = bi, q0
+                nt128 += 1
         ctx.n_tiles = nt
+        ctx.n_tiles128 = nt128
         ctx.decode_splits = (dec_ctx + self._decode_split - 1) // self._decode_split
         ctx.h_tokens = h_tok[:T].tolist()
 

@@ -35,6 +35,13 @@ def decode_split() -> int:
 GEMM_SCRATCH_FLOATS = 16 << 20        # 64 MB of split-K partial sums
 GEMM_COUNTERS = 1 << 16
 
+kernel_lib.declare("ce_attention_prefill_tc_supported", _i, [_i, _i, _i])
+# q, k_pool, v_pool, out, seq_slot, q_start, ctx_len, block_table, tiles, status,
+# n_tiles, total_tokens, nh, nkv, d, q_stride, page_size, max_pages, num_pages, window, scale, stream
+kernel_lib.declare("ce_attention_prefill_tc", _i, [_p] * 10 + [_i] * 10 + [_f, _p])
+
+#: set to False to keep portions of prompts off the tcgen05 attention kernel (the mma.sync one takes them)
+USE_TENSOR_ATTENTION = True
 #: set to False to keep bfloat16 products off the tcgen05 kernel
 USE_TENSOR_GEMM = True
 
@@ -104,7 +111,13 @@ def attention_bf16(ctx, qkv, out, cache, table, nh, nkv, d, window, scale) -> bo
             ws.attn_counters.data_ptr(), ws.attn_counters.numel(), ctx.positions.data_ptr(), ctx.seq_slot.data_ptr(), ctx.q_start.data_ptr(), ctx.ctx_len.data_ptr(),
             table.data_ptr(), ctx.status.data_ptr(), ctx.n_decode, nh, nkv, d, qkv.shape[1], *args, splits, stream),
                 k.ce_attention_decode_kernels())
-    if ctx.n_tiles > 0:
+    if ctx.n_tiles > 0 and USE_TENSOR_ATTENTION and getattr(ctx, "n_tiles128", 0) > 0 and \
+            k.ce_attention_prefill_tc_supported(d, cache.page_size, qkv.shape[1]):
+        ops._ok(k.ce_attention_prefill_tc(
+            qkv.data_ptr(), cache.k_pool.data_ptr(), cache.v_pool.data_ptr(), out.data_ptr(), ctx.seq_slot.data_ptr(),
+            ctx.q_start.data_ptr(), ctx.ctx_len.data_ptr(), table.data_ptr(), ctx.tiles128.data_ptr(),
+            ctx.status.data_ptr(), ctx.n_tiles128, qkv.shape[0], nh, nkv, d, qkv.shape[1], *args, stream))
+    elif ctx.n_tiles > 0:
         ops._ok(k.ce_attention_prefill_bf16(
             qkv.data_ptr(), cache.k_pool.data_ptr(), cache.v_pool.data_ptr(), out.data_ptr(),
             ctx.positions.data_ptr(), ctx.seq_slot.data_ptr(), ctx.q_start.data_ptr(), ctx.ctx_len.data_ptr(),

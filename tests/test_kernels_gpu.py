@@ -358,7 +358,7 @@ class FakeCtx:
         mk = lambda a: torch.tensor(a, dtype=torch.int32, device=dev())
         order = sorted(range(len(seqs)), key=lambda i: 0 if seqs[i][1] == 1 else 1)
         self.order = order
-        pos, qs, ctx, tiles = [], [0], [], []
+        pos, qs, ctx, tiles, tiles128 = [], [0], [], [], []
         self.n_decode = sum(1 for c, n in seqs if n == 1)
         dec = 1
         for bi, i in enumerate(order):
@@ -370,11 +370,14 @@ class FakeCtx:
                 dec = max(dec, c + n)
             else:
                 tiles += [[bi, q0] for q0 in range(0, n, 64)]
+                tiles128 += [[bi, q0] for q0 in range(0, n, 128)]
         self.T = qs[-1]
         self.positions, self.q_start, self.ctx_len = mk(pos), mk(qs), mk(ctx)
         self.seq_slot = mk(order)                  # sequence bi of the step uses block-table row order[bi]
         self.tiles = mk(tiles if tiles else [[0, 0]])
         self.n_tiles = len(tiles)
+        self.tiles128 = mk(tiles128 if tiles128 else [[0, 0]])
+        self.n_tiles128 = len(tiles128)
         from carbon_engine_b200 import ops_tensor
         split = ops_tensor.decode_split()
         self.decode_splits = (dec + split - 1) // split
@@ -535,3 +538,28 @@ def test_tcgen05_product_refuses_what_tma_cannot_address(ops):
     from carbon_engine_b200.parts import linear
     linear.matmul_nt(a, w, out, linear.STORE)                          # the plain kernel takes it
     assert rel_err(out, a.double().cpu() @ w.double().cpu().T) < 1e-2
+
+
+@pytest.mark.parametrize("nh,nkv,d,ps,window", [(32, 8, 128, 64, 0), (4, 2, 128, 16, 0), (6, 3, 64, 8, 0), (8, 2, 64, 32, 50),
+                                                 (4, 1, 128, 128, 200)])
+def test_tcgen05_attention_over_long_portions(nh, nkv, d, ps, window):
+    """Portions longer than one tile of 128 queries, with and without a cached prefix, next to short ones."""
+    from carbon_engine_b200 import ops_tensor
+    assert ops_tensor.kernels().ce_attention_prefill_tc_supported(d, ps, (nh + 2 * nkv) * d)
+    seqs = [(0, 300), (517, 131), (64, 128), (0, 1), (1000, 3), (127, 2)]
+    got, want = run_mma_attention(seqs, nh, nkv, d, ps, window, 1 / math.sqrt(d), seed=11)
+    for i in range(len(seqs)):
+        assert rel_err(got[i], want[i]) < 2e-2, (i, seqs[i])
+
+
+def test_tcgen05_attention_agrees_with_the_mma_kernel():
+    from carbon_engine_b200 import ops_tensor
+    seqs = [(200, 190), (0, 77)]
+    a, want = run_mma_attention(seqs, 8, 2, 128, 64, 0, 0.09, seed=5)
+    ops_tensor.USE_TENSOR_ATTENTION = False
+    try:
+        b, _ = run_mma_attention(seqs, 8, 2, 128, 64, 0, 0.09, seed=5)
+    finally:
+        ops_tensor.USE_TENSOR_ATTENTION = True
+    for i in range(2):
+        assert rel_err(a[i], b[i]) < 1e-2 and rel_err(a[i], want[i]) < 2e-2

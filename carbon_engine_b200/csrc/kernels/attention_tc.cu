@@ -134,18 +134,32 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_tc_kernel(const __g
                                                                       const __grid_constant__ CUtensorMap map_k,
                                                                       const __grid_constant__ CUtensorMap map_v, TcAttnArgs a) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
-    __shared__ __align__(8) uint64_t q_full, kv_full[STAGES], kv_empty[STAGES], s_full, s_free, p_full, pv_done;
-    __shared__ uint32_t tmem_slot;
-    __shared__ int s_abort;
 
     constexpr int HALVES = D / 64;                        // 64-column boxes per row of D
     constexpr uint32_t Q_BYTES = BM * D * 2, K_BYTES = BN * D * 2, P_BYTES = BM * BN * 2;
     constexpr uint32_t Q_HALF = BM * 128, K_HALF = BN * 128;
     constexpr uint32_t STAGE_BYTES = 2 * K_BYTES;          // K then V
     constexpr uint32_t TMEM_COLS = 256;                    // S: 64 columns at 0; O: D columns at 64
-    uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    unsigned char* sm = smem_raw + (base - smem_u32(smem_raw));
+    // No static shared memory and no alignment slack: the tiles start at the block's first shared byte
+    // (checked below to be 1024-aligned, as the swizzle needs), the barriers follow the tiles; two
+    // blocks then fit one SM.
+    uint32_t base = smem_u32(smem_raw);
+    unsigned char* sm = smem_raw;
     uint32_t q_addr = base, kv_addr = base + Q_BYTES, p_addr = kv_addr + STAGES * STAGE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sm + Q_BYTES + STAGES * STAGE_BYTES + P_BYTES);
+    uint64_t& q_full = bars[0];
+    uint64_t* kv_full = bars + 1;
+    uint64_t* kv_empty = bars + 1 + STAGES;
+    uint64_t& s_full = bars[1 + 2 * STAGES];
+    uint64_t& s_free = bars[2 + 2 * STAGES];
+    uint64_t& p_full = bars[3 + 2 * STAGES];
+    uint64_t& pv_done = bars[4 + 2 * STAGES];
+    uint32_t& tmem_slot = *reinterpret_cast<uint32_t*>(bars + 5 + 2 * STAGES);
+    int& s_abort = *reinterpret_cast<int*>(bars + 6 + 2 * STAGES);
+    if (base & 1023u) {                       // cannot happen with dynamic shared memory alone; refuse rather than mis-swizzle
+        if (threadIdx.x == 0) atomicCAS(a.status, 0, 69);
+        return;
+    }
 
     int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     int b = a.tiles[2 * blockIdx.x], q0 = a.tiles[2 * blockIdx.x + 1];
@@ -163,7 +177,7 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_tc_kernel(const __g
     if (threadIdx.x == 0) {
         mbar_init(&q_full, 1);
         for (int s = 0; s < STAGES; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
-        mbar_init(&s_full, 1); mbar_init(&s_free, 1); mbar_init(&p_full, 1); mbar_init(&pv_done, 1);
+        mbar_init(&s_full, 1); mbar_init(&s_free, 128); mbar_init(&p_full, 128); mbar_init(&pv_done, 1);
         s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -272,8 +286,9 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_tc_kernel(const __g
         for (int j = 0; j < n_kv; ++j) {
             int k0 = k_begin + j * BN;
             where = 66;
-            ok = mbar_wait(&s_full, j & 1);
-            if (softmax_any(!ok)) { ok = false; break; }
+            // one thread polls the barrier; the named barrier hands its verdict to all 128 and lines them up
+            bool mine = threadIdx.x == 64 ? mbar_wait(&s_full, j & 1) : true;
+            if (softmax_any(!mine)) { ok = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             float sv[BN];
             {
@@ -286,8 +301,7 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_tc_kernel(const __g
                 for (int i = 0; i < 32; ++i) sv[32 + i] = t[i];
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            if (threadIdx.x == 64) mbar_arrive(&s_free);                 // S may be overwritten by the next product
+            mbar_arrive(&s_free);                 // (128 arrivals) S may be overwritten by the next product
             bool full = row_valid && k0 >= lo && k0 + BN - 1 <= pos;
             float mx = -INFINITY;
 #pragma unroll
@@ -298,9 +312,14 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_tc_kernel(const __g
                 }
                 mx = fmaxf(mx, sv[i]);
             }
-            float m_new = fmaxf(m_run, mx * a.scale_log2);
+            // The running maximum is only a scale: it is raised (and the sums rescaled) when a tile's maximum
+            // exceeds it by more than 2^8; below that the probabilities stay within bfloat16's range and the
+            // output accumulator is left alone.
+            float m_tile = mx * a.scale_log2;
+            bool raise = m_tile > m_run + 8.0f || (m_run == -INFINITY && m_tile != -INFINITY);
+            float m_new = raise ? m_tile : m_run;
             float m_use = m_new == -INFINITY ? 0.f : m_new;
-            float alpha = exp2f(m_run - m_use);
+            float alpha = raise ? exp2f(m_run - m_use) : 1.0f;
             float sum = 0.f;
             uint32_t packed[BN / 2];
 #pragma unroll
@@ -312,11 +331,11 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_tc_kernel(const __g
             }
             l_run = l_run * alpha + sum;
             m_run = m_new;
-            // P and (if a maximum moved) O may be touched only after the previous PV product is complete
+            // P and (if a scale was raised) O may be touched only after the previous PV product is complete
             if (j > 0) {
                 where = 67;
-                ok = mbar_wait(&pv_done, (j - 1) & 1);
-                if (softmax_any(!ok)) { ok = false; break; }
+                mine = threadIdx.x == 64 ? mbar_wait(&pv_done, (j - 1) & 1) : true;
+                if (softmax_any(!mine)) { ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 if (__any_sync(0xffffffffu, alpha != 1.0f)) {
 #pragma unroll 1
@@ -353,13 +372,12 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_tc_kernel(const __g
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            if (threadIdx.x == 64) mbar_arrive(&p_full);
+            mbar_arrive(&p_full);                 // (128 arrivals) P, and the zeroed rows of V, are in shared memory
         }
         if (ok) {                       // (uniform: every exit from the loop above is taken by all 128 threads)
             where = 68;
-            ok = mbar_wait(&pv_done, (n_kv - 1) & 1);
-            if (softmax_any(!ok)) ok = false;
+            bool mine = threadIdx.x == 64 ? mbar_wait(&pv_done, (n_kv - 1) & 1) : true;
+            if (softmax_any(!mine)) ok = false;
         }
         if (!ok) { atomicCAS(a.status, 0, where); atomicExch(&s_abort, 1); }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -445,7 +463,7 @@ int get_map(const void* ptr, long long rows, long long cols, long long ld, int b
 
 template <int D>
 int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const TcAttnArgs& a, dim3 grid, cudaStream_t stream) {
-    size_t smem = (size_t)BM * D * 2 + STAGES * 2 * BN * D * 2 + BM * BN * 2 + 1024;
+    size_t smem = (size_t)BM * D * 2 + STAGES * 2 * BN * D * 2 + BM * BN * 2 + 128;    // tiles + barriers
     static bool attr_set = false;
     if (!attr_set) {
         cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

@@ -231,7 +231,7 @@ __device__ __forceinline__ void warp_tile(const uint32_t (&qf)[DMAX / 16][4], fl
 // ---------------------------------------------------------------------------------------------
 // Decode: grid (n_seqs * max_splits, nkv, head groups of 16)
 // ---------------------------------------------------------------------------------------------
-template <int DMAX>
+template <int DMAX, int ST>
 __global__ void __launch_bounds__(AM_THREADS) attention_decode_kernel(MmaAttnArgs a) {
     ce_pdl_begin();
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -246,7 +246,7 @@ __global__ void __launch_bounds__(AM_THREADS) attention_decode_kernel(MmaAttnArg
     const int* table = a.block_table + (size_t)a.seq_slot[b] * a.max_pages;
     int d = a.d, ld = d + AM_PAD;
     bf16* Ks = reinterpret_cast<bf16*>(smem_raw);
-    bf16* Vs = Ks + AM_STAGES * AM_TILE * ld;
+    bf16* Vs = Ks + ST * AM_TILE * ld;
 
     int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, quad = lane & 3, grp = lane >> 2;
     int heads_here = min(16, G - hg * 16);
@@ -274,20 +274,20 @@ __global__ void __launch_bounds__(AM_THREADS) attention_decode_kernel(MmaAttnArg
 
     int n_tiles = (k_end - k_begin + AM_TILE - 1) / AM_TILE;
 #pragma unroll
-    for (int p = 0; p < AM_STAGES - 1; ++p) {
+    for (int p = 0; p < ST - 1; ++p) {
         if (p < n_tiles) stage_tile(Ks + p * AM_TILE * ld, Vs + p * AM_TILE * ld, a, table, kvh, k_begin + p * AM_TILE, lo, pos);
         cp_async_commit();
     }
     for (int it = 0; it < n_tiles; ++it) {
-        cp_async_wait<AM_STAGES - 2>();       // tile `it` has landed
+        cp_async_wait<ST - 2>();       // tile `it` has landed
         __syncthreads();                      // ... for everyone, and everyone is done with tile it-1
-        int nxt = it + AM_STAGES - 1;
+        int nxt = it + ST - 1;
         if (nxt < n_tiles) {
-            int st = nxt % AM_STAGES;         // the stage tile it-1 was computed from
+            int st = nxt % ST;         // the stage tile it-1 was computed from
             stage_tile(Ks + st * AM_TILE * ld, Vs + st * AM_TILE * ld, a, table, kvh, k_begin + nxt * AM_TILE, lo, pos);
         }
         cp_async_commit();
-        int cur = it % AM_STAGES;
+        int cur = it % ST;
         int k0 = k_begin + it * AM_TILE + warp * 16;
         if (k0 <= pos) {
             const bf16* kt = Ks + (cur * AM_TILE + warp * 16) * ld;
@@ -587,16 +587,23 @@ extern "C" int ce_attention_decode_bf16(const void* q, const void* k_pool, const
     size_t smem = stage_bytes(d);
     size_t comb = (size_t)(4 * 16 * d + 128) * sizeof(float);
     if (comb > smem) smem = comb;
-    if (d <= 64) {
-        if ((rc = set_smem(attention_decode_kernel<64>, smem, "ce_attention_decode_bf16"))) return rc;
-        ce_launch(attention_decode_kernel<64>, grid, AM_THREADS, smem, stream, a);
-    } else if (d <= 128) {
-        if ((rc = set_smem(attention_decode_kernel<128>, smem, "ce_attention_decode_bf16"))) return rc;
-        ce_launch(attention_decode_kernel<128>, grid, AM_THREADS, smem, stream, a);
-    } else {
-        if ((rc = set_smem(attention_decode_kernel<256>, smem, "ce_attention_decode_bf16"))) return rc;
-        ce_launch(attention_decode_kernel<256>, grid, AM_THREADS, smem, stream, a);
+    // Few blocks: three staging buffers each (loads run further ahead).  Many blocks: two, so that three
+    // blocks share an SM (measured: 4.67 vs 4.83 ms a step at batch 8, 5990 vs 5630 tokens/s at batch 64).
+    bool deep = (long long)grid.x * grid.y * grid.z <= 1200;
+    if (!deep) {
+        smem = stage_bytes(d, 2);
+        if (comb > smem) smem = comb;
     }
+#define AM_DECODE_CASE(DM)                                                                                        \
+    if (deep) {                                                                                                   \
+        if ((rc = set_smem(attention_decode_kernel<DM, 3>, smem, "ce_attention_decode_bf16"))) return rc;         \
+        ce_launch(attention_decode_kernel<DM, 3>, grid, AM_THREADS, smem, stream, a);                             \
+    } else {                                                                                                      \
+        if ((rc = set_smem(attention_decode_kernel<DM, 2>, smem, "ce_attention_decode_bf16"))) return rc;         \
+        ce_launch(attention_decode_kernel<DM, 2>, grid, AM_THREADS, smem, stream, a);                             \
+    }
+    if (d <= 64) { AM_DECODE_CASE(64) } else if (d <= 128) { AM_DECODE_CASE(128) } else { AM_DECODE_CASE(256) }
+#undef AM_DECODE_CASE
     if ((rc = ce_check_launch("ce_attention_decode_bf16"))) return rc;
     if (a.fused_merge) return CE_OK;
     ce_launch(attention_merge_kernel, dim3(n_seqs, nh), d >= 128 ? 128 : (d + 31) / 32 * 32, max_splits * sizeof(float), stream, a);

@@ -21,6 +21,7 @@
 #include "common.cuh"
 #include <cuda.h>
 #include <mutex>
+#include <stdio.h>
 #include <stdlib.h>
 #include <unordered_map>
 
@@ -88,12 +89,22 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
     for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+// Optional timing trace (CE_GEMM_TRACE=1): block (0,0,0) of every launch stamps %globaltimer at a few
+// places into a ring of 256 records; ce_gemm_tc_trace() copies the ring out.  Off by default.
+__device__ unsigned long long g_trace[256 * 8];
+__device__ unsigned int g_trace_n;
+__device__ __forceinline__ unsigned long long gtime() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
 struct TcArgs {
     void* out;               // [M, ldo] bf16 or float32
     float* scratch;          // split-K partials: [splits][tiles][nacc][BN][128]
     int* counters;           // one per output tile, zero between launches
     int* status;
-    int M, N, K, ldo, mode, splits, kblocks_per_split, kblocks;
+    int M, N, K, ldo, mode, splits, kblocks_per_split, kblocks, trace;
 };
 
 __device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + __expf(-g)) * u; }
@@ -126,6 +137,14 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
     int kb0 = split * a.kblocks_per_split;
     int kb1 = min(kb0 + a.kblocks_per_split, a.kblocks);
     int nkb = kb1 - kb0;
+    __shared__ unsigned long long* s_rec;
+    bool tracing = a.trace && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+    if (tracing && threadIdx.x == 0) {
+        unsigned int idx = atomicAdd(&g_trace_n, 1u) & 255u;
+        s_rec = g_trace + idx * 8;
+        s_rec[0] = gtime();
+        s_rec[7] = ((unsigned long long)a.N << 32) | (unsigned)a.K;
+    }
 
     // Dependent launch: this grid may start while the kernel before it still runs.  Weights are
     // written by no kernel, so their loads start at once; the tokens (and everything the epilogue
@@ -160,6 +179,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
                 if (NACC == 2) tma_load_2d(st + W_BYTES, &map_w, &full_bar[i], k, a.N + n0);
             }
             ce_pdl_wait();
+            if (tracing) s_rec[1] = gtime();
             for (int i = 0; i < first; ++i) {            // their tokens: after it
                 tma_load_2d(tiles + (size_t)i * STAGE_BYTES + NACC * W_BYTES, &map_x, &full_bar[i], (kb0 + i) * BK, m0);
                 issued = i + 1;
@@ -192,6 +212,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
                 int s = i % stages;
                 ok = mbar_wait(&full_bar[s], (i / stages) & 1);
                 if (!ok) break;
+                if (tracing && i == 0) s_rec[2] = gtime();
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 uint32_t st = base + s * STAGE_BYTES;
 #pragma unroll
@@ -205,6 +226,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
             }
             if (ok) umma_commit(&acc_bar);           // the accumulators are complete
             else { atomicExch(a.status, 5); atomicExch(&s_abort, 1); }
+            if (tracing) s_rec[3] = gtime();
         }
     } else {
         // ---- epilogue: 4 warps, each reads the 32 accumulator lanes of its quadrant
@@ -215,6 +237,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
         ce_pdl_wait();
         bool ok = nkb > 0 ? mbar_wait(&acc_bar, 0) : true;
         if (!ok) { atomicExch(a.status, 5); atomicExch(&s_abort, 1); }
+        if (tracing && threadIdx.x == 64) s_rec[4] = gtime();
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         uint32_t taddr = tmem + ((uint32_t)(quad * 32) << 16);
         if (a.splits == 1) {
@@ -270,6 +293,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
             }
             __threadfence();
             asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (tracing && threadIdx.x == 64) s_rec[5] = gtime();
             if (threadIdx.x == 64) s_ticket = atomicAdd(&a.counters[tile], 1);
             asm volatile("bar.sync 1, 128;" ::: "memory");
             if (s_ticket == a.splits - 1) {
@@ -480,6 +504,238 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_persistent_kernel(const __gri
     }
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// Many tokens, CTA pairs: two CTAs of a cluster work on one tile of 256 weight rows x BN tokens with
+// tcgen05.mma.cta_group::2.  Each CTA loads its own 128 weight rows and only HALF of the token tile;
+// the tensor cores of both SMs read both halves, so a pair moves a third less operand data through
+// L2 and shared memory per flop than two single CTAs (the single-CTA kernel is bound by exactly that).
+// The leader CTA's MMA thread issues the MMAs for both; it learns that the peer's stage has landed
+// from an mbarrier that the peer arrives on across the cluster; its tcgen05.commit frees the stage
+// and publishes the accumulators in BOTH CTAs (commit with multicast::cluster; loads use none).
+// Each CTA runs the epilogue for its own 128 rows out of its own tensor memory.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t local_addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
+    return r;
+}
+// Arrival on a barrier of another CTA of the cluster.  Relaxed: it only says that tensor memory has been
+// read (tcgen05.wait::ld has returned); a release here would also wait for the epilogue's global stores.
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ bool mbar_test_cluster(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n.reg .pred p;\nmbarrier.test_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity) {
+    for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
+        uint32_t ok;
+        asm volatile("{\n.reg .pred p;\nmbarrier.test_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+                     : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+        if (ok) return true;
+        if (i > 64) __nanosleep(i > 4096 ? 1024 : 128);
+    }
+    return false;
+}
+// A TMA load of a CTA pair: the data goes to the executing CTA's shared memory, the bytes are counted on
+// a barrier that may lie in the other CTA of the pair (a shared::cluster address).  No multicast.
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, uint32_t cluster_bar, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(smem_u32(dst)), "l"(map), "r"(cluster_bar), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void umma2_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}"
+                 ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma2_commit_both(uint64_t* bar) {
+    unsigned short mask = 3;          // the barrier at this offset in both CTAs of the pair
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(smem_u32(bar)), "h"(mask) : "memory");
+}
+
+// BN: tokens per pair tile (each CTA loads BN/2 of them).  NACC: 1, or 2 for SwiGLU (gate and up rows).
+// KSUB: k-blocks of 64 per stage (per barrier round of the MMA thread).
+template <int BN, int NACC, int KSUB>
+__global__ void __launch_bounds__(THREADS) gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w,
+                                                              const __grid_constant__ CUtensorMap map_x, TcArgs a,
+                                                              int stages, int tiles_n, int tiles_m) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    __shared__ __align__(8) uint64_t full_bar[8], empty_bar[8], acc_full[2], acc_empty[2];
+    __shared__ uint32_t tmem_slot;
+
+    constexpr int HALF_N = BN / 2;
+    constexpr uint32_t W_BYTES = BM * BK * 2, X_BYTES = HALF_N * BK * 2;
+    constexpr uint32_t SUB_BYTES = NACC * W_BYTES + X_BYTES;          // one k-block: W rows (gate, up), then tokens
+    constexpr uint32_t STAGE_BYTES = KSUB * SUB_BYTES;
+    constexpr uint32_t ACC_COLS = NACC * BN;
+    constexpr uint32_t TMEM_COLS = 2 * ACC_COLS;
+    static_assert(TMEM_COLS <= 512 && (TMEM_COLS & (TMEM_COLS - 1)) == 0, "two accumulator sets must fit tensor memory");
+    const int rounds = (a.kblocks + KSUB - 1) / KSUB;                 // a k-block beyond K reads zeros
+    uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    unsigned char* tiles = smem_raw + (base - smem_u32(smem_raw));
+    int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    uint32_t rank = cluster_rank();                  // 0: leader
+    int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+    int total = tiles_n * tiles_m;                   // pair tiles: tiles_n of 256 weight rows, tiles_m of BN tokens
+
+    ce_pdl_launch_dependents();
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < stages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 2); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(TMEM_COLS));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    cluster_sync_all();                              // both CTAs' barriers exist before anything arrives on them
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    uint32_t tmem = tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // ---- producer (in each CTA): its 128 weight rows (and the up rows for SwiGLU), its half of the
+            // tokens, into its own shared memory; the bytes of BOTH CTAs are counted on the leader's barrier
+            ce_pdl_wait();
+            int s = 0, issued = 0;
+            uint32_t ph = 0;                 // parity of the phase of empty_bar[s] that frees the stage's previous use
+            bool ok = true, wrapped = false;
+            for (int tile = pair; tile < total && ok; tile += n_pairs) {
+                int n0 = (tile / tiles_m) * (2 * BM) + rank * BM, m0 = (tile % tiles_m) * BN + rank * HALF_N;
+                for (int r = 0; r < rounds; ++r) {
+                    if (wrapped) ok = mbar_wait_cluster(&empty_bar[s], ph ^ 1);
+                    if (!ok) break;
+                    uint32_t bar = map_to_cta(smem_u32(&full_bar[s]), 0);
+                    if (rank == 0) mbar_expect_tx(&full_bar[s], 2 * STAGE_BYTES);
+#pragma unroll
+                    for (int j = 0; j < KSUB; ++j) {
+                        unsigned char* st = tiles + (size_t)s * STAGE_BYTES + j * SUB_BYTES;
+                        int kx = (r * KSUB + j) * BK;
+                        tma_load_2d_pair(st, &map_w, bar, kx, n0);
+                        if (NACC == 2) tma_load_2d_pair(st + W_BYTES, &map_w, bar, kx, a.N + n0);
+                        tma_load_2d_pair(st + NACC * W_BYTES, &map_x, bar, kx, m0);
+                    }
+                    ++issued;
+                    if (++s == stages) { s = 0; ph ^= 1; wrapped = true; }
+                }
+            }
+            if (!ok) {
+                // give the copies in flight time to land before the block may leave (the leader's barriers
+                // count the bytes of both blocks; the peer cannot wait on them, so it waits by the clock)
+                atomicExch(a.status, 5);
+                if (rank == 0) for (int i = max(0, issued - stages); i < issued; ++i) mbar_wait_cluster(&full_bar[i % stages], (i / stages) & 1);
+                else for (int i = 0; i < 64; ++i) __nanosleep(1000);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && rank == 0) {
+            // ---- leader: MMAs for both CTAs.  This one thread's instruction stream is the critical path
+            // (a barrier test alone takes about a hundred cycles), so the next stage's barrier is tested
+            // BEFORE this stage's MMAs are issued: the test's latency passes while they are queued.
+            int lt = 0, s = 0;
+            uint32_t ph = 0;
+            bool ok = true;
+            uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((2 * BM) >> 4) << 24);
+            const uint64_t desc_hi = umma_desc(0);
+            bool ready = false;
+            for (int tile = pair; tile < total && ok; tile += n_pairs, ++lt) {
+                int buf = lt & 1;
+                if (lt >= 2) ok = mbar_wait_cluster(&acc_empty[buf], ((lt >> 1) - 1) & 1);   // both epilogues have drained this set
+                if (!ok) break;
+                uint32_t d_tmem = tmem + buf * ACC_COLS;
+                for (int r = 0; r < rounds; ++r) {
+                    if (!ready) ok = mbar_wait_cluster(&full_bar[s], ph);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    int sn = s + 1 == stages ? 0 : s + 1;
+                    uint32_t phn = sn == 0 ? ph ^ 1 : ph;
+                    ready = mbar_test_cluster(&full_bar[sn], phn);
+#pragma unroll
+                    for (int j = 0; j < KSUB; ++j) {
+                        uint32_t st = (base + s * STAGE_BYTES + j * SUB_BYTES) >> 4;
+#pragma unroll
+                        for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+                            uint64_t bdesc = desc_hi | (uint64_t)((st + ((NACC * W_BYTES + kk * UMMA_K * 2) >> 4)) & 0x3FFF);
+                            uint32_t acc = (r > 0 || j > 0 || kk > 0) ? 1u : 0u;
+                            umma2_bf16(d_tmem, desc_hi | (uint64_t)((st + ((kk * UMMA_K * 2) >> 4)) & 0x3FFF), bdesc, idesc, acc);
+                            if (NACC == 2)
+                                umma2_bf16(d_tmem + BN, desc_hi | (uint64_t)((st + ((W_BYTES + kk * UMMA_K * 2) >> 4)) & 0x3FFF), bdesc, idesc, acc);
+                        }
+                    }
+                    umma2_commit_both(&empty_bar[s]);     // the stage is free in both CTAs
+                    s = sn; ph = phn;
+                }
+                if (ok) umma2_commit_both(&acc_full[buf]);
+            }
+            if (!ok) atomicExch(a.status, 5);
+        }
+    } else {
+        // ---- epilogue (in each CTA): its own 128 rows
+        int quad = warp & 3;
+        int row = quad * 32 + lane;
+        ce_pdl_wait();
+        int lt = 0;
+        bool ok = true;
+        uint32_t leader_empty[2] = {map_to_cta(smem_u32(&acc_empty[0]), 0), map_to_cta(smem_u32(&acc_empty[1]), 0)};
+        for (int tile = pair; tile < total && ok; tile += n_pairs, ++lt) {
+            int buf = lt & 1;
+            int n = (tile / tiles_m) * (2 * BM) + rank * BM + row;
+            int m0 = (tile % tiles_m) * BN;
+            int m_valid = min(BN, a.M - m0);
+            ok = mbar_wait_cluster(&acc_full[buf], (lt >> 1) & 1);
+            if (!ok) { atomicExch(a.status, 5); break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            uint32_t taddr = tmem + buf * ACC_COLS + ((uint32_t)(quad * 32) << 16);
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 32) {
+                if (c >= m_valid) break;
+                float g[32], u[32];
+                tmem_ld32(taddr + c, g);
+                if (NACC == 2) tmem_ld32(taddr + BN + c, u);
+                if (n < a.N) {
+                    if (a.mode == TC_ACCUM_F32) {
+                        float* xp = (float*)a.out + (size_t)(m0 + c) * a.ldo + n;
+                        float xv[32];
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) xv[j] = (c + j < m_valid) ? xp[(size_t)j * a.ldo] : 0.f;
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (c + j < m_valid) xp[(size_t)j * a.ldo] = xv[j] + g[j];
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (c + j < m_valid) epilogue_store(a, m0 + c + j, n, g[j], NACC == 2 ? u[j] : 0.f);
+                    }
+                }
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (threadIdx.x == 64) mbar_arrive_remote(leader_empty[buf]);     // (two arrivals: one per CTA)
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    }
+    __syncthreads();
+    cluster_sync_all();                              // nobody leaves while the other may still signal it
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS));
+    }
+}
+
 // ---- host side ------------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                 const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -585,6 +841,51 @@ int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, const TcArgs
     return ce_check_launch("ce_gemm_tc (persistent)");
 }
 
+template <int BN, int NACC, int KSUB>
+int launch_pair(const CUtensorMap& mw, const CUtensorMap& mx, const TcArgs& a, int tiles_n, int tiles_m, cudaStream_t stream) {
+    constexpr size_t stage = KSUB * (NACC * BM * BK * 2 + (BN / 2) * BK * 2);
+    int stages = (int)((200 * 1024) / stage);
+    if (stages > 8) stages = 8;
+    size_t smem = stages * stage + 1024;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel<BN, NACC, KSUB>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 2048);
+        if (e != cudaSuccess) return ce_fail(CE_ERR_CUDA, "ce_gemm_tc: %s", cudaGetErrorString(e));
+        attr_set = true;
+    }
+    long long total = (long long)tiles_n * tiles_m;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * (sm_count() / 2));
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    // Tiles are dealt to pairs in a fixed stride, so every pair has to be resident at once: not every
+    // SM can be paired (a cluster lies within one GPC), so ask how many pairs fit.
+    static int max_pairs = 0;
+    if (max_pairs == 0) {
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        int n = 0;
+        cudaError_t e = cudaOccupancyMaxActiveClusters(&n, gemm_tc_pair_kernel<BN, NACC, KSUB>, &cfg);
+        if (e != cudaSuccess || n < 1) return ce_fail(CE_ERR_CUDA, "ce_gemm_tc (pairs): no resident cluster: %s", cudaGetErrorString(e));
+        max_pairs = n;
+        if (getenv("CE_GEMM_TRACE")) fprintf(stderr, "[carbon_engine_b200] gemm pairs<%d,%d>: %d resident\n", BN, NACC, n);
+    }
+    int pairs = max_pairs;
+    if (total < pairs) pairs = (int)total;
+    cfg.gridDim = dim3(2 * pairs);
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ce_pdl_enabled() ? 2 : 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel<BN, NACC, KSUB>, mw, mx, a, stages, tiles_n, tiles_m);
+    if (e != cudaSuccess) return ce_fail(CE_ERR_CUDA, "ce_gemm_tc (pairs): %s", cudaGetErrorString(e));
+    return ce_check_launch("ce_gemm_tc (pairs)");
+}
+
 }  // namespace
 
 // How many splits of K a product of these sizes uses (it depends on N and K only while the tokens
@@ -602,6 +903,13 @@ extern "C" int ce_gemm_tc_splits(int M, int N, int K) {
     if (s > by_traffic) s = by_traffic;
     if (s > 16) s = 16;
     return s < 1 ? 1 : s;
+}
+
+// Copies out the timing ring (256 records of 8 values) and the number of records written so far.
+extern "C" int ce_gemm_tc_trace(unsigned long long* out, unsigned int* count) {
+    if (cudaMemcpyFromSymbol(out, g_trace, sizeof(unsigned long long) * 256 * 8) != cudaSuccess) return CE_ERR_CUDA;
+    if (cudaMemcpyFromSymbol(count, g_trace_n, sizeof(unsigned int)) != cudaSuccess) return CE_ERR_CUDA;
+    return CE_OK;
 }
 
 extern "C" int ce_gemm_tc_tile_tokens(int M) {
@@ -642,7 +950,20 @@ extern "C" int ce_gemm_tc(const void* A, const void* W, void* C, int M, int N, i
         int prc = get_map(W, (long long)N * nacc, K, K, BM, &pw);
         if (prc) return prc;
         if ((prc = get_map(A, M, K, lda, pbn, &px))) return prc;
-        TcArgs pa{C, scratch, counters, status, M, N, K, ldc, mode, 1, kblocks, kblocks};
+        static int ptrace = getenv("CE_GEMM_TRACE") ? 1 : 0;
+        TcArgs pa{C, scratch, counters, status, M, N, K, ldc, mode, 1, kblocks, kblocks, ptrace};
+        static int use_pairs = getenv("CE_GEMM_NO_PAIRS") ? 0 : 1;
+        if (use_pairs && N >= 2 * BM) {     // CTA pairs: 256 weight rows a tile, each CTA loads half of the tokens
+            CUtensorMap px2;
+            if ((prc = get_map(A, M, K, lda, pbn / 2, &px2))) return prc;
+            long long tiles_n2 = (N + 2 * BM - 1) / (2 * BM);
+            static int ksub = getenv("CE_GEMM_KSUB") ? atoi(getenv("CE_GEMM_KSUB")) : 2;
+            if (ksub == 1)
+                return nacc == 2 ? launch_pair<128, 2, 1>(pw, px2, pa, (int)tiles_n2, (int)tiles_m, stream)
+                                 : launch_pair<256, 1, 1>(pw, px2, pa, (int)tiles_n2, (int)tiles_m, stream);
+            return nacc == 2 ? launch_pair<128, 2, 2>(pw, px2, pa, (int)tiles_n2, (int)tiles_m, stream)
+                             : launch_pair<256, 1, 2>(pw, px2, pa, (int)tiles_n2, (int)tiles_m, stream);
+        }
         return nacc == 2 ? launch_persistent<128, 2>(pw, px, pa, (int)tiles_n, (int)tiles_m, stream)
                          : launch_persistent<256, 1>(pw, px, pa, (int)tiles_n, (int)tiles_m, stream);
     }
@@ -659,7 +980,8 @@ extern "C" int ce_gemm_tc(const void* A, const void* W, void* C, int M, int N, i
     int rc = get_map(W, (long long)N * nacc, K, K, BM, &mw);
     if (rc) return rc;
     if ((rc = get_map(A, M, K, lda, bn, &mx))) return rc;
-    TcArgs a{C, scratch, counters, status, M, N, K, ldc, mode, splits, (kblocks + splits - 1) / splits, kblocks};
+    static int trace = getenv("CE_GEMM_TRACE") ? 1 : 0;
+    TcArgs a{C, scratch, counters, status, M, N, K, ldc, mode, splits, (kblocks + splits - 1) / splits, kblocks, trace};
 #define TC_CASE(BN_)                                                                  \
     case BN_:                                                                         \
         return nacc == 2 ? launch<BN_, 2>(mw, mx, a, grid, stream) : launch<BN_, 1>(mw, mx, a, grid, stream);

@@ -2,7 +2,7 @@
 // accumulators): a split-KV kernel for sequences that bring one token, and a flash kernel for
 // sequences that bring a portion of a prompt.  Both read keys and values through the block table.
 //
-// Decode: one block per (sequence, KV head, group of up to 16 query heads, split of 256 positions).
+// Decode: one block per (sequence, KV head, group of up to 16 query heads, split of the positions).
 // The query heads that share the KV head are the 16 rows of the MMA tile, so K and V are read once
 // per KV head (the reference's paged_decode_tc does the same for up to 8 heads,
 // src/kernels/attention_tc.cu:682-807).  Each of the 4 warps takes 16 of every 64 staged keys and
@@ -18,11 +18,12 @@
 // Scores are scaled in float32, the softmax runs in float32 with exp2, probabilities are rounded to
 // bfloat16 for the PV product (as in src/kernels/attention_tc.cu:505-515), outputs are rounded once.
 #include "common.cuh"
+#include "tensor_map.h"
 #include <stdlib.h>
 
 #define AM_THREADS 128
 #define AM_TILE 64           // keys staged per iteration
-#define AM_SPLIT 256         // positions per decode split
+#define AM_SPLIT 128         // decode splits are multiples of this many positions
 #define AM_STAGES 3          // decode: staged tiles in flight: loads of tiles i+1, i+2 run while tile i is computed
 #define AM_PF_STAGES 2       // prefill: two stages, so that three blocks fit one SM
 #define AM_PAD 8             // padding of a staged row, in elements (keeps 32-bit and ldmatrix reads conflict-free)
@@ -383,6 +384,286 @@ __global__ void __launch_bounds__(AM_THREADS) attention_decode_kernel(MmaAttnArg
     if (threadIdx.x == 0) a.counters[cidx] = 0;                        // ready for the next launch
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// Decode with TMA staging (head sizes that are multiples of 64, pages of a power of two >= 8 rows).
+// Same work split and same arithmetic as attention_decode_kernel, but a fifth warp's first lane brings
+// every tile of 64 keys with a few cp.async.bulk.tensor copies (one per page piece and 64 columns)
+// into 128-byte-swizzled shared memory, counted on an mbarrier per stage; the four computing warps
+// never stage anything, meet no block-wide barrier inside the loop (a warp frees a stage with one
+// mbarrier arrival), and skip rescaling the output when no row's maximum moved.  A copy brings whole
+// page pieces, whatever they hold: a warp zeroes the V rows of its keys that are not visible before it
+// uses them, so that a probability of 0 never meets a NaN; scores of such keys are masked as before.
+// ---------------------------------------------------------------------------------------------
+#define AMT_THREADS 160
+#define AMT_SPIN (1u << 22)
+
+__device__ __forceinline__ uint32_t amt_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ bool amt_wait(uint64_t* bar, uint32_t parity) {
+    for (uint32_t i = 0; i < AMT_SPIN; ++i) {
+        uint32_t ok;
+        asm volatile("{\n.reg .pred p;\nmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+                     : "=r"(ok) : "r"(amt_smem(bar)), "r"(parity) : "memory");
+        if (ok) return true;
+        if (i > 256) __nanosleep(64);
+    }
+    return false;
+}
+__device__ __forceinline__ void ldmatrix_x4_addr(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans_addr(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+
+// One warp: its 16 keys (rows slab .. slab+15 of the staged tile) against the 16 query rows.
+// ks, vs: shared addresses of the stage's K and V; each is d/64 panels of [64 keys][128 bytes], swizzled.
+template <int DMAX, bool MASK>
+__device__ __forceinline__ void warp_tile_swz(const uint32_t (&qf)[DMAX / 16][4], float (&o)[DMAX / 8][4], float (&m)[2],
+                                              float (&l)[2], uint32_t ks, uint32_t vs, int slab, int d, int key_base,
+                                              int lo, int hi, float scale_log2) {
+    int lane = threadIdx.x & 31, quad = lane & 3;
+    int mi = lane >> 3, rr = lane & 7;
+    float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+    float s2[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+    // K: matrices 0,1 = keys slab..slab+7 (columns +0, +8), matrices 2,3 = keys slab+8..slab+15
+    uint32_t krow = ks + (uint32_t)(slab + (mi >> 1) * 8 + rr) * 128u;
+#pragma unroll
+    for (int kk = 0; kk < DMAX / 16; ++kk) {
+        if (kk * 16 < d) {
+            uint32_t kb[4];
+            uint32_t chunk = (uint32_t)((kk & 3) * 2 + (mi & 1));
+            ldmatrix_x4_addr(kb, krow + (uint32_t)(kk >> 2) * 8192u + ((chunk ^ (uint32_t)rr) << 4));
+            if (kk & 1) { mma16816(s2[0], qf[kk], kb[0], kb[1]); mma16816(s2[1], qf[kk], kb[2], kb[3]); }
+            else { mma16816(s[0], qf[kk], kb[0], kb[1]); mma16816(s[1], qf[kk], kb[2], kb[3]); }
+        }
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) { s[0][e] += s2[0][e]; s[1][e] += s2[1][e]; }
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            if (MASK) {
+                int key = key_base + j * 8 + 2 * quad + (e & 1);
+                if (!(key >= lo && key <= hi)) s[j][e] = -INFINITY;
+            }
+            mx[e >> 1] = fmaxf(mx[e >> 1], s[j][e]);
+        }
+    }
+    float alpha[2], muse[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+        float mn = fmaxf(m[r], mx[r] * scale_log2);
+        muse[r] = mn == -INFINITY ? 0.f : mn;
+        alpha[r] = exp2f(m[r] - muse[r]);
+        m[r] = mn;
+        l[r] *= alpha[r];
+    }
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            float p = exp2f(fmaf(s[j][e], scale_log2, -muse[e >> 1]));
+            s[j][e] = p;
+            l[e >> 1] += p;
+        }
+    }
+    // most tiles move no row's maximum: then every alpha is exactly 1 and the output needs no rescaling
+    if (__any_sync(0xffffffffu, alpha[0] != 1.0f || alpha[1] != 1.0f)) {
+#pragma unroll
+        for (int dn = 0; dn < DMAX / 8; ++dn) {
+            o[dn][0] *= alpha[0]; o[dn][1] *= alpha[0]; o[dn][2] *= alpha[1]; o[dn][3] *= alpha[1];
+        }
+    }
+    uint32_t pa[4] = {pack_bf16(s[0][0], s[0][1]), pack_bf16(s[0][2], s[0][3]), pack_bf16(s[1][0], s[1][1]), pack_bf16(s[1][2], s[1][3])};
+    // V (transposed on load): matrices 0,1 = keys slab.., slab+8.. at column block dn, matrices 2,3 at dn+1
+    uint32_t vrow = vs + (uint32_t)(slab + (mi & 1) * 8 + rr) * 128u;
+#pragma unroll
+    for (int dn = 0; dn < DMAX / 8; dn += 2) {
+        if (dn * 8 < d) {
+            uint32_t vb[4];
+            uint32_t chunk = (uint32_t)(dn + (mi >> 1));
+            ldmatrix_x4_trans_addr(vb, vrow + (chunk >> 3) * 8192u + (((chunk & 7u) ^ (uint32_t)rr) << 4));
+            mma16816(o[dn], pa, vb[0], vb[1]);
+            mma16816(o[dn + 1], pa, vb[2], vb[3]);
+        }
+    }
+}
+
+template <int DMAX, int ST>
+__global__ void __launch_bounds__(AMT_THREADS) attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k,
+                                                                          const __grid_constant__ CUtensorMap map_v,
+                                                                          MmaAttnArgs a, int box_rows) {
+    ce_pdl_begin();
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    __shared__ __align__(8) uint64_t full_bar[ST], empty_bar[ST];
+    int b = blockIdx.x / a.max_splits, split = blockIdx.x % a.max_splits;
+    int kvh = blockIdx.y, hg = blockIdx.z;
+    int G = a.nh / a.nkv;
+    int t = b;
+    int pos = a.positions[t];
+    int lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
+    int k_begin = split * a.split, k_end = min(k_begin + a.split, pos + 1);
+    if (k_begin > pos || k_end <= lo) return;     // the merge kernel skips these splits too
+    const int* table = a.block_table + (size_t)a.seq_slot[b] * a.max_pages;
+    int d = a.d, panels = d >> 6;
+    uint32_t base = (amt_smem(smem_raw) + 1023u) & ~1023u;        // the swizzle is keyed on address bits
+    unsigned char* tiles = smem_raw + (base - amt_smem(smem_raw));
+    uint32_t kv_bytes = (uint32_t)panels * 8192u;                 // K (or V) of one stage
+    uint32_t stage_bytes = 2u * kv_bytes;
+    int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, quad = lane & 3, grp = lane >> 2;
+    int n_tiles = (k_end - k_begin + AM_TILE - 1) / AM_TILE;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < ST; ++s) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(amt_smem(&full_bar[s])), "r"(1));
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(amt_smem(&empty_bar[s])), "r"(4));
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    if (warp == 4) {
+        // ---- producer
+        if (lane == 0) {
+            int shift = 31 - __clz(a.page_size);
+            int s = 0;
+            uint32_t ph = 0;
+            bool wrapped = false, ok = true;
+            for (int it = 0; it < n_tiles && ok; ++it) {
+                if (wrapped) ok = amt_wait(&empty_bar[s], ph ^ 1);
+                if (!ok) { atomicExch(a.status, 7); break; }
+                int k0 = k_begin + it * AM_TILE;
+                // the pieces of this tile that hold a visible key
+                int first = 0, last = AM_TILE / box_rows - 1;
+                while (first < last && k0 + (first + 1) * box_rows <= lo) ++first;
+                while (last > first && k0 + last * box_rows > pos) --last;
+                uint32_t bar = amt_smem(&full_bar[s]);
+                uint32_t bytes = (uint32_t)(last - first + 1) * (uint32_t)box_rows * 128u * 2u * (uint32_t)panels;
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+                for (int j = first; j <= last; ++j) {
+                    int key = k0 + j * box_rows;
+                    int page = table[key >> shift];
+                    if (page < 0 || page >= a.num_pages) { atomicExch(a.status, 4); page = 0; }
+                    int row = (page * a.nkv + kvh) * a.page_size + (key & (a.page_size - 1));
+                    uint32_t dst = base + (uint32_t)s * stage_bytes + (uint32_t)(j * box_rows) * 128u;
+                    for (int pn = 0; pn < panels; ++pn) {
+                        asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                                     ::"r"(dst + (uint32_t)pn * 8192u), "l"(&map_k), "r"(bar), "r"(pn * 64), "r"(row) : "memory");
+                        asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                                     ::"r"(dst + kv_bytes + (uint32_t)pn * 8192u), "l"(&map_v), "r"(bar), "r"(pn * 64), "r"(row) : "memory");
+                    }
+                }
+                if (++s == ST) { s = 0; ph ^= 1; wrapped = true; }
+            }
+        }
+        return;       // the computing warps wait for every copy before they leave the loop
+    }
+
+    int heads_here = min(16, G - hg * 16);
+    uint32_t qf[DMAX / 16][4];
+    {
+        int h0 = kvh * G + hg * 16;
+        const bf16* q0 = a.q + (size_t)t * a.q_stride + (size_t)(h0 + grp) * d;
+        const bf16* q1 = q0 + (size_t)8 * d;
+        bool v0 = grp < heads_here, v1 = grp + 8 < heads_here;
+#pragma unroll
+        for (int kk = 0; kk < DMAX / 16; ++kk) {
+            int col = kk * 16 + 2 * quad;
+            bool in = kk * 16 < d;
+            qf[kk][0] = (in && v0) ? *reinterpret_cast<const uint32_t*>(q0 + col) : 0u;
+            qf[kk][1] = (in && v1) ? *reinterpret_cast<const uint32_t*>(q1 + col) : 0u;
+            qf[kk][2] = (in && v0) ? *reinterpret_cast<const uint32_t*>(q0 + col + 8) : 0u;
+            qf[kk][3] = (in && v1) ? *reinterpret_cast<const uint32_t*>(q1 + col + 8) : 0u;
+        }
+    }
+    float o[DMAX / 8][4];
+#pragma unroll
+    for (int i = 0; i < DMAX / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+
+    {
+        int s = 0;
+        uint32_t ph = 0;
+        bool ok = true;
+        for (int it = 0; it < n_tiles; ++it) {
+            if (ok) ok = amt_wait(&full_bar[s], ph);
+            if (!ok) { if (lane == 0) atomicExch(a.status, 7); break; }
+            int k0 = k_begin + it * AM_TILE + warp * 16;
+            if (k0 <= pos && k0 + 15 >= lo) {
+                uint32_t ks = base + (uint32_t)s * stage_bytes, vs = ks + kv_bytes;
+                if (k0 >= lo && k0 + 15 <= pos) {
+                    warp_tile_swz<DMAX, false>(qf, o, m, l, ks, vs, warp * 16, d, k0, lo, pos, a.scale_log2);
+                } else {
+                    // zero the V rows of this warp's keys that are not visible (16 bytes a lane and step)
+                    for (int c = lane; c < 16 * panels * 8; c += 32) {
+                        int r = c / (panels * 8), rest = c - r * (panels * 8);
+                        int key = k0 + r;
+                        if (key < lo || key > pos)
+                            *reinterpret_cast<uint4*>(tiles + (size_t)s * stage_bytes + kv_bytes + (size_t)(rest >> 3) * 8192 +
+                                                      (size_t)(warp * 16 + r) * 128 + (size_t)(rest & 7) * 16) = make_uint4(0, 0, 0, 0);
+                    }
+                    __syncwarp();
+                    warp_tile_swz<DMAX, true>(qf, o, m, l, ks, vs, warp * 16, d, k0, lo, pos, a.scale_log2);
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // before a later copy overwrites these rows
+                }
+            }
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(amt_smem(&empty_bar[s])) : "memory");
+            if (++s == ST) { s = 0; ph ^= 1; }
+        }
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");       // every warp is done with the staged tiles
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+    }
+    // combine the 4 warps through shared memory (the staging buffers are free now)
+    float* so = reinterpret_cast<float*>(tiles);             // [4][16][d]
+    float* sm = so + 4 * 16 * d;                             // [4][16]
+    float* sl = sm + 64;                                     // [4][16]
+#pragma unroll
+    for (int dn = 0; dn < DMAX / 8; ++dn) {
+        if (dn * 8 < d) {
+            int col = dn * 8 + 2 * quad;
+            so[(warp * 16 + grp) * d + col] = o[dn][0];
+            so[(warp * 16 + grp) * d + col + 1] = o[dn][1];
+            so[(warp * 16 + grp + 8) * d + col] = o[dn][2];
+            so[(warp * 16 + grp + 8) * d + col + 1] = o[dn][3];
+        }
+    }
+    if (quad == 0) {
+        sm[warp * 16 + grp] = m[0]; sm[warp * 16 + grp + 8] = m[1];
+        sl[warp * 16 + grp] = l[0]; sl[warp * 16 + grp + 8] = l[1];
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    for (int e = threadIdx.x; e < heads_here * d; e += 128) {
+        int r = e / d, col = e - r * d;
+        float M = fmaxf(fmaxf(sm[r], sm[16 + r]), fmaxf(sm[32 + r], sm[48 + r]));
+        float acc = 0.f, L = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            float f = sm[w * 16 + r] == -INFINITY ? 0.f : exp2f(sm[w * 16 + r] - M);
+            acc += so[(w * 16 + r) * d + col] * f;
+            L += sl[w * 16 + r] * f;
+        }
+        int h = kvh * G + hg * 16 + r;
+        size_t pb = ((size_t)b * a.nh + h) * a.max_splits + split;
+        a.part_o[pb * d + col] = acc;
+        if (col == 0) {
+            a.part_ml[pb * 2] = M;
+            a.part_ml[pb * 2 + 1] = L;
+        }
+    }
+}
+
 // grid (n_seqs, nh), one warp per 32 output columns: out[t, h, :] = sum_s O_s w_s with
 // w_s = 2^(m_s - M) / sum_s l_s 2^(m_s - M).  The weights are computed once per block by warp 0
 // (lanes over splits, fixed shuffle order), then every thread adds its column in split order.
@@ -546,6 +827,11 @@ extern "C" int ce_attention_decode_split() { return AM_SPLIT; }
 // Kernels one decode attention call launches: 1 when the last block merges the splits, else 2.
 extern "C" int ce_attention_decode_kernels() { return getenv("CE_ATTN_FUSED_MERGE") ? 1 : 2; }
 
+// The TMA-staged decode kernel takes head sizes of 64, 128, 192, 256 and pages of a power of two >= 8.
+extern "C" int ce_attention_decode_tma_supported(int d, int page_size) {
+    return d >= 64 && d <= 256 && d % 64 == 0 && page_size >= 8 && (page_size & (page_size - 1)) == 0;
+}
+
 extern "C" int ce_attention_decode_bf16(const void* q, const void* k_pool, const void* v_pool, void* out, float* scratch,
                                         int* counters, int n_counters, const int* positions, const int* seq_slot, const int* q_start,
                                         const int* ctx_len, const int* block_table, int* status, int n_seqs, int nh,
@@ -566,14 +852,23 @@ extern "C" int ce_attention_decode_bf16(const void* q, const void* k_pool, const
     a.max_pages = max_pages; a.num_pages = num_pages; a.window = window;
     a.scale_log2 = scale * 1.4426950408889634f;
     int G = nh / nkv;
-    // Splits of AM_SPLIT positions; when that makes more than about four waves of blocks, splits of
-    // twice the size (fewer blocks, fewer partial results: measured faster at large batches).  The
-    // choice depends on the number of one-token sequences and on max_splits, not on their contents.
-    a.split = AM_SPLIT;
-    a.max_splits = max_splits;
-    if ((long long)n_seqs * nkv * ((G + 15) / 16) * max_splits > 1200 && max_splits > 1) {
-        a.split = 2 * AM_SPLIT;
-        a.max_splits = (max_splits + 1) / 2;
+    // Split size: a multiple m of AM_SPLIT.  A block has a fixed cost (launch, the chain of loads that
+    // leads to its first tile, combining its warps, writing a partial) worth about six tiles of work, and
+    // blocks run in waves of `slots`; m minimises waves x (tiles of a block + 6).  Few sequences get many
+    // short splits that fill one wave; many sequences get one block each.  The choice depends on the
+    // number of one-token sequences and on max_splits, not on their contents.
+    {
+        long long pairs = (long long)n_seqs * nkv * ((G + 15) / 16);
+        long long slots = 2LL * ce_sm_count();
+        long long best = -1;
+        int best_m = 1;
+        for (int m = 1; m <= max_splits; ++m) {
+            long long blocks = pairs * ((max_splits + m - 1) / m);
+            long long cost = ((blocks + slots - 1) / slots) * ((long long)m * (AM_SPLIT / AM_TILE) + 6);
+            if (best < 0 || cost < best) { best = cost; best_m = m; }
+        }
+        a.split = best_m * AM_SPLIT;
+        a.max_splits = (max_splits + best_m - 1) / best_m;
     }
     max_splits = a.max_splits;
     // A merge kernel combines the splits.  CE_ATTN_FUSED_MERGE=1 lets the last block of a (sequence,
@@ -584,8 +879,35 @@ extern "C" int ce_attention_decode_bf16(const void* q, const void* k_pool, const
     if ((long long)n_seqs * nkv * grid.z > n_counters)
         return ce_fail(CE_ERR_ARG, "ce_attention_decode_bf16: %lld counters needed, %d given", (long long)n_seqs * nkv * grid.z, n_counters);
     a.counters = counters;
-    size_t smem = stage_bytes(d);
     size_t comb = (size_t)(4 * 16 * d + 128) * sizeof(float);
+    static int use_tma = getenv("CE_ATTN_NO_TMA") ? 0 : 1;
+    if (use_tma && ce_attention_decode_tma_supported(d, page_size) && !a.fused_merge) {
+        // staged by TMA: pieces of min(page, 64) rows x 64 columns
+        int box_rows = page_size < AM_TILE ? page_size : AM_TILE;
+        long long pool_rows = (long long)num_pages * nkv * page_size;
+        CUtensorMap mk, mv;
+        if ((rc = ce_tensor_map_bf16(k_pool, pool_rows, d, d, box_rows, &mk, "ce_attention_decode_bf16"))) return rc;
+        if ((rc = ce_tensor_map_bf16(v_pool, pool_rows, d, d, box_rows, &mv, "ce_attention_decode_bf16"))) return rc;
+        bool deep3 = d <= 128;          // registers allow two blocks an SM either way; three stages fit beside each other
+        size_t stage = (size_t)2 * (d / 64) * 8192;
+        size_t tsmem = (deep3 ? 3 : 2) * stage;
+        if (comb > tsmem) tsmem = comb;
+        tsmem += 1024;
+#define AMT_CASE(DM)                                                                                                   \
+        if (deep3) {                                                                                                   \
+            if ((rc = set_smem(attention_decode_tma_kernel<DM, 3>, tsmem, "ce_attention_decode_bf16"))) return rc;     \
+            ce_launch(attention_decode_tma_kernel<DM, 3>, grid, AMT_THREADS, tsmem, stream, mk, mv, a, box_rows);      \
+        } else {                                                                                                       \
+            if ((rc = set_smem(attention_decode_tma_kernel<DM, 2>, tsmem, "ce_attention_decode_bf16"))) return rc;     \
+            ce_launch(attention_decode_tma_kernel<DM, 2>, grid, AMT_THREADS, tsmem, stream, mk, mv, a, box_rows);      \
+        }
+        if (d == 64) { AMT_CASE(64) } else if (d == 128) { AMT_CASE(128) } else { AMT_CASE(256) }
+#undef AMT_CASE
+        if ((rc = ce_check_launch("ce_attention_decode_bf16"))) return rc;
+        ce_launch(attention_merge_kernel, dim3(n_seqs, nh), d >= 128 ? 128 : (d + 31) / 32 * 32, max_splits * sizeof(float), stream, a);
+        return ce_check_launch("ce_attention_decode_bf16 (merge)");
+    }
+    size_t smem = stage_bytes(d);
     if (comb > smem) smem = comb;
     // Few blocks: three staging buffers each (loads run further ahead).  Many blocks: two, so that three
     // blocks share an SM (measured: 4.67 vs 4.83 ms a step at batch 8, 5990 vs 5630 tokens/s at batch 64).

@@ -20,7 +20,7 @@
 // kernel of attention_mma.cu.  (The reference's counterpart is flash_prefill_tc,
 // src/kernels/attention_tc.cu:180-565, on mma.sync m16n8k16.)
 #include "common.cuh"
-#include <cuda.h>
+#include "tensor_map.h"
 #include <mutex>
 #include <unordered_map>
 
@@ -409,56 +409,9 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_tc_kernel(const __g
 }
 
 // ---- host side ------------------------------------------------------------------------------------
-typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-EncodeTiled encode_fn() {
-    static EncodeTiled fn = nullptr;
-    static std::once_flag once;
-    std::call_once(once, [] {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiled)p;
-    });
-    return fn;
-}
-
-struct MapKey {
-    const void* ptr; long long rows, cols, ld; int box_rows;
-    bool operator==(const MapKey& o) const { return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows; }
-};
-struct MapHash {
-    size_t operator()(const MapKey& k) const {
-        size_t hsh = (size_t)k.ptr;
-        for (long long v : {k.rows, k.cols, k.ld, (long long)k.box_rows}) hsh = hsh * 1000003u ^ (size_t)v;
-        return hsh;
-    }
-};
 // bf16 matrix [rows, cols], row stride ld elements, boxes of box_rows x 64 columns, 128-byte swizzle
 int get_map(const void* ptr, long long rows, long long cols, long long ld, int box_rows, CUtensorMap* out) {
-    static std::unordered_map<MapKey, CUtensorMap, MapHash> cache;
-    static std::mutex mu;
-    MapKey key{ptr, rows, cols, ld, box_rows};
-    std::lock_guard<std::mutex> lock(mu);
-    auto it = cache.find(key);
-    if (it != cache.end()) { *out = it->second; return CE_OK; }
-    EncodeTiled enc = encode_fn();
-    if (!enc) return ce_fail(CE_ERR_CUDA, "ce_attention_prefill_tc: cuTensorMapEncodeTiled is not available in this driver");
-    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-    cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
-    cuuint32_t elem[2] = {1, 1};
-    CUtensorMap m;
-    CUresult r = enc(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
-                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return ce_fail(CE_ERR_CUDA, "ce_attention_prefill_tc: cuTensorMapEncodeTiled failed (%d)", (int)r);
-    if (cache.size() > 4096) cache.clear();
-    cache.emplace(key, m);
-    *out = m;
-    return CE_OK;
+    return ce_tensor_map_bf16(ptr, rows, cols, ld, box_rows, out, "ce_attention_prefill_tc");
 }
 
 template <int D>

@@ -46,6 +46,7 @@ inline cudaError_t ce_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, si
 }
 int ce_fail(int code, const char* fmt, ...);
 int ce_check_launch(const char* what);
+int ce_sm_count();
 
 template <typename T> struct CeType;
 template <> struct CeType<float> {

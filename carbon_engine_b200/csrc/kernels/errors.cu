@@ -41,3 +41,14 @@ bool ce_pdl_enabled() {
     return g_pdl != 0;
 }
 extern "C" void ce_set_pdl(int on) { g_pdl = on ? 1 : 0; }
+
+// Multiprocessors of the current device (asked once).
+int ce_sm_count() {
+    static int n = 0;
+    if (n == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    }
+    return n;
+}

@@ -19,7 +19,7 @@
 // The reference calls a library (cuBLAS through candle) for these products and runs the residual
 // add, SiLU and multiply as separate kernels (src/model/layers.rs:441, 625-648).
 #include "common.cuh"
-#include <cuda.h>
+#include "tensor_map.h"
 #include <mutex>
 #include <stdio.h>
 #include <stdlib.h>
@@ -737,58 +737,9 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_pair_kernel(const __grid_cons
 }
 
 // ---- host side ------------------------------------------------------------------------------------
-typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiled encode_fn() {
-    static EncodeTiled fn = nullptr;
-    static std::once_flag once;
-    std::call_once(once, [] {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiled)p;
-    });
-    return fn;
-}
-
-struct MapKey {
-    const void* ptr; long long rows, cols, ld; int box_rows;
-    bool operator==(const MapKey& o) const { return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows; }
-};
-struct MapHash {
-    size_t operator()(const MapKey& k) const {
-        size_t h = (size_t)k.ptr;
-        for (long long v : {k.rows, k.cols, k.ld, (long long)k.box_rows}) h = h * 1000003u ^ (size_t)v;
-        return h;
-    }
-};
-
-// A tensor map of a row-major bf16 matrix [rows, cols] with row stride ld, boxes of box_rows x 64.
+// bf16 matrix [rows, cols], row stride ld elements, boxes of box_rows x 64 columns, 128-byte swizzle
 int get_map(const void* ptr, long long rows, long long cols, long long ld, int box_rows, CUtensorMap* out) {
-    static std::unordered_map<MapKey, CUtensorMap, MapHash> cache;
-    static std::mutex mu;
-    MapKey key{ptr, rows, cols, ld, box_rows};
-    std::lock_guard<std::mutex> lock(mu);
-    auto it = cache.find(key);
-    if (it != cache.end()) { *out = it->second; return CE_OK; }
-    EncodeTiled enc = encode_fn();
-    if (!enc) return ce_fail(CE_ERR_CUDA, "ce_gemm_tc: cuTensorMapEncodeTiled is not available in this driver");
-    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
-    cuuint32_t elem[2] = {1, 1};
-    CUtensorMap m;
-    CUresult r = enc(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
-                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return ce_fail(CE_ERR_CUDA, "ce_gemm_tc: cuTensorMapEncodeTiled failed (%d)", (int)r);
-    if (cache.size() > 4096) cache.clear();
-    cache.emplace(key, m);
-    *out = m;
-    return CE_OK;
+    return ce_tensor_map_bf16(ptr, rows, cols, ld, box_rows, out, "ce_gemm_tc");
 }
 
 template <int BN, int NACC>
@@ -813,16 +764,6 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, const TcArgs& a, dim3 g
     return ce_check_launch("ce_gemm_tc");
 }
 
-int sm_count() {
-    static int n = 0;
-    if (n == 0) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-    }
-    return n;
-}
-
 template <int BN, int NACC>
 int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, const TcArgs& a, int tiles_n, int tiles_m, cudaStream_t stream) {
     constexpr size_t stage = NACC * BM * BK * 2 + BN * BK * 2;
@@ -836,7 +777,7 @@ int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, const TcArgs
         attr_set = true;
     }
     long long total = (long long)tiles_n * tiles_m;
-    int grid = (int)(total < sm_count() ? total : sm_count());
+    int grid = (int)(total < ce_sm_count() ? total : ce_sm_count());
     ce_launch(gemm_tc_persistent_kernel<BN, NACC>, grid, THREADS, smem, stream, mw, mx, a, stages, tiles_n, tiles_m);
     return ce_check_launch("ce_gemm_tc (persistent)");
 }
@@ -855,7 +796,7 @@ int launch_pair(const CUtensorMap& mw, const CUtensorMap& mx, const TcArgs& a, i
     }
     long long total = (long long)tiles_n * tiles_m;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(2 * (sm_count() / 2));
+    cfg.gridDim = dim3(2 * (ce_sm_count() / 2));
     cfg.blockDim = dim3(THREADS);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;

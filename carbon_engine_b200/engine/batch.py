@@ -93,7 +93,7 @@ class StepContext:
         self.n_tiles = 0                     # 64-token tiles of the sequences that bring more than one token
         self.tiles128 = bufs.dev_section("tiles128")
         self.n_tiles128 = 0                  # the same in tiles of 128 tokens (tcgen05 attention)
-        self.decode_splits = 1               # grid size of the split-KV decode kernel: >= ceil(longest decode context / 256)
+        self.decode_splits = 1               # grid size of the split-KV decode kernel: >= ceil(longest decode context / positions per split)
         self._scratch = {}
         self.n_decode = 0                    # the first n_decode sequences bring exactly one token
         self.max_position = 0

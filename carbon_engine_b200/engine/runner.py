@@ -29,6 +29,15 @@ _STATUS = {
 }
 
 
+def _split_bucket(splits: int) -> int:
+    """Round a split count up to the next value with at most three significant bits (1..8, 10, 12, 14,
+    16, 20, ...): a graph per bucket, and a grid at most a quarter larger than the contexts need."""
+    step = 1
+    while splits > 8 * step:
+        step *= 2
+    return (splits + step - 1) // step * step
+
+
 class ModelRunner:
     def __init__(self, model, storage: CacheStorage, max_step_tokens: int):
         self.model, self.storage = model, storage
@@ -187,9 +196,7 @@ class ModelRunner:
         return self.graphs_enabled
 
     def _replay_decode(self, ctx: StepContext, rows: torch.Tensor) -> torch.Tensor:
-        bucket = 1
-        while bucket < ctx.decode_splits:
-            bucket *= 2
+        bucket = _split_bucket(ctx.decode_splits)
         ctx.decode_splits = bucket          # a larger grid, the same result
         key = (ctx.B, bucket)
         entry = self._graphs.get(key)

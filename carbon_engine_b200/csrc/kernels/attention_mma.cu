@@ -418,80 +418,88 @@ __device__ __forceinline__ void ldmatrix_x4_trans_addr(uint32_t (&r)[4], uint32_
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
 }
 
-// One warp: its 16 keys (rows slab .. slab+15 of the staged tile) against the 16 query rows.
+// One warp: its 16 keys (rows slab .. slab+15 of the staged tile) against up to 8 query heads, with the
+// KEYS as the 16 rows of the MMA tile and the heads as its 8 columns: S^T = K Q^T and O^T = V^T P^T.  A
+// group of 4 heads wastes half of a tile this way, not three quarters, and the products take half as
+// many mma.sync instructions, which is what bounds this kernel.  A thread's score fragment holds keys
+// lane/4 and lane/4 + 8 for heads 2*(lane%4) and 2*(lane%4) + 1; its running maxima, sums and output
+// columns are for those two heads.
 // ks, vs: shared addresses of the stage's K and V; each is d/64 panels of [64 keys][128 bytes], swizzled.
 template <int DMAX, bool MASK>
-__device__ __forceinline__ void warp_tile_swz(const uint32_t (&qf)[DMAX / 16][4], float (&o)[DMAX / 8][4], float (&m)[2],
+__device__ __forceinline__ void warp_tile_swz(const uint32_t (&qf)[DMAX / 16][2], float (&o)[DMAX / 16][4], float (&m)[2],
                                               float (&l)[2], uint32_t ks, uint32_t vs, int slab, int d, int key_base,
                                               int lo, int hi, float scale_log2) {
-    int lane = threadIdx.x & 31, quad = lane & 3;
+    int lane = threadIdx.x & 31, quad = lane & 3, grp = lane >> 2;
     int mi = lane >> 3, rr = lane & 7;
-    float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-    float s2[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-    // K: matrices 0,1 = keys slab..slab+7 (columns +0, +8), matrices 2,3 = keys slab+8..slab+15
-    uint32_t krow = ks + (uint32_t)(slab + (mi >> 1) * 8 + rr) * 128u;
+    float s[4] = {0.f, 0.f, 0.f, 0.f}, s2[4] = {0.f, 0.f, 0.f, 0.f}, s3[4] = {0.f, 0.f, 0.f, 0.f}, s4[4] = {0.f, 0.f, 0.f, 0.f};
+    // K as the A operand: matrices 0,1 = keys slab.., slab+8.. at columns +0; matrices 2,3 at columns +8
+    uint32_t krow = ks + (uint32_t)(slab + (mi & 1) * 8 + rr) * 128u;
 #pragma unroll
     for (int kk = 0; kk < DMAX / 16; ++kk) {
         if (kk * 16 < d) {
-            uint32_t kb[4];
-            uint32_t chunk = (uint32_t)((kk & 3) * 2 + (mi & 1));
-            ldmatrix_x4_addr(kb, krow + (uint32_t)(kk >> 2) * 8192u + ((chunk ^ (uint32_t)rr) << 4));
-            if (kk & 1) { mma16816(s2[0], qf[kk], kb[0], kb[1]); mma16816(s2[1], qf[kk], kb[2], kb[3]); }
-            else { mma16816(s[0], qf[kk], kb[0], kb[1]); mma16816(s[1], qf[kk], kb[2], kb[3]); }
+            uint32_t ka[4];
+            uint32_t chunk = (uint32_t)((kk & 3) * 2 + (mi >> 1));
+            ldmatrix_x4_addr(ka, krow + (uint32_t)(kk >> 2) * 8192u + ((chunk ^ (uint32_t)rr) << 4));
+            // four chains of accumulators: an MMA waits for the one four steps before it, not for the last
+            if ((kk & 3) == 0) mma16816(s, ka, qf[kk][0], qf[kk][1]);
+            else if ((kk & 3) == 1) mma16816(s2, ka, qf[kk][0], qf[kk][1]);
+            else if ((kk & 3) == 2) mma16816(s3, ka, qf[kk][0], qf[kk][1]);
+            else mma16816(s4, ka, qf[kk][0], qf[kk][1]);
         }
     }
 #pragma unroll
-    for (int e = 0; e < 4; ++e) { s[0][e] += s2[0][e]; s[1][e] += s2[1][e]; }
-    float mx[2] = {-INFINITY, -INFINITY};
-#pragma unroll
-    for (int j = 0; j < 2; ++j) {
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            if (MASK) {
-                int key = key_base + j * 8 + 2 * quad + (e & 1);
-                if (!(key >= lo && key <= hi)) s[j][e] = -INFINITY;
-            }
-            mx[e >> 1] = fmaxf(mx[e >> 1], s[j][e]);
-        }
+    for (int e = 0; e < 4; ++e) s[e] = (s[e] + s2[e]) + (s3[e] + s4[e]);
+    if (MASK) {
+        int k_a = key_base + grp, k_b = k_a + 8;
+        if (!(k_a >= lo && k_a <= hi)) s[0] = s[1] = -INFINITY;
+        if (!(k_b >= lo && k_b <= hi)) s[2] = s[3] = -INFINITY;
     }
+    // maxima over the 16 keys: within the thread, then over the 8 threads that share lane % 4
+    float mx[2] = {fmaxf(s[0], s[2]), fmaxf(s[1], s[3])};
     float alpha[2], muse[2];
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
-        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
-        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 4));
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 8));
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 16));
         float mn = fmaxf(m[r], mx[r] * scale_log2);
         muse[r] = mn == -INFINITY ? 0.f : mn;
         alpha[r] = exp2f(m[r] - muse[r]);
         m[r] = mn;
         l[r] *= alpha[r];
     }
+    float p[4];
 #pragma unroll
-    for (int j = 0; j < 2; ++j) {
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            float p = exp2f(fmaf(s[j][e], scale_log2, -muse[e >> 1]));
-            s[j][e] = p;
-            l[e >> 1] += p;
-        }
+    for (int e = 0; e < 4; ++e) {
+        p[e] = exp2f(fmaf(s[e], scale_log2, -muse[e & 1]));
+        l[e & 1] += p[e];                       // this thread's keys only: the 8 partial sums are added at the end
     }
-    // most tiles move no row's maximum: then every alpha is exactly 1 and the output needs no rescaling
+    // most tiles move no head's maximum: then every alpha is exactly 1 and the output needs no rescaling
     if (__any_sync(0xffffffffu, alpha[0] != 1.0f || alpha[1] != 1.0f)) {
 #pragma unroll
-        for (int dn = 0; dn < DMAX / 8; ++dn) {
-            o[dn][0] *= alpha[0]; o[dn][1] *= alpha[0]; o[dn][2] *= alpha[1]; o[dn][3] *= alpha[1];
+        for (int dn = 0; dn < DMAX / 16; ++dn) {
+            o[dn][0] *= alpha[0]; o[dn][1] *= alpha[1]; o[dn][2] *= alpha[0]; o[dn][3] *= alpha[1];
         }
     }
-    uint32_t pa[4] = {pack_bf16(s[0][0], s[0][1]), pack_bf16(s[0][2], s[0][3]), pack_bf16(s[1][0], s[1][1]), pack_bf16(s[1][2], s[1][3])};
-    // V (transposed on load): matrices 0,1 = keys slab.., slab+8.. at column block dn, matrices 2,3 at dn+1
-    uint32_t vrow = vs + (uint32_t)(slab + (mi & 1) * 8 + rr) * 128u;
+    // P^T as the B operand: this thread needs head lane/4 at keys 2q, 2q+1 (b0) and 2q+8, 2q+9 (b1), q = lane%4.
+    // Key 2q (+8) lies in the thread with lane/4 = 2q, key 2q+1 (+8) in the one with lane/4 = 2q+1; both
+    // hold the head pair (lane/4)/2 when their lane%4 equals that; the head's parity picks the half.
+    uint32_t p01 = pack_bf16(p[0], p[1]), p23 = pack_bf16(p[2], p[3]);
+    int src_a = ((2 * quad) << 2) | (grp >> 1), src_b = ((2 * quad + 1) << 2) | (grp >> 1);
+    uint32_t a01 = __shfl_sync(0xffffffffu, p01, src_a), a23 = __shfl_sync(0xffffffffu, p23, src_a);
+    uint32_t b01 = __shfl_sync(0xffffffffu, p01, src_b), b23 = __shfl_sync(0xffffffffu, p23, src_b);
+    uint32_t sel = (grp & 1) ? 0x7632u : 0x5410u;       // high halves or low halves of (x, y)
+    uint32_t pb0 = __byte_perm(a01, b01, sel), pb1 = __byte_perm(a23, b23, sel);
+    // V^T as the A operand (transposed on load): matrices 0,1 = keys slab..+7 at d columns +0, +8;
+    // matrices 2,3 = keys slab+8..+15 at d columns +0, +8
+    uint32_t vrow = vs + (uint32_t)(slab + (mi >> 1) * 8 + rr) * 128u;
 #pragma unroll
-    for (int dn = 0; dn < DMAX / 8; dn += 2) {
-        if (dn * 8 < d) {
-            uint32_t vb[4];
-            uint32_t chunk = (uint32_t)(dn + (mi >> 1));
-            ldmatrix_x4_trans_addr(vb, vrow + (chunk >> 3) * 8192u + (((chunk & 7u) ^ (uint32_t)rr) << 4));
-            mma16816(o[dn], pa, vb[0], vb[1]);
-            mma16816(o[dn + 1], pa, vb[2], vb[3]);
+    for (int dn = 0; dn < DMAX / 16; ++dn) {
+        if (dn * 16 < d) {
+            uint32_t va[4];
+            uint32_t chunk = (uint32_t)(dn * 2 + (mi & 1));
+            ldmatrix_x4_trans_addr(va, vrow + (chunk >> 3) * 8192u + (((chunk & 7u) ^ (uint32_t)rr) << 4));
+            mma16816(o[dn], va, pb0, pb1);
         }
     }
 }
@@ -500,7 +508,12 @@ template <int DMAX, int ST>
 __global__ void __launch_bounds__(AMT_THREADS) attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k,
                                                                           const __grid_constant__ CUtensorMap map_v,
                                                                           MmaAttnArgs a, int box_rows) {
-    ce_pdl_begin();
+    // Dependent launch: positions, sequence slots and block tables are inputs of the step (complete
+    // before its first kernel may start), and every key but the newest was written by earlier steps.  So
+    // the block looks up its pages and starts the copies of all tiles except the one that holds the
+    // newest key while the kernels before it still run; only that tile, the query and everything the
+    // block writes wait for them.
+    ce_pdl_launch_dependents();
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     __shared__ __align__(8) uint64_t full_bar[ST], empty_bar[ST];
     int b = blockIdx.x / a.max_splits, split = blockIdx.x % a.max_splits;
@@ -535,11 +548,12 @@ __global__ void __launch_bounds__(AMT_THREADS) attention_decode_tma_kernel(const
             int shift = 31 - __clz(a.page_size);
             int s = 0;
             uint32_t ph = 0;
-            bool wrapped = false, ok = true;
+            bool wrapped = false, ok = true, waited = false;
             for (int it = 0; it < n_tiles && ok; ++it) {
                 if (wrapped) ok = amt_wait(&empty_bar[s], ph ^ 1);
                 if (!ok) { atomicExch(a.status, 7); break; }
                 int k0 = k_begin + it * AM_TILE;
+                if (!waited && k0 + AM_TILE > pos) { ce_pdl_wait(); waited = true; }   // the newest key is written by the kernel before this one
                 // the pieces of this tile that hold a visible key
                 int first = 0, last = AM_TILE / box_rows - 1;
                 while (first < last && k0 + (first + 1) * box_rows <= lo) ++first;
@@ -566,26 +580,24 @@ __global__ void __launch_bounds__(AMT_THREADS) attention_decode_tma_kernel(const
         return;       // the computing warps wait for every copy before they leave the loop
     }
 
-    int heads_here = min(16, G - hg * 16);
-    uint32_t qf[DMAX / 16][4];
+    int heads_here = min(8, G - hg * 8);
+    ce_pdl_wait();
+    // Q^T as the B operand: head lane/4, columns kk*16 + 2*(lane%4) (+1) and + 8 (+9)
+    uint32_t qf[DMAX / 16][2];
     {
-        int h0 = kvh * G + hg * 16;
-        const bf16* q0 = a.q + (size_t)t * a.q_stride + (size_t)(h0 + grp) * d;
-        const bf16* q1 = q0 + (size_t)8 * d;
-        bool v0 = grp < heads_here, v1 = grp + 8 < heads_here;
+        const bf16* q0 = a.q + (size_t)t * a.q_stride + (size_t)(kvh * G + hg * 8 + grp) * d;
+        bool v0 = grp < heads_here;
 #pragma unroll
         for (int kk = 0; kk < DMAX / 16; ++kk) {
             int col = kk * 16 + 2 * quad;
             bool in = kk * 16 < d;
             qf[kk][0] = (in && v0) ? *reinterpret_cast<const uint32_t*>(q0 + col) : 0u;
-            qf[kk][1] = (in && v1) ? *reinterpret_cast<const uint32_t*>(q1 + col) : 0u;
-            qf[kk][2] = (in && v0) ? *reinterpret_cast<const uint32_t*>(q0 + col + 8) : 0u;
-            qf[kk][3] = (in && v1) ? *reinterpret_cast<const uint32_t*>(q1 + col + 8) : 0u;
+            qf[kk][1] = (in && v0) ? *reinterpret_cast<const uint32_t*>(q0 + col + 8) : 0u;
         }
     }
-    float o[DMAX / 8][4];
+    float o[DMAX / 16][4];      // O^T: rows d = dn*16 + lane/4 (+8), columns heads 2*(lane%4) (+1)
 #pragma unroll
-    for (int i = 0; i < DMAX / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    for (int i = 0; i < DMAX / 16; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
 
     {
@@ -621,40 +633,41 @@ __global__ void __launch_bounds__(AMT_THREADS) attention_decode_tma_kernel(const
     }
     asm volatile("bar.sync 1, 128;" ::: "memory");       // every warp is done with the staged tiles
 #pragma unroll
-    for (int r = 0; r < 2; ++r) {
-        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
-        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+    for (int r = 0; r < 2; ++r) {              // the sums of the 8 threads that share a head pair
+        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 4);
+        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 8);
+        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 16);
     }
     // combine the 4 warps through shared memory (the staging buffers are free now)
-    float* so = reinterpret_cast<float*>(tiles);             // [4][16][d]
-    float* sm = so + 4 * 16 * d;                             // [4][16]
-    float* sl = sm + 64;                                     // [4][16]
+    float* so = reinterpret_cast<float*>(tiles);             // [4][8][d]
+    float* sm = so + 4 * 8 * d;                              // [4][8]
+    float* sl = sm + 32;                                     // [4][8]
 #pragma unroll
-    for (int dn = 0; dn < DMAX / 8; ++dn) {
-        if (dn * 8 < d) {
-            int col = dn * 8 + 2 * quad;
-            so[(warp * 16 + grp) * d + col] = o[dn][0];
-            so[(warp * 16 + grp) * d + col + 1] = o[dn][1];
-            so[(warp * 16 + grp + 8) * d + col] = o[dn][2];
-            so[(warp * 16 + grp + 8) * d + col + 1] = o[dn][3];
+    for (int dn = 0; dn < DMAX / 16; ++dn) {
+        if (dn * 16 < d) {
+            int row = dn * 16 + grp;
+            so[(warp * 8 + 2 * quad) * d + row] = o[dn][0];
+            so[(warp * 8 + 2 * quad + 1) * d + row] = o[dn][1];
+            so[(warp * 8 + 2 * quad) * d + row + 8] = o[dn][2];
+            so[(warp * 8 + 2 * quad + 1) * d + row + 8] = o[dn][3];
         }
     }
-    if (quad == 0) {
-        sm[warp * 16 + grp] = m[0]; sm[warp * 16 + grp + 8] = m[1];
-        sl[warp * 16 + grp] = l[0]; sl[warp * 16 + grp + 8] = l[1];
+    if (grp == 0) {
+        sm[warp * 8 + 2 * quad] = m[0]; sm[warp * 8 + 2 * quad + 1] = m[1];
+        sl[warp * 8 + 2 * quad] = l[0]; sl[warp * 8 + 2 * quad + 1] = l[1];
     }
     asm volatile("bar.sync 1, 128;" ::: "memory");
     for (int e = threadIdx.x; e < heads_here * d; e += 128) {
         int r = e / d, col = e - r * d;
-        float M = fmaxf(fmaxf(sm[r], sm[16 + r]), fmaxf(sm[32 + r], sm[48 + r]));
+        float M = fmaxf(fmaxf(sm[r], sm[8 + r]), fmaxf(sm[16 + r], sm[24 + r]));
         float acc = 0.f, L = 0.f;
 #pragma unroll
         for (int w = 0; w < 4; ++w) {
-            float f = sm[w * 16 + r] == -INFINITY ? 0.f : exp2f(sm[w * 16 + r] - M);
-            acc += so[(w * 16 + r) * d + col] * f;
-            L += sl[w * 16 + r] * f;
+            float f = sm[w * 8 + r] == -INFINITY ? 0.f : exp2f(sm[w * 8 + r] - M);
+            acc += so[(w * 8 + r) * d + col] * f;
+            L += sl[w * 8 + r] * f;
         }
-        int h = kvh * G + hg * 16 + r;
+        int h = kvh * G + hg * 8 + r;
         size_t pb = ((size_t)b * a.nh + h) * a.max_splits + split;
         a.part_o[pb * d + col] = acc;
         if (col == 0) {
@@ -852,14 +865,18 @@ extern "C" int ce_attention_decode_bf16(const void* q, const void* k_pool, const
     a.max_pages = max_pages; a.num_pages = num_pages; a.window = window;
     a.scale_log2 = scale * 1.4426950408889634f;
     int G = nh / nkv;
+    static int use_tma = getenv("CE_ATTN_NO_TMA") ? 0 : 1;
+    static int fused = getenv("CE_ATTN_FUSED_MERGE") ? 1 : 0;
+    bool tma = use_tma && !fused && ce_attention_decode_tma_supported(d, page_size);
+    int hgroup = tma ? 8 : 16;           // query heads of one KV head that a block takes
     // Split size: a multiple m of AM_SPLIT.  A block has a fixed cost (launch, the chain of loads that
     // leads to its first tile, combining its warps, writing a partial) worth about six tiles of work, and
     // blocks run in waves of `slots`; m minimises waves x (tiles of a block + 6).  Few sequences get many
     // short splits that fill one wave; many sequences get one block each.  The choice depends on the
     // number of one-token sequences and on max_splits, not on their contents.
     {
-        long long pairs = (long long)n_seqs * nkv * ((G + 15) / 16);
-        long long slots = 2LL * ce_sm_count();
+        long long pairs = (long long)n_seqs * nkv * ((G + hgroup - 1) / hgroup);
+        long long slots = 2LL * ce_sm_count();           // two blocks share an SM (shared memory of three stages each)
         long long best = -1;
         int best_m = 1;
         for (int m = 1; m <= max_splits; ++m) {
@@ -873,22 +890,22 @@ extern "C" int ce_attention_decode_bf16(const void* q, const void* k_pool, const
     max_splits = a.max_splits;
     // A merge kernel combines the splits.  CE_ATTN_FUSED_MERGE=1 lets the last block of a (sequence,
     // KV head) do it instead; measured slower (4.9 -> 5.0 ms a step at batch 8, 8B sizes), so it is off.
-    static int fused = getenv("CE_ATTN_FUSED_MERGE") ? 1 : 0;
     a.fused_merge = fused && (size_t)16 * max_splits * sizeof(float) <= 16 * 1024;
-    dim3 grid(n_seqs * max_splits, nkv, (G + 15) / 16);
-    if ((long long)n_seqs * nkv * grid.z > n_counters)
+    dim3 grid(n_seqs * max_splits, nkv, (G + hgroup - 1) / hgroup);
+    if (!tma && (long long)n_seqs * nkv * grid.z > n_counters)
         return ce_fail(CE_ERR_ARG, "ce_attention_decode_bf16: %lld counters needed, %d given", (long long)n_seqs * nkv * grid.z, n_counters);
     a.counters = counters;
     size_t comb = (size_t)(4 * 16 * d + 128) * sizeof(float);
-    static int use_tma = getenv("CE_ATTN_NO_TMA") ? 0 : 1;
-    if (use_tma && ce_attention_decode_tma_supported(d, page_size) && !a.fused_merge) {
+    if (tma) {
         // staged by TMA: pieces of min(page, 64) rows x 64 columns
         int box_rows = page_size < AM_TILE ? page_size : AM_TILE;
         long long pool_rows = (long long)num_pages * nkv * page_size;
         CUtensorMap mk, mv;
         if ((rc = ce_tensor_map_bf16(k_pool, pool_rows, d, d, box_rows, &mk, "ce_attention_decode_bf16"))) return rc;
         if ((rc = ce_tensor_map_bf16(v_pool, pool_rows, d, d, box_rows, &mv, "ce_attention_decode_bf16"))) return rc;
-        bool deep3 = d <= 128;          // registers allow two blocks an SM either way; three stages fit beside each other
+        // three stages: with two (and three blocks an SM) the computing warps wait for data (measured:
+        // 30 against 22 microseconds at batch 8)
+        bool deep3 = d <= 128;
         size_t stage = (size_t)2 * (d / 64) * 8192;
         size_t tsmem = (deep3 ? 3 : 2) * stage;
         if (comb > tsmem) tsmem = comb;

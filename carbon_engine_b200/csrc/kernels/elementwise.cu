@@ -379,7 +379,11 @@ extern "C" int ce_swiglu(const void* gu, void* out, int dtype, int T, int I, cud
 // ---------------------------------------------------------------------------------------------
 __global__ void scatter_i32_kernel(int* __restrict__ dst, const int* __restrict__ idx, const int* __restrict__ val,
                                    int n, long long dst_len) {
-    ce_pdl_begin();
+    // No early launch of dependents here: block tables are step inputs, and kernels further down the
+    // stream read them BEFORE their own wait (the decode attention looks up pages while the kernels
+    // before it still run).  Without the early launch the next kernel starts only when these writes are
+    // complete, and so does everything after it.
+    ce_pdl_wait();
     int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n && idx[i] >= 0 && idx[i] < dst_len) dst[idx[i]] = val[i];
 }

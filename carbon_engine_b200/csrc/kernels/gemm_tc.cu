@@ -93,10 +93,32 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
 // places into a ring of 256 records; ce_gemm_tc_trace() copies the ring out.  Off by default.
 __device__ unsigned long long g_trace[256 * 8];
 __device__ unsigned int g_trace_n;
+__device__ unsigned long long g_trace_all[256 * 4];      // per launch (sequence number & 255): latest mainloop end, partials written, block end
 __device__ __forceinline__ unsigned long long gtime() {
     unsigned long long t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
+}
+
+
+// ---- clusters: rank of this CTA, addresses in another CTA's shared memory, cluster-wide barrier
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t local_addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ float ld_cluster_f32(uint32_t cluster_addr) {
+    float v;
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(cluster_addr) : "memory");
+    return v;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
 struct TcArgs {
@@ -105,6 +127,7 @@ struct TcArgs {
     int* counters;           // one per output tile, zero between launches
     int* status;
     int M, N, K, ldo, mode, splits, kblocks_per_split, kblocks, trace;
+    int cluster;             // 1: the splits of a tile form a cluster and add their partial sums through shared memory
 };
 
 __device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + __expf(-g)) * u; }
@@ -227,6 +250,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
             if (ok) umma_commit(&acc_bar);           // the accumulators are complete
             else { atomicExch(a.status, 5); atomicExch(&s_abort, 1); }
             if (tracing) s_rec[3] = gtime();
+            if (a.trace) atomicMax(&g_trace_all[(a.trace & 255) * 4 + 0], gtime());
         }
     } else {
         // ---- epilogue: 4 warps, each reads the 32 accumulator lanes of its quadrant
@@ -265,6 +289,29 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
                     }
                 }
             }
+        } else if (a.cluster) {
+            // partial sums to this block's shared memory (the stages are free: every load has been
+            // consumed by an MMA that has completed): [acc][m][128]; they are added after the role branches
+            float* part = reinterpret_cast<float*>(tiles);
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 16) {
+                if (c >= m_valid) break;
+                float g[16], u[16];
+                if (nkb > 0 && ok) {
+                    tmem_ld16(taddr + c, g);
+                    if (NACC == 2) tmem_ld16(taddr + BN + c, u);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) g[j] = u[j] = 0.f;
+                }
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    if (c + j < m_valid) {
+                        part[(size_t)(c + j) * BM + row] = g[j];
+                        if (NACC == 2) part[(size_t)(BN + c + j) * BM + row] = u[j];
+                    }
+                }
+            }
         } else {
             // partial sums to scratch: [split][tile][acc][m][128]
             int tile = blockIdx.y * gridDim.x + blockIdx.x;
@@ -294,38 +341,46 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
             __threadfence();
             asm volatile("bar.sync 1, 128;" ::: "memory");
             if (tracing && threadIdx.x == 64) s_rec[5] = gtime();
+            if (a.trace && threadIdx.x == 64) atomicMax(&g_trace_all[(a.trace & 255) * 4 + 1], gtime());
             if (threadIdx.x == 64) s_ticket = atomicAdd(&a.counters[tile], 1);
             asm volatile("bar.sync 1, 128;" ::: "memory");
             if (s_ticket == a.splits - 1) {
                 __threadfence();
                 if (n < a.N && s_abort == 0) {
-                    // eight tokens at a time, all their loads in flight together; sums in split order
+                    // A batch of tokens at a time, with the loads of up to eight splits (and of the residual
+                    // values the tile adds into) all in flight together: one trip to L2 for up to eight
+                    // splits.  Sums are taken in split order.
+                    constexpr int TB = NACC == 2 ? 4 : 8;
                     size_t split_stride = (size_t)n_tiles * NACC * BN * BM;
                     const float* p0 = a.scratch + ((size_t)tile * NACC) * BN * BM + row;
-                    for (int mb = 0; mb < m_valid; mb += 8) {
-                        float g[8], u[8], xv[8];
+                    for (int mb = 0; mb < m_valid; mb += TB) {
+                        float g[TB], u[TB], xv[TB];
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) {
+                        for (int j = 0; j < TB; ++j) {
                             g[j] = u[j] = 0.f;
-                            // the residual values this tile adds into travel together with the partial sums
                             xv[j] = (a.mode == TC_ACCUM_F32 && mb + j < m_valid)
                                         ? __ldcg((const float*)a.out + (size_t)(m0 + mb + j) * a.ldo + n) : 0.f;
                         }
-#pragma unroll 4
-                        for (int s = 0; s < a.splits; ++s) {
-                            const float* p = p0 + s * split_stride;
-                            float tg[8], tu[8];
+                        for (int s0 = 0; s0 < a.splits; s0 += 8) {
+                            float tg[8][TB], tu[8][TB];
 #pragma unroll
-                            for (int j = 0; j < 8; ++j) {
-                                bool in = mb + j < m_valid;
-                                tg[j] = in ? __ldcg(p + (size_t)(mb + j) * BM) : 0.f;
-                                tu[j] = (NACC == 2 && in) ? __ldcg(p + (size_t)(BN + mb + j) * BM) : 0.f;
+                            for (int s = 0; s < 8; ++s) {
+                                const float* p = p0 + (size_t)(s0 + s) * split_stride;
+#pragma unroll
+                                for (int j = 0; j < TB; ++j) {
+                                    bool in = s0 + s < a.splits && mb + j < m_valid;
+                                    tg[s][j] = in ? __ldcg(p + (size_t)(mb + j) * BM) : 0.f;
+                                    tu[s][j] = (NACC == 2 && in) ? __ldcg(p + (size_t)(BN + mb + j) * BM) : 0.f;
+                                }
                             }
 #pragma unroll
-                            for (int j = 0; j < 8; ++j) { g[j] += tg[j]; u[j] += tu[j]; }
+                            for (int s = 0; s < 8; ++s) {
+#pragma unroll
+                                for (int j = 0; j < TB; ++j) { g[j] += tg[s][j]; u[j] += tu[s][j]; }
+                            }
                         }
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) {
+                        for (int j = 0; j < TB; ++j) {
                             if (mb + j >= m_valid) continue;
                             if (a.mode == TC_ACCUM_F32) ((float*)a.out)[(size_t)(m0 + mb + j) * a.ldo + n] = xv[j] + g[j];
                             else epilogue_store(a, m0 + mb + j, n, g[j], u[j]);
@@ -338,6 +393,47 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     }
     __syncthreads();
+    if (a.cluster && a.splits > 1) {
+        // Split-K inside the cluster: every block has its partial tile in shared memory; block r adds rows
+        // [r * rows_per, ...) of all blocks, in split order (the same order for every token, whatever else
+        // is in the batch), and runs the epilogue for them.  No scratch memory, no ticket, no second pass
+        // through L2.
+        cluster_sync_all();
+        if (warp >= 2) {
+            int rank = (int)cluster_rank();
+            int rows_per = (BM + a.splits - 1) / a.splits;
+            int r0 = rank * rows_per, nrows = min(BM, r0 + rows_per) - r0;
+            int m_valid = min(BN, a.M - m0);
+            uint32_t part0 = smem_u32(tiles);
+            int tid = threadIdx.x - 64;
+            if (nrows > 0 && s_abort == 0) {
+                for (int item = tid; item < nrows * m_valid; item += 128) {
+                    int m = item / nrows, row = r0 + (item - m * nrows);
+                    int n = n0 + row;
+                    if (n >= a.N) continue;
+                    uint32_t off = (uint32_t)(m * BM + row) * 4u;
+                    float g = 0.f, u = 0.f;
+                    for (int sp = 0; sp < a.splits; ++sp) {
+                        uint32_t remote = map_to_cta(part0 + off, (uint32_t)sp);
+                        g += ld_cluster_f32(remote);
+                        if (NACC == 2) u += ld_cluster_f32(remote + (uint32_t)(BN * BM) * 4u);
+                    }
+                    if (a.mode == TC_ACCUM_F32) {
+                        float* xp = (float*)a.out + (size_t)(m0 + m) * a.ldo + n;
+                        *xp = *xp + g;
+                    } else {
+                        epilogue_store(a, m0 + m, n, g, u);
+                    }
+                }
+            }
+        }
+        __syncwarp();
+        cluster_sync_all();          // nobody's shared memory goes away while another block may still read it
+    }
+    if (a.trace && threadIdx.x == 0) {
+        atomicMax(&g_trace_all[(a.trace & 255) * 4 + 2], gtime());
+        if (tracing) { s_rec[6] = (unsigned long long)(a.trace & 255); }
+    }
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS));
@@ -515,23 +611,10 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_persistent_kernel(const __gri
 // and publishes the accumulators in BOTH CTAs (commit with multicast::cluster; loads use none).
 // Each CTA runs the epilogue for its own 128 rows out of its own tensor memory.
 // ---------------------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t cluster_rank() {
-    uint32_t r;
-    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-    return r;
-}
-__device__ __forceinline__ uint32_t map_to_cta(uint32_t local_addr, uint32_t rank) {
-    uint32_t r;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
-    return r;
-}
 // Arrival on a barrier of another CTA of the cluster.  Relaxed: it only says that tensor memory has been
 // read (tcgen05.wait::ld has returned); a release here would also wait for the epilogue's global stores.
 __device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
     asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
-__device__ __forceinline__ void cluster_sync_all() {
-    asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 __device__ __forceinline__ bool mbar_test_cluster(uint64_t* bar, uint32_t parity) {
     uint32_t ok;
@@ -760,6 +843,25 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, const TcArgs& a, dim3 g
         if (e != cudaSuccess) return ce_fail(CE_ERR_CUDA, "ce_gemm_tc: %s", cudaGetErrorString(e));
         attr_set = true;
     }
+    if (a.cluster) {
+        if ((size_t)NACC * BN * BM * 4 > (size_t)stages * stage)
+            return ce_fail(CE_ERR_SIZE, "ce_gemm_tc: the partial tile does not fit the stages");
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = grid;
+        cfg.blockDim = dim3(THREADS);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[2];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 1; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = grid.z;
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = ce_pdl_enabled() ? 2 : 1;
+        cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, NACC>, mw, mx, a, stages);
+        if (e != cudaSuccess) return ce_fail(CE_ERR_CUDA, "ce_gemm_tc (cluster of %d): %s", (int)grid.z, cudaGetErrorString(e));
+        return ce_check_launch("ce_gemm_tc");
+    }
     ce_launch(gemm_tc_kernel<BN, NACC>, grid, THREADS, smem, stream, mw, mx, a, stages);
     return ce_check_launch("ce_gemm_tc");
 }
@@ -829,6 +931,15 @@ int launch_pair(const CUtensorMap& mw, const CUtensorMap& mx, const TcArgs& a, i
 
 }  // namespace
 
+// Split-K partial sums go through scratch memory and are added by the block of a tile that finishes
+// last.  CE_GEMM_CLUSTER=1 adds them inside a cluster, through shared memory, instead: its tail is
+// shorter, but a cluster of 6 to 8 blocks is not always resident at once and smaller clusters leave too
+// few blocks to keep the memory busy (measured at batch 8, 8B sizes: 4.64 to 4.73 ms a step against 4.56).
+static bool cluster_split_k() {
+    static int on = getenv("CE_GEMM_CLUSTER") ? 1 : 0;
+    return on != 0;
+}
+
 // How many splits of K a product of these sizes uses (it depends on N and K only while the tokens
 // fit one tile, so a token's sums are taken in the same order whatever else is in the batch).
 extern "C" int ce_gemm_tc_splits(int M, int N, int K) {
@@ -842,14 +953,18 @@ extern "C" int ce_gemm_tc_splits(int M, int N, int K) {
     if (s > kblocks / 4) s = kblocks / 4;      // at least four k-blocks per split
     int by_traffic = (int)(0.15 * K / (4.0 * bn));   // partial sums cost S * bn * 4 / K of the weight bytes
     if (s > by_traffic) s = by_traffic;
+    if (s > 8 && bn <= 16) s = 8;              // the last block of a tile then adds all partial sums in one trip to L2
     if (s > 16) s = 16;
+    static int max_cluster = getenv("CE_GEMM_MAX_CLUSTER") ? atoi(getenv("CE_GEMM_MAX_CLUSTER")) : 8;
+    if (cluster_split_k() && s > max_cluster) s = max_cluster;     // the splits of a tile form one cluster (8 is the portable limit)
     return s < 1 ? 1 : s;
 }
 
 // Copies out the timing ring (256 records of 8 values) and the number of records written so far.
-extern "C" int ce_gemm_tc_trace(unsigned long long* out, unsigned int* count) {
+extern "C" int ce_gemm_tc_trace(unsigned long long* out, unsigned int* count, unsigned long long* all) {
     if (cudaMemcpyFromSymbol(out, g_trace, sizeof(unsigned long long) * 256 * 8) != cudaSuccess) return CE_ERR_CUDA;
     if (cudaMemcpyFromSymbol(count, g_trace_n, sizeof(unsigned int)) != cudaSuccess) return CE_ERR_CUDA;
+    if (all && cudaMemcpyFromSymbol(all, g_trace_all, sizeof(unsigned long long) * 256 * 4) != cudaSuccess) return CE_ERR_CUDA;
     return CE_OK;
 }
 
@@ -892,7 +1007,7 @@ extern "C" int ce_gemm_tc(const void* A, const void* W, void* C, int M, int N, i
         if (prc) return prc;
         if ((prc = get_map(A, M, K, lda, pbn, &px))) return prc;
         static int ptrace = getenv("CE_GEMM_TRACE") ? 1 : 0;
-        TcArgs pa{C, scratch, counters, status, M, N, K, ldc, mode, 1, kblocks, kblocks, ptrace};
+        TcArgs pa{C, scratch, counters, status, M, N, K, ldc, mode, 1, kblocks, kblocks, ptrace, 0};
         static int use_pairs = getenv("CE_GEMM_NO_PAIRS") ? 0 : 1;
         if (use_pairs && N >= 2 * BM) {     // CTA pairs: 256 weight rows a tile, each CTA loads half of the tokens
             CUtensorMap px2;
@@ -921,8 +1036,15 @@ extern "C" int ce_gemm_tc(const void* A, const void* W, void* C, int M, int N, i
     int rc = get_map(W, (long long)N * nacc, K, K, BM, &mw);
     if (rc) return rc;
     if ((rc = get_map(A, M, K, lda, bn, &mx))) return rc;
-    static int trace = getenv("CE_GEMM_TRACE") ? 1 : 0;
-    TcArgs a{C, scratch, counters, status, M, N, K, ldc, mode, splits, (kblocks + splits - 1) / splits, kblocks, trace};
+    static int trace_on = getenv("CE_GEMM_TRACE") ? 1 : 0;
+    static int trace_seq = 0;
+    int trace = trace_on ? (++trace_seq | 256) : 0;
+    // the partial tile of a block must fit its stages (launch<> sizes them the same way)
+    size_t stage_b = (size_t)nacc * BM * BK * 2 + (size_t)bn * BK * 2;
+    size_t budget_b = bn <= 16 ? 100 * 1024 : 200 * 1024;
+    size_t n_st = budget_b / stage_b > 8 ? 8 : (budget_b / stage_b < 2 ? 2 : budget_b / stage_b);
+    int cluster = cluster_split_k() && splits > 1 && splits <= 8 && (size_t)nacc * bn * BM * 4 <= n_st * stage_b;
+    TcArgs a{C, scratch, counters, status, M, N, K, ldc, mode, splits, (kblocks + splits - 1) / splits, kblocks, trace, cluster};
 #define TC_CASE(BN_)                                                                  \
     case BN_:                                                                         \
         return nacc == 2 ? launch<BN_, 2>(mw, mx, a, grid, stream) : launch<BN_, 1>(mw, mx, a, grid, stream);

@@ -68,6 +68,7 @@ struct MmaAttnArgs {
     int* counters;              // decode: one per (sequence, KV head, head group), zero between launches
     int* status;
     int nh, nkv, d, q_stride, page_size, max_pages, num_pages, window, max_splits, split, fused_merge;
+    int cluster_merge;          // TMA decode kernel: the splits of a sequence form a cluster and merge through shared memory
     float scale_log2;           // scale * log2(e)
 };
 
@@ -409,6 +410,19 @@ __device__ __forceinline__ bool amt_wait(uint64_t* bar, uint32_t parity) {
     }
     return false;
 }
+__device__ __forceinline__ uint32_t amt_map(uint32_t local_addr, int rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ float amt_ld_cluster(uint32_t cluster_addr) {
+    float v;
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(cluster_addr) : "memory");
+    return v;
+}
+__device__ __forceinline__ void amt_cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
 __device__ __forceinline__ void ldmatrix_x4_addr(uint32_t (&r)[4], uint32_t addr) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
@@ -523,7 +537,8 @@ __global__ void __launch_bounds__(AMT_THREADS) attention_decode_tma_kernel(const
     int pos = a.positions[t];
     int lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
     int k_begin = split * a.split, k_end = min(k_begin + a.split, pos + 1);
-    if (k_begin > pos || k_end <= lo) return;     // the merge kernel skips these splits too
+    bool idle = k_begin > pos || k_end <= lo;     // no visible key in this split: the merge skips it
+    if (idle && !a.cluster_merge) return;
     const int* table = a.block_table + (size_t)a.seq_slot[b] * a.max_pages;
     int d = a.d, panels = d >> 6;
     uint32_t base = (amt_smem(smem_raw) + 1023u) & ~1023u;        // the swizzle is keyed on address bits
@@ -531,7 +546,7 @@ __global__ void __launch_bounds__(AMT_THREADS) attention_decode_tma_kernel(const
     uint32_t kv_bytes = (uint32_t)panels * 8192u;                 // K (or V) of one stage
     uint32_t stage_bytes = 2u * kv_bytes;
     int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, quad = lane & 3, grp = lane >> 2;
-    int n_tiles = (k_end - k_begin + AM_TILE - 1) / AM_TILE;
+    int n_tiles = idle ? 0 : (k_end - k_begin + AM_TILE - 1) / AM_TILE;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < ST; ++s) {
@@ -577,10 +592,16 @@ __global__ void __launch_bounds__(AMT_THREADS) attention_decode_tma_kernel(const
                 if (++s == ST) { s = 0; ph ^= 1; wrapped = true; }
             }
         }
-        return;       // the computing warps wait for every copy before they leave the loop
+        if (!a.cluster_merge) return;       // the computing warps wait for every copy before they leave the loop
     }
 
     int heads_here = min(8, G - hg * 8);
+    float* so = reinterpret_cast<float*>(tiles);             // [4][8][d]: the warps' outputs (the stages are free by then)
+    float* sm = so + 4 * 8 * d;                              // [4][8] maxima
+    float* sl = sm + 32;                                     // [4][8] sums
+    float* fm = sl + 32;                                     // [8] the block's maximum per head
+    float* fl = fm + 8;                                      // [8] the block's sum per head
+    if (warp < 4) {
     ce_pdl_wait();
     // Q^T as the B operand: head lane/4, columns kk*16 + 2*(lane%4) (+1) and + 8 (+9)
     uint32_t qf[DMAX / 16][2];
@@ -639,9 +660,6 @@ __global__ void __launch_bounds__(AMT_THREADS) attention_decode_tma_kernel(const
         l[r] += __shfl_xor_sync(0xffffffffu, l[r], 16);
     }
     // combine the 4 warps through shared memory (the staging buffers are free now)
-    float* so = reinterpret_cast<float*>(tiles);             // [4][8][d]
-    float* sm = so + 4 * 8 * d;                              // [4][8]
-    float* sl = sm + 32;                                     // [4][8]
 #pragma unroll
     for (int dn = 0; dn < DMAX / 16; ++dn) {
         if (dn * 16 < d) {
@@ -667,6 +685,12 @@ __global__ void __launch_bounds__(AMT_THREADS) attention_decode_tma_kernel(const
             acc += so[(w * 8 + r) * d + col] * f;
             L += sl[w * 8 + r] * f;
         }
+        if (a.cluster_merge) {
+            // stays in this block's shared memory (in the slot of warp 0, which only this thread reads)
+            so[r * d + col] = acc;
+            if (col == 0) { fm[r] = idle ? -INFINITY : M; fl[r] = idle ? 0.f : L; }
+            continue;
+        }
         int h = kvh * G + hg * 8 + r;
         size_t pb = ((size_t)b * a.nh + h) * a.max_splits + split;
         a.part_o[pb * d + col] = acc;
@@ -675,6 +699,42 @@ __global__ void __launch_bounds__(AMT_THREADS) attention_decode_tma_kernel(const
             a.part_ml[pb * 2 + 1] = L;
         }
     }
+    }   // warp < 4
+    if (!a.cluster_merge) return;
+    // Merge inside the cluster: the blocks of a cluster are the splits of one sequence and KV head.  Every
+    // block has its (maximum, sum, output) per head in shared memory; block r of the cluster merges a
+    // slice of the (head, column) elements of all blocks, in split order, and writes the result.  The
+    // arithmetic is the merge kernel's: weights 2^(m_s - M) / sum_s l_s 2^(m_s - M).
+    __syncwarp();
+    amt_cluster_sync();
+    if (warp < 4) {
+        int ns = a.max_splits, rank = split;
+        int total = heads_here * d, per = (total + ns - 1) / ns;
+        int e_end = min(total, (rank + 1) * per);
+        for (int e = rank * per + (int)threadIdx.x; e < e_end; e += 128) {
+            int r = e / d, col = e - r * d;
+            float ms[8], M = -INFINITY;
+#pragma unroll
+            for (int sp = 0; sp < 8; ++sp) {
+                ms[sp] = sp < ns ? amt_ld_cluster(amt_map(amt_smem(fm + r), sp)) : -INFINITY;
+                M = fmaxf(M, ms[sp]);
+            }
+            float L = 0.f, acc = 0.f, w[8];
+#pragma unroll
+            for (int sp = 0; sp < 8; ++sp) {
+                w[sp] = (sp < ns && ms[sp] != -INFINITY) ? exp2f(ms[sp] - M) : 0.f;
+                if (w[sp] != 0.f) L += amt_ld_cluster(amt_map(amt_smem(fl + r), sp)) * w[sp];
+            }
+            float inv = L > 0.f ? 1.0f / L : 0.f;
+#pragma unroll
+            for (int sp = 0; sp < 8; ++sp)
+                if (w[sp] != 0.f) acc = fmaf(amt_ld_cluster(amt_map(amt_smem(so + r * d + col), sp)), w[sp] * inv, acc);
+            int h = kvh * G + hg * 8 + r;
+            a.out[((size_t)t * a.nh + h) * d + col] = __float2bfloat16_rn(acc);
+        }
+    }
+    __syncwarp();
+    amt_cluster_sync();          // no block's shared memory goes away while another may still read it
 }
 
 // grid (n_seqs, nh), one warp per 32 output columns: out[t, h, :] = sum_s O_s w_s with
@@ -838,7 +898,9 @@ extern "C" long long ce_attention_decode_scratch(int n_seqs, int nh, int d, int 
 // max_splits >= ceil(longest context / AM_SPLIT); it fixes the grid, not the result.
 extern "C" int ce_attention_decode_split() { return AM_SPLIT; }
 // Kernels one decode attention call launches: 1 when the last block merges the splits, else 2.
-extern "C" int ce_attention_decode_kernels() { return getenv("CE_ATTN_FUSED_MERGE") ? 1 : 2; }
+// (of the call before: the in-cluster merge needs one kernel, the merge kernel a second)
+static int g_decode_launches = 2;
+extern "C" int ce_attention_decode_kernels() { return g_decode_launches; }
 
 // The TMA-staged decode kernel takes head sizes of 64, 128, 192, 256 and pages of a power of two >= 8.
 extern "C" int ce_attention_decode_tma_supported(int d, int page_size) {
@@ -869,6 +931,8 @@ extern "C" int ce_attention_decode_bf16(const void* q, const void* k_pool, const
     static int fused = getenv("CE_ATTN_FUSED_MERGE") ? 1 : 0;
     bool tma = use_tma && !fused && ce_attention_decode_tma_supported(d, page_size);
     int hgroup = tma ? 8 : 16;           // query heads of one KV head that a block takes
+    static int no_cluster = getenv("CE_ATTN_NO_CLUSTER") ? 1 : 0;
+    bool cluster_ok = tma && !no_cluster;  // the splits of a sequence merge inside a cluster: no merge kernel
     // Split size: a multiple m of AM_SPLIT.  A block has a fixed cost (launch, the chain of loads that
     // leads to its first tile, combining its warps, writing a partial) worth about six tiles of work, and
     // blocks run in waves of `slots`; m minimises waves x (tiles of a block + 6).  Few sequences get many
@@ -880,6 +944,7 @@ extern "C" int ce_attention_decode_bf16(const void* q, const void* k_pool, const
         long long best = -1;
         int best_m = 1;
         for (int m = 1; m <= max_splits; ++m) {
+            if (cluster_ok && (max_splits + m - 1) / m > 8) continue;      // a cluster holds at most 8 splits
             long long blocks = pairs * ((max_splits + m - 1) / m);
             long long cost = ((blocks + slots - 1) / slots) * ((long long)m * (AM_SPLIT / AM_TILE) + 6);
             if (best < 0 || cost < best) { best = cost; best_m = m; }
@@ -910,17 +975,41 @@ extern "C" int ce_attention_decode_bf16(const void* q, const void* k_pool, const
         size_t tsmem = (deep3 ? 3 : 2) * stage;
         if (comb > tsmem) tsmem = comb;
         tsmem += 1024;
+        a.cluster_merge = cluster_ok && max_splits <= 8;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = grid;
+        cfg.blockDim = dim3(AMT_THREADS);
+        cfg.dynamicSmemBytes = tsmem;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[2];
+        int n_attr = 0;
+        if (ce_pdl_enabled()) {
+            attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+            ++n_attr;
+        }
+        if (a.cluster_merge) {
+            attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+            attr[n_attr].val.clusterDim.x = max_splits; attr[n_attr].val.clusterDim.y = 1; attr[n_attr].val.clusterDim.z = 1;
+            ++n_attr;
+        }
+        cfg.attrs = attr;
+        cfg.numAttrs = n_attr;
+        cudaError_t le = cudaSuccess;
 #define AMT_CASE(DM)                                                                                                   \
         if (deep3) {                                                                                                   \
             if ((rc = set_smem(attention_decode_tma_kernel<DM, 3>, tsmem, "ce_attention_decode_bf16"))) return rc;     \
-            ce_launch(attention_decode_tma_kernel<DM, 3>, grid, AMT_THREADS, tsmem, stream, mk, mv, a, box_rows);      \
+            le = cudaLaunchKernelEx(&cfg, attention_decode_tma_kernel<DM, 3>, mk, mv, a, box_rows);                    \
         } else {                                                                                                       \
             if ((rc = set_smem(attention_decode_tma_kernel<DM, 2>, tsmem, "ce_attention_decode_bf16"))) return rc;     \
-            ce_launch(attention_decode_tma_kernel<DM, 2>, grid, AMT_THREADS, tsmem, stream, mk, mv, a, box_rows);      \
+            le = cudaLaunchKernelEx(&cfg, attention_decode_tma_kernel<DM, 2>, mk, mv, a, box_rows);                    \
         }
         if (d == 64) { AMT_CASE(64) } else if (d == 128) { AMT_CASE(128) } else { AMT_CASE(256) }
 #undef AMT_CASE
+        if (le != cudaSuccess) return ce_fail(CE_ERR_CUDA, "ce_attention_decode_bf16: %s", cudaGetErrorString(le));
         if ((rc = ce_check_launch("ce_attention_decode_bf16"))) return rc;
+        g_decode_launches = a.cluster_merge ? 1 : 2;
+        if (a.cluster_merge) return CE_OK;
         ce_launch(attention_merge_kernel, dim3(n_seqs, nh), d >= 128 ? 128 : (d + 31) / 32 * 32, max_splits * sizeof(float), stream, a);
         return ce_check_launch("ce_attention_decode_bf16 (merge)");
     }
@@ -944,6 +1033,7 @@ extern "C" int ce_attention_decode_bf16(const void* q, const void* k_pool, const
     if (d <= 64) { AM_DECODE_CASE(64) } else if (d <= 128) { AM_DECODE_CASE(128) } else { AM_DECODE_CASE(256) }
 #undef AM_DECODE_CASE
     if ((rc = ce_check_launch("ce_attention_decode_bf16"))) return rc;
+    g_decode_launches = a.fused_merge ? 1 : 2;
     if (a.fused_merge) return CE_OK;
     ce_launch(attention_merge_kernel, dim3(n_seqs, nh), d >= 128 ? 128 : (d + 31) / 32 * 32, max_splits * sizeof(float), stream, a);
     return ce_check_launch("ce_attention_decode_bf16 (merge)");

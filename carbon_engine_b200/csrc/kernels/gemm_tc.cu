@@ -207,9 +207,10 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
                 tma_load_2d(tiles + (size_t)i * STAGE_BYTES + NACC * W_BYTES, &map_x, &full_bar[i], (kb0 + i) * BK, m0);
                 issued = i + 1;
             }
+            int s = first == stages ? 0 : first;         // stage and parity walk along without divisions
+            uint32_t eph = 0;                            // parity of the phase that frees stage s for its next use
             for (int i = first; i < nkb && ok; ++i) {
-                int s = i % stages;
-                ok = mbar_wait(&empty_bar[s], ((i / stages) - 1) & 1);
+                ok = mbar_wait(&empty_bar[s], eph);
                 if (!ok) break;
                 unsigned char* st = tiles + (size_t)s * STAGE_BYTES;
                 mbar_expect_tx(&full_bar[s], STAGE_BYTES);
@@ -218,6 +219,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
                 if (NACC == 2) tma_load_2d(st + W_BYTES, &map_w, &full_bar[s], k, a.N + n0);
                 tma_load_2d(st + NACC * W_BYTES, &map_x, &full_bar[s], k, m0);
                 issued = i + 1;
+                if (++s == stages) { s = 0; eph ^= 1; }
             }
             if (!ok) {
                 atomicExch(a.status, 5);
@@ -230,22 +232,30 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
         if (lane == 0) {
             // ---- MMA issuer
             uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-            bool ok = true;
+            bool ok = true, ready = false;
+            int s = 0;
+            uint32_t ph = 0;
+            const uint64_t desc_hi = umma_desc(0);
             for (int i = 0; i < nkb; ++i) {
-                int s = i % stages;
-                ok = mbar_wait(&full_bar[s], (i / stages) & 1);
+                // this thread's instruction stream bounds a block's rate when few blocks share the weights:
+                // no divisions, and the next stage's barrier is tested before this stage's MMAs are issued
+                if (!ready) ok = mbar_wait(&full_bar[s], ph);
                 if (!ok) break;
                 if (tracing && i == 0) s_rec[2] = gtime();
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                uint32_t st = base + s * STAGE_BYTES;
+                int sn = s + 1 == stages ? 0 : s + 1;
+                uint32_t phn = sn == 0 ? ph ^ 1 : ph;
+                ready = i + 1 < nkb && mbar_try_wait(&full_bar[sn], phn);
+                uint32_t st = (base + s * STAGE_BYTES) >> 4;
 #pragma unroll
                 for (int kk = 0; kk < BK / UMMA_K; ++kk) {
-                    uint64_t bdesc = umma_desc(st + NACC * W_BYTES + kk * UMMA_K * 2);
+                    uint64_t bdesc = desc_hi | (uint64_t)((st + ((NACC * W_BYTES + kk * UMMA_K * 2) >> 4)) & 0x3FFF);
                     uint32_t acc = (i > 0 || kk > 0) ? 1u : 0u;
-                    umma_bf16(tmem, umma_desc(st + kk * UMMA_K * 2), bdesc, idesc, acc);
-                    if (NACC == 2) umma_bf16(tmem + BN, umma_desc(st + W_BYTES + kk * UMMA_K * 2), bdesc, idesc, acc);
+                    umma_bf16(tmem, desc_hi | (uint64_t)((st + ((kk * UMMA_K * 2) >> 4)) & 0x3FFF), bdesc, idesc, acc);
+                    if (NACC == 2) umma_bf16(tmem + BN, desc_hi | (uint64_t)((st + ((W_BYTES + kk * UMMA_K * 2) >> 4)) & 0x3FFF), bdesc, idesc, acc);
                 }
                 umma_commit(&empty_bar[s]);          // the stage is free once these MMAs have read it
+                s = sn; ph = phn;
             }
             if (ok) umma_commit(&acc_bar);           // the accumulators are complete
             else { atomicExch(a.status, 5); atomicExch(&s_abort, 1); }
@@ -942,16 +952,18 @@ static bool cluster_split_k() {
 
 // How many splits of K a product of these sizes uses (it depends on N and K only while the tokens
 // fit one tile, so a token's sums are taken in the same order whatever else is in the batch).
+extern "C" int ce_gemm_tc_tile_tokens(int M);
 extern "C" int ce_gemm_tc_splits(int M, int N, int K) {
     int kblocks = (K + BK - 1) / BK;
     if (M > 256) return 1;
-    int bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
-    int tiles = (N + BM - 1) / BM;
+    int bn = ce_gemm_tc_tile_tokens(M);
+    int tiles = ((N + BM - 1) / BM) * ((M + bn - 1) / bn);
     static int target = getenv("CE_GEMM_TARGET_CTAS") ? atoi(getenv("CE_GEMM_TARGET_CTAS")) : 0;
     // up to 16 tokens: about two CTAs per SM, each with half an SM of shared memory; more tokens: one per SM
     int s = (target ? target : (bn <= 16 ? 296 : 148)) / tiles;
     if (s > kblocks / 4) s = kblocks / 4;      // at least four k-blocks per split
-    int by_traffic = (int)(0.15 * K / (4.0 * bn));   // partial sums cost S * bn * 4 / K of the weight bytes
+    static double traffic = getenv("CE_GEMM_TRAFFIC") ? atof(getenv("CE_GEMM_TRAFFIC")) : 0.3;
+    int by_traffic = (int)(traffic * K / (4.0 * bn));   // partial sums cost S * bn * 4 / K of the weight bytes
     if (s > by_traffic) s = by_traffic;
     if (s > 8 && bn <= 16) s = 8;              // the last block of a tile then adds all partial sums in one trip to L2
     if (s > 16) s = 16;
@@ -969,7 +981,9 @@ extern "C" int ce_gemm_tc_trace(unsigned long long* out, unsigned int* count, un
 }
 
 extern "C" int ce_gemm_tc_tile_tokens(int M) {
-    return M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
+    static int max_bn = getenv("CE_GEMM_MAX_BN") ? atoi(getenv("CE_GEMM_MAX_BN")) : 256;
+    int bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
+    return bn > max_bn ? max_bn : bn;
 }
 
 // Scratch floats a product needs (0 without split-K).

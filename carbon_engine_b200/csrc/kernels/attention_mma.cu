@@ -196,7 +196,7 @@ __device__ __forceinline__ void warp_tile(const uint32_t (&qf)[DMAX / 16][4], fl
         mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
         float mn = fmaxf(m[r], mx[r] * scale_log2);
         muse[r] = mn == -INFINITY ? 0.f : mn;
-        alpha[r] = exp2f(m[r] - muse[r]);
+        alpha[r] = ce_exp2_fast(m[r] - muse[r]);
         m[r] = mn;
         l[r] *= alpha[r];
     }
@@ -204,7 +204,7 @@ __device__ __forceinline__ void warp_tile(const uint32_t (&qf)[DMAX / 16][4], fl
     for (int j = 0; j < NK8; ++j) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-            float p = exp2f(fmaf(s[j][e], scale_log2, -muse[e >> 1]));
+            float p = ce_exp2_fast(fmaf(s[j][e], scale_log2, -muse[e >> 1]));
             s[j][e] = p;
             l[e >> 1] += p;
         }
@@ -330,7 +330,7 @@ __global__ void __launch_bounds__(AM_THREADS) attention_decode_kernel(MmaAttnArg
         float acc = 0.f, L = 0.f;
 #pragma unroll
         for (int w = 0; w < 4; ++w) {
-            float f = sm[w * 16 + r] == -INFINITY ? 0.f : exp2f(sm[w * 16 + r] - M);
+            float f = sm[w * 16 + r] == -INFINITY ? 0.f : ce_exp2_fast(sm[w * 16 + r] - M);
             acc += so[(w * 16 + r) * d + col] * f;
             L += sl[w * 16 + r] * f;
         }
@@ -363,7 +363,7 @@ __global__ void __launch_bounds__(AM_THREADS) attention_decode_kernel(MmaAttnArg
         float L = 0.f;
         for (int s = lane; s < ns; s += 32) {
             float ms = __ldcg(&a.part_ml[(base + s) * 2]);
-            float f = ms == -INFINITY ? 0.f : exp2f(ms - M);
+            float f = ms == -INFINITY ? 0.f : ce_exp2_fast(ms - M);
             wts[r * ns + s] = f;
             L += __ldcg(&a.part_ml[(base + s) * 2 + 1]) * f;
         }
@@ -478,14 +478,14 @@ __device__ __forceinline__ void warp_tile_swz(const uint32_t (&qf)[DMAX / 16][2]
         mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 16));
         float mn = fmaxf(m[r], mx[r] * scale_log2);
         muse[r] = mn == -INFINITY ? 0.f : mn;
-        alpha[r] = exp2f(m[r] - muse[r]);
+        alpha[r] = ce_exp2_fast(m[r] - muse[r]);
         m[r] = mn;
         l[r] *= alpha[r];
     }
     float p[4];
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
-        p[e] = exp2f(fmaf(s[e], scale_log2, -muse[e & 1]));
+        p[e] = ce_exp2_fast(fmaf(s[e], scale_log2, -muse[e & 1]));
         l[e & 1] += p[e];                       // this thread's keys only: the 8 partial sums are added at the end
     }
     // most tiles move no head's maximum: then every alpha is exactly 1 and the output needs no rescaling
@@ -681,7 +681,7 @@ __global__ void __launch_bounds__(AMT_THREADS) attention_decode_tma_kernel(const
         float acc = 0.f, L = 0.f;
 #pragma unroll
         for (int w = 0; w < 4; ++w) {
-            float f = sm[w * 8 + r] == -INFINITY ? 0.f : exp2f(sm[w * 8 + r] - M);
+            float f = sm[w * 8 + r] == -INFINITY ? 0.f : ce_exp2_fast(sm[w * 8 + r] - M);
             acc += so[(w * 8 + r) * d + col] * f;
             L += sl[w * 8 + r] * f;
         }
@@ -722,7 +722,7 @@ __global__ void __launch_bounds__(AMT_THREADS) attention_decode_tma_kernel(const
             float L = 0.f, acc = 0.f, w[8];
 #pragma unroll
             for (int sp = 0; sp < 8; ++sp) {
-                w[sp] = (sp < ns && ms[sp] != -INFINITY) ? exp2f(ms[sp] - M) : 0.f;
+                w[sp] = (sp < ns && ms[sp] != -INFINITY) ? ce_exp2_fast(ms[sp] - M) : 0.f;
                 if (w[sp] != 0.f) L += amt_ld_cluster(amt_map(amt_smem(fl + r), sp)) * w[sp];
             }
             float inv = L > 0.f ? 1.0f / L : 0.f;
@@ -758,7 +758,7 @@ __global__ void attention_merge_kernel(MmaAttnArgs a) {
         float L = 0.f;
         for (int s = lane; s < ns; s += 32) {
             float ms = a.part_ml[(base + s) * 2];
-            float f = ms == -INFINITY ? 0.f : exp2f(ms - M);
+            float f = ms == -INFINITY ? 0.f : ce_exp2_fast(ms - M);
             wts[s] = f;
             L += a.part_ml[(base + s) * 2 + 1] * f;
         }

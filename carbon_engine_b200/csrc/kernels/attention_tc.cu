@@ -77,6 +77,24 @@ __device__ __forceinline__ void umma(uint32_t d_tmem, uint64_t a, uint64_t b, ui
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// 64 columns of this thread's lane: two loads in flight, one wait
+__device__ __forceinline__ void tmem_ld64(uint32_t taddr, float (&v)[64]) {
+    uint32_t r[64];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        uint32_t* q = r + 32 * h;
+        asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+                     "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                     : "=r"(q[0]), "=r"(q[1]), "=r"(q[2]), "=r"(q[3]), "=r"(q[4]), "=r"(q[5]), "=r"(q[6]), "=r"(q[7]),
+                       "=r"(q[8]), "=r"(q[9]), "=r"(q[10]), "=r"(q[11]), "=r"(q[12]), "=r"(q[13]), "=r"(q[14]), "=r"(q[15]),
+                       "=r"(q[16]), "=r"(q[17]), "=r"(q[18]), "=r"(q[19]), "=r"(q[20]), "=r"(q[21]), "=r"(q[22]), "=r"(q[23]),
+                       "=r"(q[24]), "=r"(q[25]), "=r"(q[26]), "=r"(q[27]), "=r"(q[28]), "=r"(q[29]), "=r"(q[30]), "=r"(q[31])
+                     : "r"(taddr + 32 * h));
+    }
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 64; ++i) v[i] = __uint_as_float(r[i]);
+}
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
     uint32_t r[32];
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
@@ -104,13 +122,14 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) 
                    "r"(__float_as_uint(v[31]))
                  : "memory");
 }
-// Barrier 1 over the 128 softmax threads that also ORs a flag: a wait that gave up in any of them ends
-// the loop in all of them at the same place, so no thread is left alone at a later barrier.
-__device__ __forceinline__ bool softmax_any(bool pred) {
-    uint32_t r;
-    asm volatile("{\n.reg .pred p, q;\nsetp.ne.b32 p, %1, 0;\nbarrier.cta.red.or.pred q, 1, 128, p;\nselp.u32 %0, 1, 0, q;\n}"
-                 : "=r"(r) : "r"((uint32_t)pred) : "memory");
-    return r != 0;
+// A softmax warp's wait: lane 0 polls (bounded), the warp takes its verdict.  The four warps are not lined
+// up with one another here (a block-wide vote at every wait cost about a third of a tile's time): each
+// arrives on s_free and p_full by itself.  If one warp gives up, it stops arriving, the MMA thread's next
+// wait runs out, and so do the other warps' waits; every loop ends, only later.
+__device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity) {
+    int lane = threadIdx.x & 31;
+    uint32_t ok = lane == 0 ? (mbar_wait(bar, parity) ? 1u : 0u) : 1u;
+    return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
@@ -147,23 +166,30 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_tc_kernel(const __g
     unsigned char* sm = smem_raw;
     uint32_t q_addr = base, kv_addr = base + Q_BYTES, p_addr = kv_addr + STAGES * STAGE_BYTES;
     uint64_t* bars = reinterpret_cast<uint64_t*>(sm + Q_BYTES + STAGES * STAGE_BYTES + P_BYTES);
+    // K and V have rings of their own: K(j) is free again as soon as S(j) is complete, long before V(j),
+    // so the copy of K(j+2) starts two softmax periods before S(j+2) needs it
     uint64_t& q_full = bars[0];
-    uint64_t* kv_full = bars + 1;
-    uint64_t* kv_empty = bars + 1 + STAGES;
-    uint64_t& s_full = bars[1 + 2 * STAGES];
-    uint64_t& s_free = bars[2 + 2 * STAGES];
-    uint64_t& p_full = bars[3 + 2 * STAGES];
-    uint64_t& pv_done = bars[4 + 2 * STAGES];
-    uint32_t& tmem_slot = *reinterpret_cast<uint32_t*>(bars + 5 + 2 * STAGES);
-    int& s_abort = *reinterpret_cast<int*>(bars + 6 + 2 * STAGES);
+    uint64_t* k_full = bars + 1;
+    uint64_t* k_empty = bars + 1 + STAGES;
+    uint64_t* v_full = bars + 1 + 2 * STAGES;
+    uint64_t* v_empty = bars + 1 + 3 * STAGES;
+    uint64_t& s_full = bars[1 + 4 * STAGES];
+    uint64_t& s_free = bars[2 + 4 * STAGES];
+    uint64_t& p_full = bars[3 + 4 * STAGES];
+    uint64_t& pv_done = bars[4 + 4 * STAGES];
+    uint32_t& tmem_slot = *reinterpret_cast<uint32_t*>(bars + 5 + 4 * STAGES);
+    int& s_abort = *reinterpret_cast<int*>(bars + 6 + 4 * STAGES);
     if (base & 1023u) {                       // cannot happen with dynamic shared memory alone; refuse rather than mis-swizzle
         if (threadIdx.x == 0) atomicCAS(a.status, 0, 69);
         return;
     }
 
     int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    int b = a.tiles[2 * blockIdx.x], q0 = a.tiles[2 * blockIdx.x + 1];
-    int h = blockIdx.y, kvh = h / (a.nh / a.nkv);
+    // grid (heads, tiles), tiles taken from the last: under a causal mask a sequence's later tiles have more
+    // keys to visit, so the long blocks start first and the short ones fill the end of the launch
+    int tile_idx = (int)(gridDim.y - 1 - blockIdx.y);
+    int b = a.tiles[2 * tile_idx], q0 = a.tiles[2 * tile_idx + 1];
+    int h = blockIdx.x, kvh = h / (a.nh / a.nkv);
     int t0 = a.q_start[b], q_len = a.q_start[b + 1] - t0;
     int ctx_before = a.ctx_len[b] - q_len;
     int nq = min(BM, q_len - q0);
@@ -176,8 +202,8 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_tc_kernel(const __g
     ce_pdl_launch_dependents();
     if (threadIdx.x == 0) {
         mbar_init(&q_full, 1);
-        for (int s = 0; s < STAGES; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
-        mbar_init(&s_full, 1); mbar_init(&s_free, 128); mbar_init(&p_full, 128); mbar_init(&pv_done, 1);
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1); }
+        mbar_init(&s_full, 1); mbar_init(&s_free, 4); mbar_init(&p_full, 4); mbar_init(&pv_done, 1);   // 4: one arrival per softmax warp
         s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -196,18 +222,13 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_tc_kernel(const __g
         if (lane == 0) {
             // ---- producer: Q once, then K and V tiles of 64 keys, page by page
             bool ok = true;
-            int issued = 0;
             mbar_expect_tx(&q_full, Q_BYTES);
 #pragma unroll
             for (int hf = 0; hf < HALVES; ++hf) tma_load_2d(sm + hf * Q_HALF, &map_q, &q_full, h * D + hf * 64, t0 + q0);
             int box_rows = min(a.page_size, BN);
-            for (int j = 0; j < n_kv; ++j) {
-                int s = j % STAGES;
-                if (j >= STAGES) ok = mbar_wait(&kv_empty[s], ((j / STAGES) - 1) & 1);
-                if (!ok) break;
-                unsigned char* kst = sm + Q_BYTES + (size_t)s * STAGE_BYTES;
-                unsigned char* vst = kst + K_BYTES;
-                mbar_expect_tx(&kv_full[s], STAGE_BYTES);
+            // one tile of K or V: pieces of a page, 64 columns a copy
+            auto load_tile = [&](const CUtensorMap* map, unsigned char* dst, uint64_t* bar, int j) {
+                mbar_expect_tx(bar, K_BYTES);
                 int k0 = k_begin + j * BN;
                 for (int r = 0; r < BN; r += box_rows) {
                     int key = k0 + r;
@@ -218,17 +239,33 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_tc_kernel(const __g
                     }
                     int row = (page * a.nkv + kvh) * a.page_size + (key & (a.page_size - 1));
 #pragma unroll
-                    for (int hf = 0; hf < HALVES; ++hf) {
-                        tma_load_2d(kst + hf * K_HALF + r * 128, &map_k, &kv_full[s], hf * 64, row);
-                        tma_load_2d(vst + hf * K_HALF + r * 128, &map_v, &kv_full[s], hf * 64, row);
-                    }
+                    for (int hf = 0; hf < HALVES; ++hf) tma_load_2d(dst + hf * K_HALF + r * 128, map, bar, hf * 64, row);
                 }
-                issued = j + 1;
+            };
+            // order K(0), then for every j: K(j+1), V(j): the keys run one tile ahead of the values
+            int k_issued = 0, v_issued = 0;
+            for (int j = -1; j < n_kv && ok; ++j) {
+                int jk = j + 1;
+                if (jk < n_kv) {
+                    int s = jk % STAGES;
+                    if (jk >= STAGES) ok = mbar_wait(&k_empty[s], ((jk / STAGES) - 1) & 1);
+                    if (!ok) break;
+                    load_tile(&map_k, sm + Q_BYTES + (size_t)s * STAGE_BYTES, &k_full[s], jk);
+                    k_issued = jk + 1;
+                }
+                if (j >= 0) {
+                    int s = j % STAGES;
+                    if (j >= STAGES) ok = mbar_wait(&v_empty[s], ((j / STAGES) - 1) & 1);
+                    if (!ok) break;
+                    load_tile(&map_v, sm + Q_BYTES + (size_t)s * STAGE_BYTES + K_BYTES, &v_full[s], j);
+                    v_issued = j + 1;
+                }
             }
             if (!ok) {
                 atomicCAS(a.status, 0, 61);                    // 61: the producer gave up waiting for a free stage
                 atomicExch(&s_abort, 1);
-                for (int j = max(0, issued - STAGES); j < issued; ++j) mbar_wait(&kv_full[j % STAGES], (j / STAGES) & 1);
+                for (int j = max(0, k_issued - STAGES); j < k_issued; ++j) mbar_wait(&k_full[j % STAGES], (j / STAGES) & 1);
+                for (int j = max(0, v_issued - STAGES); j < v_issued; ++j) mbar_wait(&v_full[j % STAGES], (j / STAGES) & 1);
             }
         }
     } else if (warp == 1) {
@@ -242,7 +279,7 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_tc_kernel(const __g
                 if (j < n_kv) {
                     int s = j % STAGES;
                     where = 63;
-                    ok = mbar_wait(&kv_full[s], (j / STAGES) & 1);
+                    ok = mbar_wait(&k_full[s], (j / STAGES) & 1);
                     if (ok && j > 0) { where = 64; ok = mbar_wait(&s_free, (j - 1) & 1); }
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -253,12 +290,13 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_tc_kernel(const __g
                         uint32_t koff = (kk / 4) * K_HALF + (kk % 4) * 32;
                         umma(tmem_s, desc_kmajor(q_addr + off), desc_kmajor(k_addr + koff), idesc_s, kk > 0 ? 1u : 0u);
                     }
+                    umma_commit(&k_empty[s]);           // the stage's K is free once these have read it
                     umma_commit(&s_full);
                 }
                 if (j > 0) {
                     int jp = j - 1, s = jp % STAGES;
                     where = 65;
-                    ok = mbar_wait(&p_full, jp & 1);
+                    ok = mbar_wait(&p_full, jp & 1) && mbar_wait(&v_full[s], (jp / STAGES) & 1);
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     uint32_t v_addr = kv_addr + s * STAGE_BYTES + K_BYTES;
@@ -266,7 +304,7 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_tc_kernel(const __g
                     for (int kk = 0; kk < BN / 16; ++kk)
                         umma(tmem_o, desc_kmajor(p_addr + kk * 32), desc_mnmajor(v_addr + kk * 16 * 128, K_HALF, 1024), idesc_pv,
                              (jp > 0 || kk > 0) ? 1u : 0u);
-                    umma_commit(&kv_empty[s]);          // the stage's K and V are free once these have read them
+                    umma_commit(&v_empty[s]);           // the stage's V is free once these have read it
                     umma_commit(&pv_done);
                 }
             }
@@ -286,32 +324,28 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_tc_kernel(const __g
         for (int j = 0; j < n_kv; ++j) {
             int k0 = k_begin + j * BN;
             where = 66;
-            // one thread polls the barrier; the named barrier hands its verdict to all 128 and lines them up
-            bool mine = threadIdx.x == 64 ? mbar_wait(&s_full, j & 1) : true;
-            if (softmax_any(!mine)) { ok = false; break; }
+            if (!warp_wait(&s_full, j & 1)) { ok = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             float sv[BN];
-            {
-                float t[32];
-                tmem_ld32(tmem_s + lane_base, t);
-#pragma unroll
-                for (int i = 0; i < 32; ++i) sv[i] = t[i];
-                tmem_ld32(tmem_s + lane_base + 32, t);
-#pragma unroll
-                for (int i = 0; i < 32; ++i) sv[32 + i] = t[i];
-            }
+            tmem_ld64(tmem_s + lane_base, sv);
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            mbar_arrive(&s_free);                 // (128 arrivals) S may be overwritten by the next product
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&s_free);  // (one arrival per warp) S may be overwritten by the next product
             bool full = row_valid && k0 >= lo && k0 + BN - 1 <= pos;
-            float mx = -INFINITY;
+            if (!full) {                          // only tiles on the diagonal, at the window's edge or past the rows
 #pragma unroll
-            for (int i = 0; i < BN; ++i) {
-                if (!full) {
+                for (int i = 0; i < BN; ++i) {
                     int key = k0 + i;
                     if (!(row_valid && key >= lo && key <= pos)) sv[i] = -INFINITY;
                 }
-                mx = fmaxf(mx, sv[i]);
             }
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int i = 0; i < BN; i += 4) {
+                mx4[0] = fmaxf(mx4[0], sv[i]); mx4[1] = fmaxf(mx4[1], sv[i + 1]);
+                mx4[2] = fmaxf(mx4[2], sv[i + 2]); mx4[3] = fmaxf(mx4[3], sv[i + 3]);
+            }
+            float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             // The running maximum is only a scale: it is raised (and the sums rescaled) when a tile's maximum
             // exceeds it by more than 2^8; below that the probabilities stay within bfloat16's range and the
             // output accumulator is left alone.
@@ -319,23 +353,23 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_tc_kernel(const __g
             bool raise = m_tile > m_run + 8.0f || (m_run == -INFINITY && m_tile != -INFINITY);
             float m_new = raise ? m_tile : m_run;
             float m_use = m_new == -INFINITY ? 0.f : m_new;
-            float alpha = raise ? exp2f(m_run - m_use) : 1.0f;
-            float sum = 0.f;
+            float alpha = raise ? ce_exp2_fast(m_run - m_use) : 1.0f;
+            float sum = 0.f, sum1 = 0.f;
             uint32_t packed[BN / 2];
 #pragma unroll
             for (int i = 0; i < BN; i += 2) {
-                float p0 = exp2f(fmaf(sv[i], a.scale_log2, -m_use));
-                float p1 = exp2f(fmaf(sv[i + 1], a.scale_log2, -m_use));
-                sum += p0 + p1;
+                float p0 = ce_exp2_fast(fmaf(sv[i], a.scale_log2, -m_use));
+                float p1 = ce_exp2_fast(fmaf(sv[i + 1], a.scale_log2, -m_use));
+                sum += p0; sum1 += p1;
                 packed[i / 2] = pack2(p0, p1);
             }
+            sum += sum1;
             l_run = l_run * alpha + sum;
             m_run = m_new;
             // P and (if a scale was raised) O may be touched only after the previous PV product is complete
             if (j > 0) {
                 where = 67;
-                mine = threadIdx.x == 64 ? mbar_wait(&pv_done, (j - 1) & 1) : true;
-                if (softmax_any(!mine)) { ok = false; break; }
+                if (!warp_wait(&pv_done, (j - 1) & 1)) { ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 if (__any_sync(0xffffffffu, alpha != 1.0f)) {
 #pragma unroll 1
@@ -361,7 +395,7 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_tc_kernel(const __g
             // the last tile may hold rows of V past the sequence's last key: zero them
             if (k0 + BN - 1 > p_last) {
                 int s = j % STAGES;
-                mbar_wait(&kv_full[s], (j / STAGES) & 1);
+                mbar_wait(&v_full[s], (j / STAGES) & 1);
                 unsigned char* vst = sm + Q_BYTES + (size_t)s * STAGE_BYTES + K_BYTES;
                 int first_bad = p_last + 1 - k0;
                 for (int e = threadIdx.x - 64; e < (BN - first_bad) * HALVES * 8; e += 128) {
@@ -372,12 +406,12 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_tc_kernel(const __g
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            mbar_arrive(&p_full);                 // (128 arrivals) P, and the zeroed rows of V, are in shared memory
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&p_full);  // (one arrival per warp) P, and the zeroed rows of V, are in shared memory
         }
-        if (ok) {                       // (uniform: every exit from the loop above is taken by all 128 threads)
+        if (ok) {                       // (uniform within a warp: a warp leaves the loop above as one)
             where = 68;
-            bool mine = threadIdx.x == 64 ? mbar_wait(&pv_done, (n_kv - 1) & 1) : true;
-            if (softmax_any(!mine)) ok = false;
+            if (!warp_wait(&pv_done, (n_kv - 1) & 1)) ok = false;
         }
         if (!ok) { atomicCAS(a.status, 0, where); atomicExch(&s_abort, 1); }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -416,7 +450,7 @@ int get_map(const void* ptr, long long rows, long long cols, long long ld, int b
 
 template <int D>
 int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const TcAttnArgs& a, dim3 grid, cudaStream_t stream) {
-    size_t smem = (size_t)BM * D * 2 + STAGES * 2 * BN * D * 2 + BM * BN * 2 + 128;    // tiles + barriers
+    size_t smem = (size_t)BM * D * 2 + STAGES * 2 * BN * D * 2 + BM * BN * 2 + 192;    // tiles + barriers
     static bool attr_set = false;
     if (!attr_set) {
         cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -445,7 +479,7 @@ extern "C" int ce_attention_prefill_tc(const void* q, const void* k_pool, const 
         return ce_fail(CE_ERR_ARG, "ce_attention_prefill_tc: null pointer");
     if (!ce_attention_prefill_tc_supported(d, page_size, q_stride))
         return ce_fail(CE_ERR_SIZE, "ce_attention_prefill_tc: head_dim %d (64 or 128), page size %d (a power of two >= 8)", d, page_size);
-    if (nkv <= 0 || nh % nkv || nh > 65535) return ce_fail(CE_ERR_SIZE, "ce_attention_prefill_tc: %d heads, %d kv heads", nh, nkv);
+    if (nkv <= 0 || nh % nkv) return ce_fail(CE_ERR_SIZE, "ce_attention_prefill_tc: %d heads, %d kv heads", nh, nkv);
     if (((uintptr_t)q | (uintptr_t)k_pool | (uintptr_t)v_pool | (uintptr_t)out) & 15)
         return ce_fail(CE_ERR_SIZE, "ce_attention_prefill_tc: operands must be 16-byte aligned");
     CUtensorMap mq, mk, mv;
@@ -459,6 +493,7 @@ extern "C" int ce_attention_prefill_tc(const void* q, const void* k_pool, const 
     while ((1 << shift) < page_size) ++shift;
     TcAttnArgs a{(__nv_bfloat16*)out, seq_slot, q_start, ctx_len, block_table, tiles, status, nh, nkv, page_size, shift,
                  max_pages, num_pages, window, scale * 1.4426950408889634f};
-    dim3 grid(n_tiles, nh);
+    if (n_tiles > 65535) return ce_fail(CE_ERR_SIZE, "ce_attention_prefill_tc: %d tiles of 128 tokens in one step", n_tiles);
+    dim3 grid(nh, n_tiles);
     return d == 64 ? launch<64>(mq, mk, mv, a, grid, stream) : launch<128>(mq, mk, mv, a, grid, stream);
 }

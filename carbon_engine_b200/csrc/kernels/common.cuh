@@ -48,6 +48,15 @@ int ce_fail(int code, const char* fmt, ...);
 int ce_check_launch(const char* what);
 int ce_sm_count();
 
+// 2^x in one MUFU instruction (relative error about 2^-22; -inf gives 0).  exp2f() costs several
+// instructions around the same MUFU; the bfloat16 attention kernels, whose probabilities are rounded to
+// 8 bits of mantissa anyway, are bound by exactly those instructions.
+__device__ __forceinline__ float ce_exp2_fast(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 template <typename T> struct CeType;
 template <> struct CeType<float> {
     static __device__ __forceinline__ float load(const float* p) { return *p; }

@@ -154,13 +154,13 @@ def main() -> int:
     e2e = h.decode_e2e(args.batch, args.steps, args.warmup)
     points, prefill = {}, None
     if not args.no_points:
-        for b in (1, 64):
-            r = h.decode(b, min(args.steps, 32), 3)
-            points[f"decode_b{b}"] = round(r["tokens_per_s"], 1)
         pf = h.prefill(2048, 3, 3)
         flops = prefill_flops(cfg, args.layers, 2048)
         prefill = {"value": round(2048 / (pf["ms"] / 1e3), 1), "tokens": 2048, "ms": round(pf["ms"], 3),
                    "frac": round(flops / (pf["ms"] / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
+        for b in (1, 64):
+            r = h.decode(b, min(args.steps, 32), 3)
+            points[f"decode_b{b}"] = round(r["tokens_per_s"], 1)
     clocks.stop()
 
     ms = main_run["ms_per_step"]

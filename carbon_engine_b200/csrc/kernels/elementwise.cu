@@ -63,6 +63,17 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
 
 // The same for widths that are multiples of 4 and at most 4 * 4 * blockDim: every thread keeps its
 // float4 elements in registers, so the row is read once and all loads are in flight together.
+// four consecutive outputs as one store (the row starts on a 16-byte boundary: H is a multiple of 4)
+__device__ __forceinline__ void store4(float* p, float a, float b, float c, float d) {
+    *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d);
+}
+__device__ __forceinline__ void store4(__nv_bfloat16* p, float a, float b, float c, float d) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+    uint2 r;
+    r.x = *reinterpret_cast<uint32_t*>(&lo); r.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(p) = r;
+}
+
 template <typename T>
 __global__ void __launch_bounds__(1024) rmsnorm_vec_kernel(const float* __restrict__ x, const float* __restrict__ w,
                                                           T* __restrict__ out, const int* __restrict__ rows, int H,
@@ -91,19 +102,14 @@ __global__ void __launch_bounds__(1024) rmsnorm_vec_kernel(const float* __restri
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         int j = threadIdx.x + i * blockDim.x;
-        if (j < n4) {
-            CeType<T>::store(o + 4 * j, v[i].x * inv * g[i].x);
-            CeType<T>::store(o + 4 * j + 1, v[i].y * inv * g[i].y);
-            CeType<T>::store(o + 4 * j + 2, v[i].z * inv * g[i].z);
-            CeType<T>::store(o + 4 * j + 3, v[i].w * inv * g[i].w);
-        }
+        if (j < n4) store4(o + 4 * j, v[i].x * inv * g[i].x, v[i].y * inv * g[i].y, v[i].z * inv * g[i].z, v[i].w * inv * g[i].w);
     }
 }
 
 // Threads per row of the vector kernel: a function of the width only, so that the order of the sum
 // never depends on the batch.  0: use the scalar kernel.
-static int rmsnorm_vec_threads(int H, const void* x, const void* w) {
-    if (H % 4 || (((uintptr_t)x | (uintptr_t)w) & 15)) return 0;
+static int rmsnorm_vec_threads(int H, const void* x, const void* w, const void* out) {
+    if (H % 4 || (((uintptr_t)x | (uintptr_t)w | (uintptr_t)out) & 15)) return 0;
     int n4 = H / 4;
     int threads = ((n4 + 3) / 4 + 31) / 32 * 32;       // four float4 per thread where possible
     if (threads < 128) threads = 128;
@@ -116,7 +122,7 @@ extern "C" int ce_rmsnorm(const float* x, const float* w, void* out, int out_dty
     if (R == 0) return CE_OK;
     if (!x || !w || !out) return ce_fail(CE_ERR_ARG, "ce_rmsnorm: null pointer");
     if (H <= 0) return ce_fail(CE_ERR_SIZE, "ce_rmsnorm: width %d", H);
-    int vt = rmsnorm_vec_threads(H, x, w);
+    int vt = rmsnorm_vec_threads(H, x, w, out);
     if (out_dtype == CE_F32) {
         if (vt) ce_launch(rmsnorm_vec_kernel<float>, R, vt, 0, stream, x, w, (float*)out, rows, H, eps);
         else ce_launch(rmsnorm_kernel<float>, R, 256, 0, stream, x, w, (float*)out, rows, H, eps);
@@ -215,79 +221,183 @@ __global__ void qk_rope_kvwrite_kernel(QkRopeArgs a) {
     if (j < d) CeType<T>::store(dst + j, v);
 }
 
-// The same with one warp per head, for head sizes that are multiples of 64 with a full rotation:
-// lane l holds elements l, l+32, ...; the partner of element j in the rotation, j +- d/2, lies in
-// the same lane, so a head needs no shared memory and no block-wide barrier.  Four heads per block.
-template <typename T, int NE>      // NE = d / 32 elements per lane
-__global__ void __launch_bounds__(128) qk_rope_kvwrite_warp_kernel(QkRopeArgs a) {
+// Vectors of VW consecutive elements to and from float (2 and 4 elements as one access)
+template <typename T, int VW> struct RopeVec {
+    static __device__ __forceinline__ void load(const T* p, float (&v)[VW]) {
+#pragma unroll
+        for (int i = 0; i < VW; ++i) v[i] = CeType<T>::load(p + i);
+    }
+    static __device__ __forceinline__ void store(T* p, const float (&v)[VW]) {
+#pragma unroll
+        for (int i = 0; i < VW; ++i) CeType<T>::store(p + i, v[i]);
+    }
+};
+template <> struct RopeVec<float, 2> {
+    static __device__ __forceinline__ void load(const float* p, float (&v)[2]) { float2 t = *reinterpret_cast<const float2*>(p); v[0] = t.x; v[1] = t.y; }
+    static __device__ __forceinline__ void store(float* p, const float (&v)[2]) { *reinterpret_cast<float2*>(p) = make_float2(v[0], v[1]); }
+};
+template <> struct RopeVec<float, 4> {
+    static __device__ __forceinline__ void load(const float* p, float (&v)[4]) { float4 t = *reinterpret_cast<const float4*>(p); v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w; }
+    static __device__ __forceinline__ void store(float* p, const float (&v)[4]) { *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]); }
+};
+template <> struct RopeVec<__nv_bfloat16, 2> {
+    static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[2]) {
+        float2 t = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p)); v[0] = t.x; v[1] = t.y;
+    }
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, const float (&v)[2]) {
+        *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(v[0], v[1]);
+    }
+};
+template <> struct RopeVec<__nv_bfloat16, 4> {
+    static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[4]) {
+        uint2 r = *reinterpret_cast<const uint2*>(p);
+        float2 lo = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&r.x)), hi = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&r.y));
+        v[0] = lo.x; v[1] = lo.y; v[2] = hi.x; v[3] = hi.y;
+    }
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, const float (&v)[4]) {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi = __floats2bfloat162_rn(v[2], v[3]);
+        uint2 r;
+        r.x = *reinterpret_cast<uint32_t*>(&lo); r.y = *reinterpret_cast<uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(p) = r;
+    }
+};
+
+// Head sizes that are multiples of 64 (up to 256) with a full rotation: one warp per group of `hpw`
+// consecutive heads of one token.  A lane holds VW = d/64 consecutive elements of the first half of a
+// head and the VW elements d/2 further on, their partners in the rotation, so nothing is exchanged
+// between lanes but the sum of squares.  The token's position, page, cosines and sines are looked up
+// once per warp, a head's address is the last one plus a stride, and the elements of four heads are in
+// flight together; with one head per warp (few tokens: decoding) the grid is as large as it can be, with many (portions of
+// prompts) a token's heads share the lookups.  A head's arithmetic does not depend on hpw.
+// n heads, one after the other from src (stride d) to dst (stride dst_stride): RMS norm with weights w1/w2
+// (NORM), rotation by cs/sn (ROT), or neither (values: a copy).  Four heads are in flight together.
+template <typename T, int VW, bool NORM, bool ROT>
+__device__ __forceinline__ void rope_heads(const T* src, T* dst, size_t dst_stride, int n, int d, int e0, float eps,
+                                           const float (&w1)[VW], const float (&w2)[VW], const float (&cs)[VW],
+                                           const float (&sn)[VW]) {
+    constexpr int U = 4;
+    int half = d >> 1;
+    float inv_d = 1.0f / (float)d;
+    for (int hb = 0; hb < n; hb += U) {
+        float x1[U][VW], x2[U][VW];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            if (hb + u < n) {
+                RopeVec<T, VW>::load(src + (size_t)u * d + e0, x1[u]);
+                RopeVec<T, VW>::load(src + (size_t)u * d + half + e0, x2[u]);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            if (hb + u >= n) break;
+            if (NORM) {
+                float ss = 0.f;
+#pragma unroll
+                for (int i = 0; i < VW; ++i) ss = fmaf(x1[u][i], x1[u][i], ss);
+#pragma unroll
+                for (int i = 0; i < VW; ++i) ss = fmaf(x2[u][i], x2[u][i], ss);
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+                float inv = rsqrtf(fmaf(ss, inv_d, eps));
+#pragma unroll
+                for (int i = 0; i < VW; ++i) { x1[u][i] = x1[u][i] * inv * w1[i]; x2[u][i] = x2[u][i] * inv * w2[i]; }
+            }
+            if (ROT) {
+#pragma unroll
+                for (int i = 0; i < VW; ++i) {
+                    float p = x1[u][i], q = x2[u][i];
+                    x1[u][i] = p * cs[i] - q * sn[i];
+                    x2[u][i] = q * cs[i] + p * sn[i];
+                }
+            }
+            RopeVec<T, VW>::store(dst + u * dst_stride + e0, x1[u]);
+            RopeVec<T, VW>::store(dst + u * dst_stride + half + e0, x2[u]);
+        }
+        src += (size_t)U * d;
+        dst += U * dst_stride;
+    }
+}
+
+template <typename T, int VW>
+__device__ __forceinline__ void rope_heads_any(const T* src, T* dst, size_t dst_stride, int n, int d, int e0, float eps,
+                                               const float* w, bool rot, const float (&cs)[VW], const float (&sn)[VW]) {
+    float w1[VW], w2[VW];
+#pragma unroll
+    for (int i = 0; i < VW; ++i) w1[i] = w2[i] = 1.f;
+    if (w) {
+        RopeVec<float, VW>::load(w + e0, w1);
+        RopeVec<float, VW>::load(w + (d >> 1) + e0, w2);
+    }
+    if (w && rot) rope_heads<T, VW, true, true>(src, dst, dst_stride, n, d, e0, eps, w1, w2, cs, sn);
+    else if (w) rope_heads<T, VW, true, false>(src, dst, dst_stride, n, d, e0, eps, w1, w2, cs, sn);
+    else if (rot) rope_heads<T, VW, false, true>(src, dst, dst_stride, n, d, e0, eps, w1, w2, cs, sn);
+    else rope_heads<T, VW, false, false>(src, dst, dst_stride, n, d, e0, eps, w1, w2, cs, sn);
+}
+
+template <typename T, int VW>
+__global__ void __launch_bounds__(128) qk_rope_kvwrite_warp_kernel(QkRopeArgs a, int hpw) {
     ce_pdl_begin();
     int lane = threadIdx.x & 31;
-    long long head_index = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
     int heads_per_token = a.nh + 2 * a.nkv;
-    if (head_index >= (long long)a.T * heads_per_token) return;
-    int t = (int)(head_index / heads_per_token), hh = (int)(head_index - (long long)t * heads_per_token);
-    int d = a.d;
-    bool is_q = hh < a.nh, is_k = !is_q && hh < a.nh + a.nkv;
-    if (!is_q && !a.write_kv) return;
-    T* src = (T*)a.qkv + (size_t)t * heads_per_token * d + (size_t)hh * d;
-    float v[NE];
-#pragma unroll
-    for (int i = 0; i < NE; ++i) v[i] = CeType<T>::load(src + lane + 32 * i);
+    int groups = (heads_per_token + hpw - 1) / hpw;
+    long long wg = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (wg >= (long long)a.T * groups) return;
+    int t = (int)(wg / groups), g = (int)(wg - (long long)t * groups);
+    int hh0 = g * hpw, hh1 = min(hh0 + hpw, heads_per_token);
+    if (!a.write_kv) hh1 = min(hh1, a.nh);
+    if (hh0 >= hh1) return;
+    int d = a.d, half = d >> 1, e0 = VW * lane;
     int pos = a.positions[t];
-    T* dst = src;
-    if (!is_q) {
+    bool rotate = a.cos_table != nullptr;
+    if (rotate && pos >= a.max_pos && hh0 < a.nh + a.nkv) {
+        if (lane == 0) atomicExch(a.status, 3);
+        return;
+    }
+    float cs[VW], sn[VW];
+#pragma unroll
+    for (int i = 0; i < VW; ++i) { cs[i] = 1.f; sn[i] = 0.f; }
+    if (rotate && hh0 < a.nh + a.nkv) {
+        RopeVec<float, VW>::load(a.cos_table + (size_t)pos * half + e0, cs);
+        RopeVec<float, VW>::load(a.sin_table + (size_t)pos * half + e0, sn);
+    }
+    size_t page_row = 0;
+    if (hh1 > a.nh) {                      // a K or V head in this group: where the token's row lies in the pools
         int slot = a.seq_slot[a.seq_of_token[t]];
         int page = a.block_table[(size_t)slot * a.max_pages + pos / a.page_size];
         if (page < 0 || page >= a.num_pages) {
             if (lane == 0) atomicExch(a.status, 2);
             return;
         }
-        int kvh = is_k ? hh - a.nh : hh - a.nh - a.nkv;
-        T* pool = (T*)(is_k ? a.k_pool : a.v_pool);
-        dst = pool + (((size_t)page * a.nkv + kvh) * a.page_size + pos % a.page_size) * d;
+        page_row = (size_t)page * a.nkv * a.page_size + pos % a.page_size;
     }
-    if (is_q || is_k) {
-        const float* w = is_q ? a.q_weight : a.k_weight;
-        if (w) {
-            float ss = 0.f;
-#pragma unroll
-            for (int i = 0; i < NE; ++i) ss = fmaf(v[i], v[i], ss);
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-            float inv = 1.0f / sqrtf(ss / (float)d + a.eps);
-#pragma unroll
-            for (int i = 0; i < NE; ++i) v[i] = v[i] * inv * w[lane + 32 * i];
-        }
-        if (a.cos_table) {
-            if (pos >= a.max_pos) {
-                if (lane == 0) atomicExch(a.status, 3);
-                return;
-            }
-            const float* c = a.cos_table + (size_t)pos * (d / 2);
-            const float* s = a.sin_table + (size_t)pos * (d / 2);
-#pragma unroll
-            for (int i = 0; i < NE / 2; ++i) {
-                int j = lane + 32 * i;                      // element j pairs with j + d/2 = this lane's element i + NE/2
-                float x1 = v[i], x2 = v[i + NE / 2];
-                v[i] = x1 * c[j] - x2 * s[j];
-                v[i + NE / 2] = x2 * c[j] + x1 * s[j];
-            }
-        }
-    }
-#pragma unroll
-    for (int i = 0; i < NE; ++i) CeType<T>::store(dst + lane + 32 * i, v[i]);
+    T* row = (T*)a.qkv + (size_t)t * heads_per_token * d;
+    // the group's query heads (in place), key heads and value heads (into the pools)
+    int q1 = min(hh1, a.nh);
+    if (hh0 < q1) rope_heads_any<T, VW>(row + (size_t)hh0 * d, row + (size_t)hh0 * d, (size_t)d, q1 - hh0, d, e0, a.eps, a.q_weight, rotate, cs, sn);
+    int k0 = max(hh0, a.nh), k1 = min(hh1, a.nh + a.nkv);
+    if (k0 < k1)
+        rope_heads_any<T, VW>(row + (size_t)k0 * d, (T*)a.k_pool + (page_row + (size_t)(k0 - a.nh) * a.page_size) * d,
+                              (size_t)a.page_size * d, k1 - k0, d, e0, a.eps, a.k_weight, rotate, cs, sn);
+    int v0 = max(hh0, a.nh + a.nkv);
+    if (v0 < hh1)
+        rope_heads_any<T, VW>(row + (size_t)v0 * d, (T*)a.v_pool + (page_row + (size_t)(v0 - a.nh - a.nkv) * a.page_size) * d,
+                              (size_t)a.page_size * d, hh1 - v0, d, e0, a.eps, nullptr, false, cs, sn);
 }
 
 template <typename T>
 static bool launch_rope_warp(const QkRopeArgs& a, cudaStream_t stream) {
-    long long heads = (long long)a.T * (a.nh + 2 * a.nkv);
-    if (a.d % 64 || a.d > 256 || (a.cos_table && a.rd != a.d) || (heads + 3) / 4 > 2147483647LL) return false;
-    unsigned blocks = (unsigned)((heads + 3) / 4);
-    switch (a.d / 32) {
-        case 2: ce_launch(qk_rope_kvwrite_warp_kernel<T, 2>, blocks, 128, 0, stream, a); return true;
-        case 4: ce_launch(qk_rope_kvwrite_warp_kernel<T, 4>, blocks, 128, 0, stream, a); return true;
-        case 6: ce_launch(qk_rope_kvwrite_warp_kernel<T, 6>, blocks, 128, 0, stream, a); return true;
-        case 8: ce_launch(qk_rope_kvwrite_warp_kernel<T, 8>, blocks, 128, 0, stream, a); return true;
+    int heads_per_token = a.nh + 2 * a.nkv;
+    if (a.d % 64 || a.d > 256 || (a.cos_table && a.rd != a.d)) return false;
+    // few tokens: a warp per head; many: four warps share a token's heads
+    int hpw = a.T >= 256 ? (heads_per_token + 3) / 4 : 1;
+    long long warps = (long long)a.T * ((heads_per_token + hpw - 1) / hpw);
+    if ((warps + 3) / 4 > 2147483647LL) return false;
+    unsigned blocks = (unsigned)((warps + 3) / 4);
+    switch (a.d / 64) {
+        case 1: ce_launch(qk_rope_kvwrite_warp_kernel<T, 1>, blocks, 128, 0, stream, a, hpw); return true;
+        case 2: ce_launch(qk_rope_kvwrite_warp_kernel<T, 2>, blocks, 128, 0, stream, a, hpw); return true;
+        case 3: ce_launch(qk_rope_kvwrite_warp_kernel<T, 3>, blocks, 128, 0, stream, a, hpw); return true;
+        case 4: ce_launch(qk_rope_kvwrite_warp_kernel<T, 4>, blocks, 128, 0, stream, a, hpw); return true;
     }
     return false;
 }

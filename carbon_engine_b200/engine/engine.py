@@ -97,7 +97,7 @@ class Engine:
                  device: str = "cuda:0", hf_overrides: Optional[Dict[str, Any]] = None, dummy_weight: bool = False,
                  seed: int = 0, kv_tokens: Optional[int] = None, memory_ratio: float = 0.9, page_size: int = 16,
                  max_seq_len: int = 0, max_running_requests: int = 16, max_prefill_tokens: int = 4096,
-                 cuda_graphs: bool = False, poison_cache: bool = False):
+                 cuda_graphs: bool = False, poison_cache: bool = False, host_lookahead: bool = True):
         self.device = require_gpu(device)
         self.dtype = parse_dtype(dtype)
         self.model, self.config, self.max_seq_len = build_model(
@@ -118,6 +118,8 @@ class Engine:
         self._done: Dict[int, RequestOutput] = {}
         self._next_id = 0
         self.d2h_bytes_last = 0
+        # while a decode step runs, the next one is laid out on the host on the guess that the same requests go on
+        self.host_lookahead = bool(host_lookahead)
 
     # -- sizing ---------------------------------------------------------------------------------
     def _bytes_per_token(self) -> int:
@@ -170,13 +172,21 @@ class Engine:
                 tokens: List[int] = []
                 if sampled_ids:
                     lives = [self._live[r] for r in sampled_ids]
-                    outs = [self.scheduler.tokens_of(r) for r in sampled_ids]
                     plens = [len(l.prompt) for l in lives]
+                    if any(l.params.has_penalties() for l in lives):    # token histories only where penalties read them
+                        outs = [self.scheduler.tokens_of(r) for r in sampled_ids]
+                        counts = [len(o) - p for o, p in zip(outs, plens)]
+                        generated = [o[p:] for o, p in zip(outs, plens)]
+                    else:
+                        counts = [self.scheduler.num_tokens(r) - p for r, p in zip(sampled_ids, plens)]
+                        generated = None
                     want_lp = [i for i, l in enumerate(lives) if l.params.logprobs > 0]
                     base = logits[want_lp].cpu().numpy() if want_lp else None    # before penalties
-                    dev = self.sampler.sample(logits, [l.params for l in lives], [l.seed for l in lives],
-                                              [len(o) - p for o, p in zip(outs, plens)],
-                                              [l.prompt for l in lives], [o[p:] for o, p in zip(outs, plens)])
+                    dev = self.sampler.sample(logits, [l.params for l in lives], [l.seed for l in lives], counts,
+                                              [l.prompt for l in lives], generated)
+                    if self.host_lookahead and all(e.sample and e.count == 1 for e in plan):
+                        # the step is on its way: lay out the next one on the host while it runs
+                        self.runner.prepare_decode_ahead(sampled_ids)
                     host = dev.cpu()
                     self.d2h_bytes_last = host.numel() * 4
                     tokens = host.tolist()

@@ -49,12 +49,14 @@ class ModelRunner:
         self._graphs = {}
         from .. import ops_tensor
         self._decode_split = ops_tensor.decode_split()
+        self._ahead = None                   # a next step laid out on the host in advance (prepare_decode_ahead)
         self._graph_pool = None
         self.h2d_bytes_last = 0
         self.kernel_launches = 0
 
     # -- requests -------------------------------------------------------------------------------
     def open_request(self, request_id: int) -> int:
+        self._discard_ahead()
         slot = self.storage.manager.open(request_id)
         self.storage.slot_opened(slot)
         self.storage.zero_state(slot)
@@ -62,18 +64,70 @@ class ModelRunner:
 
     def adopt_request(self, request_id: int) -> int:
         """A request the scheduler opened in the cache manager: prepare its slot on the device."""
+        self._discard_ahead()
         slot = self.storage.manager.slot_of(request_id)
         self.storage.slot_opened(slot)
         self.storage.zero_state(slot)
         return slot
 
     def close_request(self, request_id: int) -> None:
+        self._discard_ahead()
         self.storage.manager.close(request_id)
 
     # -- the step -------------------------------------------------------------------------------
     def prepare(self, entries: Sequence[StepEntry]):
         """Reserve pages, lay the step out in the pinned buffer and upload it.  Returns the context,
         the device tensor of wanted rows and the (request, new length) pairs to commit."""
+        ahead, self._ahead = self._ahead, None
+        if ahead is not None:
+            if self._ahead_matches(ahead, entries):
+                ctx, n_rows, commits, n_upd = ahead["layout"]
+                tokens = [e.tokens[0] for e in entries]
+                self.bufs.host_section("tokens")[:len(tokens)] = np.asarray(tokens, dtype=np.int32)
+                ctx.h_tokens = tokens
+                return self._send(ctx, n_rows, commits, n_upd)
+            self.storage._synced[:] = ahead["synced"]        # its table updates were never sent
+        return self._send(*self._layout(entries))
+
+    def prepare_decode_ahead(self, request_ids: Sequence[int]) -> None:
+        """Lay out the NEXT step on the host while the current one runs, on the guess that these requests
+        each bring one token and nothing else changes: pages reserved, positions, slots and table updates
+        written to the pinned buffer; only the token ids are missing.  ``prepare`` uses the layout if its
+        entries are exactly these requests with one token and one wanted place each, and throws it away
+        otherwise (a request finished, one arrived, a prompt portion joined)."""
+        self._discard_ahead()
+        if not request_ids:
+            return
+        synced = self.storage._synced.copy()
+        try:
+            layout = self._layout([StepEntry(r, [0], [0]) for r in request_ids])
+        except Exception:
+            self.storage._synced[:] = synced                # the step itself will meet the same error, and report it
+            return
+        self._ahead = {"ids": tuple(request_ids), "layout": layout, "synced": synced}
+
+    def _discard_ahead(self) -> None:
+        ahead, self._ahead = self._ahead, None
+        if ahead is not None:
+            self.storage._synced[:] = ahead["synced"]
+
+    @staticmethod
+    def _ahead_matches(ahead, entries: Sequence[StepEntry]) -> bool:
+        ids = ahead["ids"]
+        return len(entries) == len(ids) and all(
+            e.request_id == r and len(e.tokens) == 1 and len(e.want) == 1 and e.want[0] == 0 for e, r in zip(entries, ids))
+
+    def _send(self, ctx, n_rows: int, commits, n_upd):
+        b = self.bufs
+        self.h2d_bytes_last = b.upload()
+        for g, n in enumerate(n_upd):
+            if n:
+                ops.scatter_i32(self.storage.device_tables[g], b.dev_section(f"upd_idx{g}", n),
+                                b.dev_section(f"upd_val{g}", n))
+        return ctx, b.dev_section("rows", n_rows), commits
+
+    def _layout(self, entries: Sequence[StepEntry]):
+        """Checks, page reservations and the step's layout in the pinned host buffer (nothing is sent)."""
         mgr = self.storage.manager
         if not entries:
             raise StepError("a step needs at least one entry")
@@ -166,12 +220,7 @@ class ModelRunner:
                 n_upd.append(len(idx))
             else:
                 n_upd.append(0)
-        self.h2d_bytes_last = b.upload()
-        for g, n in enumerate(n_upd):
-            if n:
-                ops.scatter_i32(self.storage.device_tables[g], b.dev_section(f"upd_idx{g}", n),
-                                b.dev_section(f"upd_val{g}", n))
-        return ctx, b.dev_section("rows", len(rows)), commits
+        return ctx, len(rows), commits, n_upd
 
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         """Run one step and return float32 logits [wanted, vocab] on the device, in the order of the

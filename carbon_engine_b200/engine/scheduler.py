@@ -106,6 +106,13 @@ class Scheduler:
         self._lib.sched_copy_tokens(self._h, request_id, buf.ctypes.data_as(ctypes.POINTER(ctypes.c_int32)), n)
         return buf[:n].tolist()
 
+    def num_tokens(self, request_id: int) -> int:
+        """Prompt plus generated tokens of a request so far."""
+        n = self._lib.sched_num_tokens(self._h, request_id)
+        if n < 0:
+            raise KeyError(request_id)
+        return n
+
     def prompt_len_of(self, request_id: int) -> int:
         return self._lib.sched_prompt_len(self._h, request_id)
 

@@ -204,3 +204,38 @@ def test_cuda_graphs_give_the_same_tokens_as_eager(models, dtype):
     for a, b in zip(eager, graphed):
         assert a.token_ids == b.token_ids
     assert len(eng.runner._graphs) >= 3            # several batch sizes were captured
+
+
+@pytest.mark.parametrize("graphs", [False, True])
+def test_host_lookahead_gives_the_same_tokens(models, graphs):
+    """While a decode step runs, the next one is laid out on the host on the guess that the same requests
+    go on with one token each.  The guess fails when a request finishes, a queued one is admitted or a
+    late one arrives; the step then takes the ordinary way.  Same tokens either way, pages crossed and
+    reused in between, no page or slot lost."""
+    from carbon_engine_b200 import SamplingParams
+    d, cfg, w = models["A"]
+    rng = np.random.default_rng(21)
+    prompts = [random_tokens(rng, n, cfg["vocab_size"]) for n in (20, 5, 61, 33, 9, 47)]
+    sps = [SamplingParams(max_tokens=m, ignore_eos=True) for m in (35, 12, 50, 7, 41, 23)]
+
+    def run(lookahead):
+        eng = make_engine(d, "float32", "A", max_running_requests=4, cuda_graphs=graphs, host_lookahead=lookahead)
+        ids = [eng.add_request(p, s) for p, s in zip(prompts[:5], sps[:5])]
+        done, steps, used = {}, 0, 0
+        while eng.has_unfinished():
+            for out in eng.step():
+                done[out.request_id] = out.token_ids
+            steps += 1
+            if steps == 15:                           # a late arrival, in the middle of the others' decoding
+                ids.append(eng.add_request(prompts[5], sps[5]))
+            used += eng.runner._ahead is not None
+        eng.storage.manager.check()
+        assert eng.storage.manager.free_slots() == 4
+        return [done[i] for i in ids], used
+
+    plain_way, used_off = run(False)
+    ahead_way, used_on = run(True)
+    assert used_off == 0 and used_on > 20             # the layout in advance was really taken, many times
+    assert plain_way == ahead_way
+    for p, s, got in zip(prompts, sps, ahead_way):
+        assert got == plain.greedy_generate(cfg, w, p, s.max_tokens)

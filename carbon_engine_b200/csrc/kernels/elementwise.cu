@@ -78,17 +78,22 @@ template <typename T>
 __global__ void __launch_bounds__(1024) rmsnorm_vec_kernel(const float* __restrict__ x, const float* __restrict__ w,
                                                           T* __restrict__ out, const int* __restrict__ rows, int H,
                                                           float eps) {
-    ce_pdl_begin();
+    ce_pdl_launch_dependents();          // the weights (and the row list) do not depend on the kernel before
     __shared__ float scratch[32];
     int r = blockIdx.x, n4 = H >> 2;
-    const float4* xr = reinterpret_cast<const float4*>(x + (size_t)(rows ? rows[r] : r) * H);
     const float4* wr = reinterpret_cast<const float4*>(w);
     float4 v[4], g[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         int j = threadIdx.x + i * blockDim.x;
-        v[i] = j < n4 ? xr[j] : make_float4(0.f, 0.f, 0.f, 0.f);
         g[i] = j < n4 ? wr[j] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    const float4* xr = reinterpret_cast<const float4*>(x + (size_t)(rows ? rows[r] : r) * H);
+    ce_pdl_wait();
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        int j = threadIdx.x + i * blockDim.x;
+        v[i] = j < n4 ? xr[j] : make_float4(0.f, 0.f, 0.f, 0.f);
     }
     float ss = 0.f;
 #pragma unroll
@@ -336,7 +341,9 @@ __device__ __forceinline__ void rope_heads_any(const T* src, T* dst, size_t dst_
 
 template <typename T, int VW>
 __global__ void __launch_bounds__(128) qk_rope_kvwrite_warp_kernel(QkRopeArgs a, int hpw) {
-    ce_pdl_begin();
+    // positions, slots, block tables, cosines, sines and norm weights are inputs of the step or constants:
+    // they are looked up while the kernel before this one (the QKV product) still runs; only its output waits
+    ce_pdl_launch_dependents();
     int lane = threadIdx.x & 31;
     int heads_per_token = a.nh + 2 * a.nkv;
     int groups = (heads_per_token + hpw - 1) / hpw;
@@ -371,6 +378,7 @@ __global__ void __launch_bounds__(128) qk_rope_kvwrite_warp_kernel(QkRopeArgs a,
         page_row = (size_t)page * a.nkv * a.page_size + pos % a.page_size;
     }
     T* row = (T*)a.qkv + (size_t)t * heads_per_token * d;
+    ce_pdl_wait();
     // the group's query heads (in place), key heads and value heads (into the pools)
     int q1 = min(hh1, a.nh);
     if (hh0 < q1) rope_heads_any<T, VW>(row + (size_t)hh0 * d, row + (size_t)hh0 * d, (size_t)d, q1 - hh0, d, e0, a.eps, a.q_weight, rotate, cs, sn);

@@ -128,9 +128,12 @@ struct TcArgs {
     int* status;
     int M, N, K, ldo, mode, splits, kblocks_per_split, kblocks, trace;
     int cluster;             // 1: the splits of a tile form a cluster and add their partial sums through shared memory
+    int l2_ahead;            // pair kernel: weights are requested into L2 this many rounds before their copy (0: off)
 };
 
 __device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + __expf(-g)) * u; }
+// the same with the approximate reciprocal (the result is rounded to bfloat16 right after)
+__device__ __forceinline__ float silu_mul_fast(float g, float u) { return __fdividef(g, 1.0f + __expf(-g)) * u; }
 
 __device__ __forceinline__ void epilogue_store(const TcArgs& a, int m, int n, float v, float up) {
     size_t o = (size_t)m * a.ldo + n;
@@ -648,6 +651,11 @@ __device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* m
     asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
                  ::"r"(smem_u32(dst)), "l"(map), "r"(cluster_bar), "r"(x), "r"(y) : "memory");
 }
+// Ask for a box to be brought into L2 (no shared memory, no barrier): weights that come from DRAM are
+// requested a few rounds before the copy that needs them.
+__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* map, int x, int y) {
+    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(map), "r"(x), "r"(y) : "memory");
+}
 __device__ __forceinline__ void umma2_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
     asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}"
                  ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
@@ -658,21 +666,26 @@ __device__ __forceinline__ void umma2_commit_both(uint64_t* bar) {
                  ::"r"(smem_u32(bar)), "h"(mask) : "memory");
 }
 
-// BN: tokens per pair tile (each CTA loads BN/2 of them).  NACC: 1, or 2 for SwiGLU (gate and up rows).
-// KSUB: k-blocks of 64 per stage (per barrier round of the MMA thread).
-template <int BN, int NACC, int KSUB>
+// BN: tokens per pair tile (each CTA loads BN/2 of them).  KSUB: k-blocks of 64 per stage (per barrier
+// round of the MMA thread).  GU (SwiGLU): a CTA's 128 rows are 64 gate rows and the 64 up rows of the same
+// features, brought by two TMA boxes into ONE tile, so the product is the same single-accumulator product
+// as any other and a pair tile covers 128 features; in the epilogue the warps that hold the up rows (lanes
+// 64..127 of tensor memory) hand their values to the warps that hold the gate rows through shared memory.
+template <int BN, bool GU, int KSUB>
 __global__ void __launch_bounds__(THREADS) gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w,
                                                               const __grid_constant__ CUtensorMap map_x, TcArgs a,
                                                               int stages, int tiles_n, int tiles_m) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     __shared__ __align__(8) uint64_t full_bar[8], empty_bar[8], acc_full[2], acc_empty[2];
     __shared__ uint32_t tmem_slot;
+    __shared__ float xbuf[GU ? 2 * 2 * 64 * 17 : 1]; // GU: per buffer, 16 gate and 16 up values of 64 features (padded rows)
 
     constexpr int HALF_N = BN / 2;
+    constexpr int ROWS_N = GU ? BM / 2 : BM;         // output features of one CTA's tile
     constexpr uint32_t W_BYTES = BM * BK * 2, X_BYTES = HALF_N * BK * 2;
-    constexpr uint32_t SUB_BYTES = NACC * W_BYTES + X_BYTES;          // one k-block: W rows (gate, up), then tokens
+    constexpr uint32_t SUB_BYTES = W_BYTES + X_BYTES;                 // one k-block: weight rows, then tokens
     constexpr uint32_t STAGE_BYTES = KSUB * SUB_BYTES;
-    constexpr uint32_t ACC_COLS = NACC * BN;
+    constexpr uint32_t ACC_COLS = BN;
     constexpr uint32_t TMEM_COLS = 2 * ACC_COLS;
     static_assert(TMEM_COLS <= 512 && (TMEM_COLS & (TMEM_COLS - 1)) == 0, "two accumulator sets must fit tensor memory");
     const int rounds = (a.kblocks + KSUB - 1) / KSUB;                 // a k-block beyond K reads zeros
@@ -681,7 +694,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_pair_kernel(const __grid_cons
     int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     uint32_t rank = cluster_rank();                  // 0: leader
     int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
-    int total = tiles_n * tiles_m;                   // pair tiles: tiles_n of 256 weight rows, tiles_m of BN tokens
+    int total = tiles_n * tiles_m;                   // pair tiles: tiles_n of 2 * ROWS_N features, tiles_m of BN tokens
 
     ce_pdl_launch_dependents();
     if (threadIdx.x == 0) {
@@ -708,8 +721,16 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_pair_kernel(const __grid_cons
             uint32_t ph = 0;                 // parity of the phase of empty_bar[s] that frees the stage's previous use
             bool ok = true, wrapped = false;
             for (int tile = pair; tile < total && ok; tile += n_pairs) {
-                int n0 = (tile / tiles_m) * (2 * BM) + rank * BM, m0 = (tile % tiles_m) * BN + rank * HALF_N;
+                int n0 = (tile / tiles_m) * (2 * ROWS_N) + rank * ROWS_N, m0 = (tile % tiles_m) * BN + rank * HALF_N;
                 for (int r = 0; r < rounds; ++r) {
+                    if (a.l2_ahead > 0 && r + a.l2_ahead < rounds) {
+#pragma unroll
+                        for (int j = 0; j < KSUB; ++j) {
+                            int kx = ((r + a.l2_ahead) * KSUB + j) * BK;
+                            tma_prefetch_2d(&map_w, kx, n0);
+                            if (GU) tma_prefetch_2d(&map_w, kx, a.N + n0);
+                        }
+                    }
                     if (wrapped) ok = mbar_wait_cluster(&empty_bar[s], ph ^ 1);
                     if (!ok) break;
                     uint32_t bar = map_to_cta(smem_u32(&full_bar[s]), 0);
@@ -718,9 +739,9 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_pair_kernel(const __grid_cons
                     for (int j = 0; j < KSUB; ++j) {
                         unsigned char* st = tiles + (size_t)s * STAGE_BYTES + j * SUB_BYTES;
                         int kx = (r * KSUB + j) * BK;
-                        tma_load_2d_pair(st, &map_w, bar, kx, n0);
-                        if (NACC == 2) tma_load_2d_pair(st + W_BYTES, &map_w, bar, kx, a.N + n0);
-                        tma_load_2d_pair(st + NACC * W_BYTES, &map_x, bar, kx, m0);
+                        tma_load_2d_pair(st, &map_w, bar, kx, n0);          // GU: a box of 64 gate rows ...
+                        if (GU) tma_load_2d_pair(st + W_BYTES / 2, &map_w, bar, kx, a.N + n0);   // ... and the 64 up rows below them
+                        tma_load_2d_pair(st + W_BYTES, &map_x, bar, kx, m0);
                     }
                     ++issued;
                     if (++s == stages) { s = 0; ph ^= 1; wrapped = true; }
@@ -762,11 +783,9 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_pair_kernel(const __grid_cons
                         uint32_t st = (base + s * STAGE_BYTES + j * SUB_BYTES) >> 4;
 #pragma unroll
                         for (int kk = 0; kk < BK / UMMA_K; ++kk) {
-                            uint64_t bdesc = desc_hi | (uint64_t)((st + ((NACC * W_BYTES + kk * UMMA_K * 2) >> 4)) & 0x3FFF);
+                            uint64_t bdesc = desc_hi | (uint64_t)((st + ((W_BYTES + kk * UMMA_K * 2) >> 4)) & 0x3FFF);
                             uint32_t acc = (r > 0 || j > 0 || kk > 0) ? 1u : 0u;
                             umma2_bf16(d_tmem, desc_hi | (uint64_t)((st + ((kk * UMMA_K * 2) >> 4)) & 0x3FFF), bdesc, idesc, acc);
-                            if (NACC == 2)
-                                umma2_bf16(d_tmem + BN, desc_hi | (uint64_t)((st + ((W_BYTES + kk * UMMA_K * 2) >> 4)) & 0x3FFF), bdesc, idesc, acc);
                         }
                     }
                     umma2_commit_both(&empty_bar[s]);     // the stage is free in both CTAs
@@ -786,33 +805,73 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_pair_kernel(const __grid_cons
         uint32_t leader_empty[2] = {map_to_cta(smem_u32(&acc_empty[0]), 0), map_to_cta(smem_u32(&acc_empty[1]), 0)};
         for (int tile = pair; tile < total && ok; tile += n_pairs, ++lt) {
             int buf = lt & 1;
-            int n = (tile / tiles_m) * (2 * BM) + rank * BM + row;
+            int n = (tile / tiles_m) * (2 * ROWS_N) + rank * ROWS_N + (GU ? (row & 63) : row);
+            bool up_row = GU && row >= 64;
             int m0 = (tile % tiles_m) * BN;
             int m_valid = min(BN, a.M - m0);
+            const bool accum = !GU && a.mode == TC_ACCUM_F32 && n < a.N;
+            float xv[32];
+            if (accum) {       // the residual values of the first 32 tokens are on their way before the accumulators are ready
+                const float* xp = (const float*)a.out + (size_t)m0 * a.ldo + n;
+#pragma unroll
+                for (int j = 0; j < 32; ++j) xv[j] = j < m_valid ? xp[(size_t)j * a.ldo] : 0.f;
+            }
             ok = mbar_wait_cluster(&acc_full[buf], (lt >> 1) & 1);
             if (!ok) { atomicExch(a.status, 5); break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             uint32_t taddr = tmem + buf * ACC_COLS + ((uint32_t)(quad * 32) << 16);
+            if (!GU && a.mode == TC_ACCUM_F32) {
+                // x += product, 32 tokens a chunk; the next chunk's residual values are loaded while this one is stored
 #pragma unroll 1
-            for (int c = 0; c < BN; c += 32) {
-                if (c >= m_valid) break;
-                float g[32], u[32];
-                tmem_ld32(taddr + c, g);
-                if (NACC == 2) tmem_ld32(taddr + BN + c, u);
-                if (n < a.N) {
-                    if (a.mode == TC_ACCUM_F32) {
+                for (int c = 0; c < BN; c += 32) {
+                    if (c >= m_valid) break;
+                    float g[32], xn[32];
+                    tmem_ld32(taddr + c, g);
+                    if (accum) {
                         float* xp = (float*)a.out + (size_t)(m0 + c) * a.ldo + n;
-                        float xv[32];
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) xv[j] = (c + j < m_valid) ? xp[(size_t)j * a.ldo] : 0.f;
+                        for (int j = 0; j < 32; ++j) xn[j] = (c + 32 + j < m_valid) ? xp[(size_t)(32 + j) * a.ldo] : 0.f;
 #pragma unroll
                         for (int j = 0; j < 32; ++j)
                             if (c + j < m_valid) xp[(size_t)j * a.ldo] = xv[j] + g[j];
-                    } else {
 #pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (c + j < m_valid) epilogue_store(a, m0 + c + j, n, g[j], NACC == 2 ? u[j] : 0.f);
+                        for (int j = 0; j < 32; ++j) xv[j] = xn[j];
                     }
+                }
+            } else
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 32) {
+                if (c >= m_valid) break;
+                float g[32];
+                tmem_ld32(taddr + c, g);
+                if (GU) {
+                    // Rows 64..127 hold the up values of the features whose gate values rows 0..63 hold.  The two
+                    // threads of a feature share its 32 tokens: the gate thread takes tokens 0..15 (and needs their
+                    // up values), the up thread tokens 16..31 (and needs their gate values); both then work.
+                    float* xg = xbuf + ((c >> 5) & 1) * (2 * 64 * 17) + (row & 63) * 17;     // gate values of tokens 16..31
+                    float* xu = xg + 64 * 17;                                               // up values of tokens 0..15
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        if (up_row) xu[j] = g[j];
+                        else xg[j] = g[16 + j];
+                    }
+                    asm volatile("bar.sync 2, 128;" ::: "memory");     // (the buffer used two chunks ago has been read by then)
+                    if (n < a.N) {
+                        int t0 = up_row ? 16 : 0;
+                        __nv_bfloat16* op = (__nv_bfloat16*)a.out + (size_t)(m0 + c + t0) * a.ldo + n;
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            float gate = up_row ? xg[j] : g[j];
+                            float upv = up_row ? g[16 + j] : xu[j];
+                            if (c + t0 + j < m_valid) op[(size_t)j * a.ldo] = __float2bfloat16_rn(silu_mul_fast(gate, upv));
+                        }
+                    }
+                    continue;
+                }
+                if (n < a.N) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        if (c + j < m_valid) epilogue_store(a, m0 + c + j, n, g[j], 0.f);
                 }
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -894,15 +953,15 @@ int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, const TcArgs
     return ce_check_launch("ce_gemm_tc (persistent)");
 }
 
-template <int BN, int NACC, int KSUB>
+template <int BN, bool GU, int KSUB>
 int launch_pair(const CUtensorMap& mw, const CUtensorMap& mx, const TcArgs& a, int tiles_n, int tiles_m, cudaStream_t stream) {
-    constexpr size_t stage = KSUB * (NACC * BM * BK * 2 + (BN / 2) * BK * 2);
+    constexpr size_t stage = KSUB * (BM * BK * 2 + (BN / 2) * BK * 2);
     int stages = (int)((200 * 1024) / stage);
     if (stages > 8) stages = 8;
     size_t smem = stages * stage + 1024;
     static bool attr_set = false;
     if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel<BN, NACC, KSUB>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 2048);
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel<BN, GU, KSUB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return ce_fail(CE_ERR_CUDA, "ce_gemm_tc: %s", cudaGetErrorString(e));
         attr_set = true;
     }
@@ -922,10 +981,10 @@ int launch_pair(const CUtensorMap& mw, const CUtensorMap& mx, const TcArgs& a, i
         cfg.attrs = attr;
         cfg.numAttrs = 1;
         int n = 0;
-        cudaError_t e = cudaOccupancyMaxActiveClusters(&n, gemm_tc_pair_kernel<BN, NACC, KSUB>, &cfg);
+        cudaError_t e = cudaOccupancyMaxActiveClusters(&n, gemm_tc_pair_kernel<BN, GU, KSUB>, &cfg);
         if (e != cudaSuccess || n < 1) return ce_fail(CE_ERR_CUDA, "ce_gemm_tc (pairs): no resident cluster: %s", cudaGetErrorString(e));
         max_pairs = n;
-        if (getenv("CE_GEMM_TRACE")) fprintf(stderr, "[carbon_engine_b200] gemm pairs<%d,%d>: %d resident\n", BN, NACC, n);
+        if (getenv("CE_GEMM_TRACE")) fprintf(stderr, "[carbon_engine_b200] gemm pairs<%d,%d>: %d resident\n", BN, (int)GU, n);
     }
     int pairs = max_pairs;
     if (total < pairs) pairs = (int)total;
@@ -934,7 +993,7 @@ int launch_pair(const CUtensorMap& mw, const CUtensorMap& mx, const TcArgs& a, i
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = ce_pdl_enabled() ? 2 : 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel<BN, NACC, KSUB>, mw, mx, a, stages, tiles_n, tiles_m);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel<BN, GU, KSUB>, mw, mx, a, stages, tiles_n, tiles_m);
     if (e != cudaSuccess) return ce_fail(CE_ERR_CUDA, "ce_gemm_tc (pairs): %s", cudaGetErrorString(e));
     return ce_check_launch("ce_gemm_tc (pairs)");
 }
@@ -1021,18 +1080,19 @@ extern "C" int ce_gemm_tc(const void* A, const void* W, void* C, int M, int N, i
         if (prc) return prc;
         if ((prc = get_map(A, M, K, lda, pbn, &px))) return prc;
         static int ptrace = getenv("CE_GEMM_TRACE") ? 1 : 0;
-        TcArgs pa{C, scratch, counters, status, M, N, K, ldc, mode, 1, kblocks, kblocks, ptrace, 0};
+        static int l2_ahead = getenv("CE_GEMM_L2_AHEAD") ? atoi(getenv("CE_GEMM_L2_AHEAD")) : 0;
+        TcArgs pa{C, scratch, counters, status, M, N, K, ldc, mode, 1, kblocks, kblocks, ptrace, 0, l2_ahead};
         static int use_pairs = getenv("CE_GEMM_NO_PAIRS") ? 0 : 1;
         if (use_pairs && N >= 2 * BM) {     // CTA pairs: 256 weight rows a tile, each CTA loads half of the tokens
-            CUtensorMap px2;
-            if ((prc = get_map(A, M, K, lda, pbn / 2, &px2))) return prc;
-            long long tiles_n2 = (N + 2 * BM - 1) / (2 * BM);
-            static int ksub = getenv("CE_GEMM_KSUB") ? atoi(getenv("CE_GEMM_KSUB")) : 2;
-            if (ksub == 1)
-                return nacc == 2 ? launch_pair<128, 2, 1>(pw, px2, pa, (int)tiles_n2, (int)tiles_m, stream)
-                                 : launch_pair<256, 1, 1>(pw, px2, pa, (int)tiles_n2, (int)tiles_m, stream);
-            return nacc == 2 ? launch_pair<128, 2, 2>(pw, px2, pa, (int)tiles_n2, (int)tiles_m, stream)
-                             : launch_pair<256, 1, 2>(pw, px2, pa, (int)tiles_n2, (int)tiles_m, stream);
+            // SwiGLU: 128 gate rows and their 128 up rows a pair tile (boxes of 64 rows), 256 tokens as well
+            CUtensorMap px2, pw2;
+            if ((prc = get_map(A, M, K, lda, 128, &px2))) return prc;
+            long long ptiles_m = (M + 255) / 256;
+            if (nacc == 2) {
+                if ((prc = get_map(W, (long long)N * 2, K, K, BM / 2, &pw2))) return prc;
+                return launch_pair<256, true, 2>(pw2, px2, pa, (int)((N + BM - 1) / BM), (int)ptiles_m, stream);
+            }
+            return launch_pair<256, false, 2>(pw, px2, pa, (int)((N + 2 * BM - 1) / (2 * BM)), (int)ptiles_m, stream);
         }
         return nacc == 2 ? launch_persistent<128, 2>(pw, px, pa, (int)tiles_n, (int)tiles_m, stream)
                          : launch_persistent<256, 1>(pw, px, pa, (int)tiles_n, (int)tiles_m, stream);
@@ -1058,7 +1118,7 @@ extern "C" int ce_gemm_tc(const void* A, const void* W, void* C, int M, int N, i
     size_t budget_b = bn <= 16 ? 100 * 1024 : 200 * 1024;
     size_t n_st = budget_b / stage_b > 8 ? 8 : (budget_b / stage_b < 2 ? 2 : budget_b / stage_b);
     int cluster = cluster_split_k() && splits > 1 && splits <= 8 && (size_t)nacc * bn * BM * 4 <= n_st * stage_b;
-    TcArgs a{C, scratch, counters, status, M, N, K, ldc, mode, splits, (kblocks + splits - 1) / splits, kblocks, trace, cluster};
+    TcArgs a{C, scratch, counters, status, M, N, K, ldc, mode, splits, (kblocks + splits - 1) / splits, kblocks, trace, cluster, 0};
 #define TC_CASE(BN_)                                                                  \
     case BN_:                                                                         \
         return nacc == 2 ? launch<BN_, 2>(mw, mx, a, grid, stream) : launch<BN_, 1>(mw, mx, a, grid, stream);

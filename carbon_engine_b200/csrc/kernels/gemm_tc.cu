@@ -150,16 +150,21 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
     __shared__ __align__(8) uint64_t full_bar[8], empty_bar[8], acc_bar;
     __shared__ uint32_t tmem_slot;
     __shared__ int s_ticket, s_abort;
+    // NACC == 2 stands for SwiGLU: the block's 128 weight rows are 64 gate rows and the 64 up rows of the
+    // same features (two TMA boxes into one tile), the product has ONE accumulator like any other, and
+    // the two threads of a feature meet in the epilogue through this buffer.  K is never split then.
+    constexpr bool GU = NACC == 2;
+    __shared__ float xbuf[GU ? 2 * 2 * 64 * 9 : 1];
 
     constexpr uint32_t W_BYTES = BM * BK * 2, X_BYTES = BN * BK * 2;
-    constexpr uint32_t STAGE_BYTES = NACC * W_BYTES + X_BYTES;
-    constexpr uint32_t TMEM_COLS = (NACC * BN) < 32 ? 32 : (NACC * BN);
+    constexpr uint32_t STAGE_BYTES = W_BYTES + X_BYTES;
+    constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
     // the dynamic buffer is aligned to 1024 bytes by hand: the swizzle pattern is keyed on address bits
     uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     unsigned char* tiles = smem_raw + (base - smem_u32(smem_raw));
 
     int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    int n0 = blockIdx.x * BM, m0 = blockIdx.y * BN, split = blockIdx.z;
+    int n0 = blockIdx.x * (GU ? BM / 2 : BM), m0 = blockIdx.y * BN, split = blockIdx.z;
     int kb0 = split * a.kblocks_per_split;
     int kb1 = min(kb0 + a.kblocks_per_split, a.kblocks);
     int nkb = kb1 - kb0;
@@ -202,12 +207,12 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
                 mbar_expect_tx(&full_bar[i], STAGE_BYTES);
                 int k = (kb0 + i) * BK;
                 tma_load_2d(st, &map_w, &full_bar[i], k, n0);
-                if (NACC == 2) tma_load_2d(st + W_BYTES, &map_w, &full_bar[i], k, a.N + n0);
+                if (GU) tma_load_2d(st + W_BYTES / 2, &map_w, &full_bar[i], k, a.N + n0);
             }
             ce_pdl_wait();
             if (tracing) s_rec[1] = gtime();
             for (int i = 0; i < first; ++i) {            // their tokens: after it
-                tma_load_2d(tiles + (size_t)i * STAGE_BYTES + NACC * W_BYTES, &map_x, &full_bar[i], (kb0 + i) * BK, m0);
+                tma_load_2d(tiles + (size_t)i * STAGE_BYTES + W_BYTES, &map_x, &full_bar[i], (kb0 + i) * BK, m0);
                 issued = i + 1;
             }
             int s = first == stages ? 0 : first;         // stage and parity walk along without divisions
@@ -219,8 +224,8 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
                 mbar_expect_tx(&full_bar[s], STAGE_BYTES);
                 int k = (kb0 + i) * BK;
                 tma_load_2d(st, &map_w, &full_bar[s], k, n0);
-                if (NACC == 2) tma_load_2d(st + W_BYTES, &map_w, &full_bar[s], k, a.N + n0);
-                tma_load_2d(st + NACC * W_BYTES, &map_x, &full_bar[s], k, m0);
+                if (GU) tma_load_2d(st + W_BYTES / 2, &map_w, &full_bar[s], k, a.N + n0);
+                tma_load_2d(st + W_BYTES, &map_x, &full_bar[s], k, m0);
                 issued = i + 1;
                 if (++s == stages) { s = 0; eph ^= 1; }
             }
@@ -252,10 +257,9 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
                 uint32_t st = (base + s * STAGE_BYTES) >> 4;
 #pragma unroll
                 for (int kk = 0; kk < BK / UMMA_K; ++kk) {
-                    uint64_t bdesc = desc_hi | (uint64_t)((st + ((NACC * W_BYTES + kk * UMMA_K * 2) >> 4)) & 0x3FFF);
+                    uint64_t bdesc = desc_hi | (uint64_t)((st + ((W_BYTES + kk * UMMA_K * 2) >> 4)) & 0x3FFF);
                     uint32_t acc = (i > 0 || kk > 0) ? 1u : 0u;
                     umma_bf16(tmem, desc_hi | (uint64_t)((st + ((kk * UMMA_K * 2) >> 4)) & 0x3FFF), bdesc, idesc, acc);
-                    if (NACC == 2) umma_bf16(tmem + BN, desc_hi | (uint64_t)((st + ((W_BYTES + kk * UMMA_K * 2) >> 4)) & 0x3FFF), bdesc, idesc, acc);
                 }
                 umma_commit(&empty_bar[s]);          // the stage is free once these MMAs have read it
                 s = sn; ph = phn;
@@ -269,7 +273,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
         // ---- epilogue: 4 warps, each reads the 32 accumulator lanes of its quadrant
         int quad = warp & 3;
         int row = quad * 32 + lane;                  // feature within the tile
-        int n = n0 + row;
+        int n = n0 + (GU ? (row & 63) : row);
         int m_valid = min(BN, a.M - m0);
         ce_pdl_wait();
         bool ok = nkb > 0 ? mbar_wait(&acc_bar, 0) : true;
@@ -277,14 +281,47 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
         if (tracing && threadIdx.x == 64) s_rec[4] = gtime();
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         uint32_t taddr = tmem + ((uint32_t)(quad * 32) << 16);
-        if (a.splits == 1) {
+        if (GU) {
+            // Rows 64..127 of the tile hold the up values of the features whose gate values rows 0..63 hold.  The
+            // two threads of a feature share each chunk of 16 tokens: the gate thread takes tokens 0..7 (and
+            // needs their up values), the up thread tokens 8..15 (and needs their gate values).
+            ok = __all_sync(0xffffffffu, ok);            // tensor-memory loads and the barrier below are taken by whole warps
+            bool up_row = row >= 64;
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 16) {
+                if (c >= m_valid) break;
+                float g[16];
+                if (ok && nkb > 0) tmem_ld16(taddr + c, g);
+                else {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) g[j] = 0.f;
+                }
+                float* xg = xbuf + ((c >> 4) & 1) * (2 * 64 * 9) + (row & 63) * 9;     // gate values of tokens 8..15
+                float* xu = xg + 64 * 9;                                              // up values of tokens 0..7
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    if (up_row) xu[j] = g[j];
+                    else xg[j] = g[8 + j];
+                }
+                asm volatile("bar.sync 2, 128;" ::: "memory");     // (the buffer used two chunks ago has been read by then)
+                if (ok && n < a.N) {
+                    int t0 = up_row ? 8 : 0;
+                    __nv_bfloat16* op = (__nv_bfloat16*)a.out + (size_t)(m0 + c + t0) * a.ldo + n;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        float gate = up_row ? xg[j] : g[j];
+                        float upv = up_row ? g[8 + j] : xu[j];
+                        if (c + t0 + j < m_valid) op[(size_t)j * a.ldo] = __float2bfloat16_rn(silu_mul_fast(gate, upv));
+                    }
+                }
+            }
+        } else if (a.splits == 1) {
             if (ok) {
 #pragma unroll 1
                 for (int c = 0; c < BN; c += 16) {
                     if (c >= m_valid) break;
                     float g[16], u[16];
                     tmem_ld16(taddr + c, g);
-                    if (NACC == 2) tmem_ld16(taddr + BN + c, u);
                     if (n < a.N) {
                         if (a.mode == TC_ACCUM_F32) {
                             float* xp = (float*)a.out + (size_t)(m0 + c) * a.ldo + n;
@@ -297,7 +334,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
                         } else {
 #pragma unroll
                             for (int j = 0; j < 16; ++j)
-                                if (c + j < m_valid) epilogue_store(a, m0 + c + j, n, g[j], NACC == 2 ? u[j] : 0.f);
+                                if (c + j < m_valid) epilogue_store(a, m0 + c + j, n, g[j], 0.f);
                         }
                     }
                 }
@@ -312,7 +349,6 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
                 float g[16], u[16];
                 if (nkb > 0 && ok) {
                     tmem_ld16(taddr + c, g);
-                    if (NACC == 2) tmem_ld16(taddr + BN + c, u);
                 } else {
 #pragma unroll
                     for (int j = 0; j < 16; ++j) g[j] = u[j] = 0.f;
@@ -321,7 +357,6 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
                 for (int j = 0; j < 16; ++j) {
                     if (c + j < m_valid) {
                         part[(size_t)(c + j) * BM + row] = g[j];
-                        if (NACC == 2) part[(size_t)(BN + c + j) * BM + row] = u[j];
                     }
                 }
             }
@@ -329,7 +364,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
             // partial sums to scratch: [split][tile][acc][m][128]
             int tile = blockIdx.y * gridDim.x + blockIdx.x;
             int n_tiles = gridDim.x * gridDim.y;
-            float* mine = a.scratch + (((size_t)split * n_tiles + tile) * NACC) * BN * BM;
+            float* mine = a.scratch + ((size_t)split * n_tiles + tile) * BN * BM;
             if (ok) {
 #pragma unroll 1
                 for (int c = 0; c < BN; c += 16) {
@@ -337,8 +372,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
                     float g[16], u[16];
                     if (nkb > 0) {
                         tmem_ld16(taddr + c, g);
-                        if (NACC == 2) tmem_ld16(taddr + BN + c, u);
-                    } else {
+                        } else {
 #pragma unroll
                         for (int j = 0; j < 16; ++j) g[j] = u[j] = 0.f;
                     }
@@ -346,7 +380,6 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
                     for (int j = 0; j < 16; ++j) {
                         if (c + j < m_valid) {
                             mine[(size_t)(c + j) * BM + row] = g[j];
-                            if (NACC == 2) mine[(size_t)(BN + c + j) * BM + row] = u[j];
                         }
                     }
                 }
@@ -363,9 +396,9 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
                     // A batch of tokens at a time, with the loads of up to eight splits (and of the residual
                     // values the tile adds into) all in flight together: one trip to L2 for up to eight
                     // splits.  Sums are taken in split order.
-                    constexpr int TB = NACC == 2 ? 4 : 8;
-                    size_t split_stride = (size_t)n_tiles * NACC * BN * BM;
-                    const float* p0 = a.scratch + ((size_t)tile * NACC) * BN * BM + row;
+                    constexpr int TB = 8;
+                    size_t split_stride = (size_t)n_tiles * BN * BM;
+                    const float* p0 = a.scratch + (size_t)tile * BN * BM + row;
                     for (int mb = 0; mb < m_valid; mb += TB) {
                         float g[TB], u[TB], xv[TB];
 #pragma unroll
@@ -383,7 +416,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
                                 for (int j = 0; j < TB; ++j) {
                                     bool in = s0 + s < a.splits && mb + j < m_valid;
                                     tg[s][j] = in ? __ldcg(p + (size_t)(mb + j) * BM) : 0.f;
-                                    tu[s][j] = (NACC == 2 && in) ? __ldcg(p + (size_t)(BN + mb + j) * BM) : 0.f;
+                                    tu[s][j] = 0.f;
                                 }
                             }
 #pragma unroll
@@ -429,7 +462,6 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
                     for (int sp = 0; sp < a.splits; ++sp) {
                         uint32_t remote = map_to_cta(part0 + off, (uint32_t)sp);
                         g += ld_cluster_f32(remote);
-                        if (NACC == 2) u += ld_cluster_f32(remote + (uint32_t)(BN * BM) * 4u);
                     }
                     if (a.mode == TC_ACCUM_F32) {
                         float* xp = (float*)a.out + (size_t)(m0 + m) * a.ldo + n;
@@ -896,24 +928,25 @@ int get_map(const void* ptr, long long rows, long long cols, long long ld, int b
 
 template <int BN, int NACC>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, const TcArgs& a, dim3 grid, cudaStream_t stream) {
-    constexpr size_t stage = NACC * BM * BK * 2 + BN * BK * 2;
+    constexpr size_t stage = BM * BK * 2 + BN * BK * 2;
     // small tiles: at most half an SM's shared memory, so that the blocks of the next kernel (launched
     // as a programmatic dependent) fit beside these and stream their weights while these finish
     // (measured: best for up to 16 tokens; from 32 tokens on one block per SM with a deeper pipeline wins)
     static int small_kb = getenv("CE_GEMM_SMEM_KB") ? atoi(getenv("CE_GEMM_SMEM_KB")) : 0;
-    size_t budget = small_kb ? (size_t)small_kb * 1024 : (BN <= 16 ? 100 * 1024 : 200 * 1024);
+    // (the SwiGLU product has twice the tiles and never splits K: two of its blocks share an SM at every tile size)
+    size_t budget = small_kb ? (size_t)small_kb * 1024 : ((BN <= 16 || NACC == 2) ? 100 * 1024 : 200 * 1024);
     int stages = (int)(budget / stage);
     if (stages > 8) stages = 8;
     if (stages < 2) stages = 2;
     size_t smem = stages * stage + 1024;
     static bool attr_set = false;
     if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, NACC>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 2048);
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, NACC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return ce_fail(CE_ERR_CUDA, "ce_gemm_tc: %s", cudaGetErrorString(e));
         attr_set = true;
     }
     if (a.cluster) {
-        if ((size_t)NACC * BN * BM * 4 > (size_t)stages * stage)
+        if ((size_t)BN * BM * 4 > (size_t)stages * stage)
             return ce_fail(CE_ERR_SIZE, "ce_gemm_tc: the partial tile does not fit the stages");
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = grid;
@@ -1048,10 +1081,10 @@ extern "C" int ce_gemm_tc_tile_tokens(int M) {
 // Scratch floats a product needs (0 without split-K).
 extern "C" long long ce_gemm_tc_scratch(int M, int N, int K, int mode) {
     int s = ce_gemm_tc_splits(M, N, K);
-    if (s == 1) return 0;
+    if (s == 1 || mode == TC_SWIGLU) return 0;         // (the SwiGLU product never splits K)
     int bn = ce_gemm_tc_tile_tokens(M);
     long long tiles = (long long)((N + BM - 1) / BM) * ((M + bn - 1) / bn);
-    return (long long)s * tiles * (mode == TC_SWIGLU ? 2 : 1) * bn * BM;
+    return (long long)s * tiles * bn * BM;
 }
 
 extern "C" int ce_gemm_tc_supported(int M, int N, int K, int lda) {
@@ -1098,8 +1131,10 @@ extern "C" int ce_gemm_tc(const void* A, const void* W, void* C, int M, int N, i
                          : launch_persistent<256, 1>(pw, px, pa, (int)tiles_n, (int)tiles_m, stream);
     }
     int bn = ce_gemm_tc_tile_tokens(M);
-    int splits = ce_gemm_tc_splits(M, N, K);
-    dim3 grid((N + BM - 1) / BM, (M + bn - 1) / bn, splits);
+    // SwiGLU: a block takes 64 features (64 gate rows and their 64 up rows in one tile) and all of K
+    int rows_n = nacc == 2 ? BM / 2 : BM;
+    int splits = nacc == 2 ? 1 : ce_gemm_tc_splits(M, N, K);
+    dim3 grid((N + rows_n - 1) / rows_n, (M + bn - 1) / bn, splits);
     if (grid.y > 65535) return ce_fail(CE_ERR_SIZE, "ce_gemm_tc: M=%d is too large", M);
     if (splits > 1) {
         if (!scratch || !counters || scratch_floats < ce_gemm_tc_scratch(M, N, K, mode) || n_counters < (int)(grid.x * grid.y))
@@ -1107,17 +1142,17 @@ extern "C" int ce_gemm_tc(const void* A, const void* W, void* C, int M, int N, i
                            ce_gemm_tc_scratch(M, N, K, mode), grid.x * grid.y);
     }
     CUtensorMap mw, mx;
-    int rc = get_map(W, (long long)N * nacc, K, K, BM, &mw);
+    int rc = get_map(W, (long long)N * nacc, K, K, rows_n, &mw);
     if (rc) return rc;
     if ((rc = get_map(A, M, K, lda, bn, &mx))) return rc;
     static int trace_on = getenv("CE_GEMM_TRACE") ? 1 : 0;
     static int trace_seq = 0;
     int trace = trace_on ? (++trace_seq | 256) : 0;
     // the partial tile of a block must fit its stages (launch<> sizes them the same way)
-    size_t stage_b = (size_t)nacc * BM * BK * 2 + (size_t)bn * BK * 2;
-    size_t budget_b = bn <= 16 ? 100 * 1024 : 200 * 1024;
+    size_t stage_b = (size_t)BM * BK * 2 + (size_t)bn * BK * 2;
+    size_t budget_b = (bn <= 16 || nacc == 2) ? 100 * 1024 : 200 * 1024;
     size_t n_st = budget_b / stage_b > 8 ? 8 : (budget_b / stage_b < 2 ? 2 : budget_b / stage_b);
-    int cluster = cluster_split_k() && splits > 1 && splits <= 8 && (size_t)nacc * bn * BM * 4 <= n_st * stage_b;
+    int cluster = cluster_split_k() && splits > 1 && splits <= 8 && (size_t)bn * BM * 4 <= n_st * stage_b;
     TcArgs a{C, scratch, counters, status, M, N, K, ldc, mode, splits, (kblocks + splits - 1) / splits, kblocks, trace, cluster, 0};
 #define TC_CASE(BN_)                                                                  \
     case BN_:                                                                         \

@@ -7,8 +7,10 @@
 // tokens still fill the tensor core's M dimension and stream each weight exactly once.  Both operands
 // are K-major as stored (W is [out, in], x is [tokens, in]), in 128-byte-swizzled tiles of 64 k.
 //
-// One CTA computes one 128 x BN output tile (two accumulators for SwiGLU: gate and up rows of the
-// same features), optionally over a slice of K (split-K, used when there are fewer tiles than SMs).
+// Up to 256 tokens: one CTA computes one 128 x BN output tile, optionally over a slice of K (split-K, used
+// when there are fewer tiles than SMs).  For SwiGLU the 128 rows of a tile are 64 gate rows and the 64 up
+// rows of the same features (two TMA boxes), so it is one product with one accumulator like the others,
+// and it is never split.  More tokens: persistent kernels further down (CTA pairs with cta_group::2).
 // Warp 0 issues the TMA loads, warp 1 owns tensor memory and issues the MMAs, warps 2-5 read the
 // accumulators back (tcgen05.ld) and run the epilogue.  With split-K every CTA writes its partial
 // sums to scratch memory; the CTA that arrives last for a tile adds the partials in split order
@@ -123,7 +125,7 @@ __device__ __forceinline__ void cluster_sync_all() {
 
 struct TcArgs {
     void* out;               // [M, ldo] bf16 or float32
-    float* scratch;          // split-K partials: [splits][tiles][nacc][BN][128]
+    float* scratch;          // split-K partials: [splits][tiles][BN][128]
     int* counters;           // one per output tile, zero between launches
     int* status;
     int M, N, K, ldo, mode, splits, kblocks_per_split, kblocks, trace;
@@ -320,7 +322,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
 #pragma unroll 1
                 for (int c = 0; c < BN; c += 16) {
                     if (c >= m_valid) break;
-                    float g[16], u[16];
+                    float g[16];
                     tmem_ld16(taddr + c, g);
                     if (n < a.N) {
                         if (a.mode == TC_ACCUM_F32) {
@@ -346,12 +348,12 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
 #pragma unroll 1
             for (int c = 0; c < BN; c += 16) {
                 if (c >= m_valid) break;
-                float g[16], u[16];
+                float g[16];
                 if (nkb > 0 && ok) {
                     tmem_ld16(taddr + c, g);
                 } else {
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) g[j] = u[j] = 0.f;
+                    for (int j = 0; j < 16; ++j) g[j] = 0.f;
                 }
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
@@ -361,7 +363,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
                 }
             }
         } else {
-            // partial sums to scratch: [split][tile][acc][m][128]
+            // partial sums to scratch: [split][tile][m][128]
             int tile = blockIdx.y * gridDim.x + blockIdx.x;
             int n_tiles = gridDim.x * gridDim.y;
             float* mine = a.scratch + ((size_t)split * n_tiles + tile) * BN * BM;
@@ -369,12 +371,12 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
 #pragma unroll 1
                 for (int c = 0; c < BN; c += 16) {
                     if (c >= m_valid) break;
-                    float g[16], u[16];
+                    float g[16];
                     if (nkb > 0) {
                         tmem_ld16(taddr + c, g);
                         } else {
 #pragma unroll
-                        for (int j = 0; j < 16; ++j) g[j] = u[j] = 0.f;
+                        for (int j = 0; j < 16; ++j) g[j] = 0.f;
                     }
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
@@ -400,15 +402,15 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
                     size_t split_stride = (size_t)n_tiles * BN * BM;
                     const float* p0 = a.scratch + (size_t)tile * BN * BM + row;
                     for (int mb = 0; mb < m_valid; mb += TB) {
-                        float g[TB], u[TB], xv[TB];
+                        float g[TB], xv[TB];
 #pragma unroll
                         for (int j = 0; j < TB; ++j) {
-                            g[j] = u[j] = 0.f;
+                            g[j] = 0.f;
                             xv[j] = (a.mode == TC_ACCUM_F32 && mb + j < m_valid)
                                         ? __ldcg((const float*)a.out + (size_t)(m0 + mb + j) * a.ldo + n) : 0.f;
                         }
                         for (int s0 = 0; s0 < a.splits; s0 += 8) {
-                            float tg[8][TB], tu[8][TB];
+                            float tg[8][TB];
 #pragma unroll
                             for (int s = 0; s < 8; ++s) {
                                 const float* p = p0 + (size_t)(s0 + s) * split_stride;
@@ -416,20 +418,19 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
                                 for (int j = 0; j < TB; ++j) {
                                     bool in = s0 + s < a.splits && mb + j < m_valid;
                                     tg[s][j] = in ? __ldcg(p + (size_t)(mb + j) * BM) : 0.f;
-                                    tu[s][j] = 0.f;
                                 }
                             }
 #pragma unroll
                             for (int s = 0; s < 8; ++s) {
 #pragma unroll
-                                for (int j = 0; j < TB; ++j) { g[j] += tg[s][j]; u[j] += tu[s][j]; }
+                                for (int j = 0; j < TB; ++j) g[j] += tg[s][j];
                             }
                         }
 #pragma unroll
                         for (int j = 0; j < TB; ++j) {
                             if (mb + j >= m_valid) continue;
                             if (a.mode == TC_ACCUM_F32) ((float*)a.out)[(size_t)(m0 + mb + j) * a.ldo + n] = xv[j] + g[j];
-                            else epilogue_store(a, m0 + mb + j, n, g[j], u[j]);
+                            else epilogue_store(a, m0 + mb + j, n, g[j], 0.f);
                         }
                     }
                 }
@@ -458,7 +459,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
                     int n = n0 + row;
                     if (n >= a.N) continue;
                     uint32_t off = (uint32_t)(m * BM + row) * 4u;
-                    float g = 0.f, u = 0.f;
+                    float g = 0.f;
                     for (int sp = 0; sp < a.splits; ++sp) {
                         uint32_t remote = map_to_cta(part0 + off, (uint32_t)sp);
                         g += ld_cluster_f32(remote);
@@ -467,7 +468,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
                         float* xp = (float*)a.out + (size_t)(m0 + m) * a.ldo + n;
                         *xp = *xp + g;
                     } else {
-                        epilogue_store(a, m0 + m, n, g, u);
+                        epilogue_store(a, m0 + m, n, g, 0.f);
                     }
                 }
             }

@@ -1119,14 +1119,24 @@ extern "C" int ce_gemm_tc(const void* A, const void* W, void* C, int M, int N, i
         static int use_pairs = getenv("CE_GEMM_NO_PAIRS") ? 0 : 1;
         if (use_pairs && N >= 2 * BM) {     // CTA pairs: 256 weight rows a tile, each CTA loads half of the tokens
             // SwiGLU: 128 gate rows and their 128 up rows a pair tile (boxes of 64 rows), 256 tokens as well
+            // 256 tokens a tile, or 128 where that needs clearly fewer waves of pairs (a few hundred tokens):
+            // waves x time of a tile decides; a tile of 128 tokens takes 0.75 of the time of one of 256 (measured)
+            long long rows_t = nacc == 2 ? (N + BM - 1) / BM : (N + 2 * BM - 1) / (2 * BM);
+            long long n_pairs = ce_sm_count() / 2;
+            long long t256 = rows_t * ((M + 255) / 256), t128 = rows_t * ((M + 127) / 128);
+            double c256 = (double)((t256 + n_pairs - 1) / n_pairs), c128 = (double)((t128 + n_pairs - 1) / n_pairs) * 0.75;
+            static int force_tok = getenv("CE_GEMM_PAIR_TOKENS") ? atoi(getenv("CE_GEMM_PAIR_TOKENS")) : 0;
+            int ptok = force_tok ? force_tok : (c128 < c256 ? 128 : 256);
             CUtensorMap px2, pw2;
-            if ((prc = get_map(A, M, K, lda, 128, &px2))) return prc;
-            long long ptiles_m = (M + 255) / 256;
+            if ((prc = get_map(A, M, K, lda, ptok / 2, &px2))) return prc;
+            long long ptiles_m = (M + ptok - 1) / ptok;
             if (nacc == 2) {
                 if ((prc = get_map(W, (long long)N * 2, K, K, BM / 2, &pw2))) return prc;
-                return launch_pair<256, true, 2>(pw2, px2, pa, (int)((N + BM - 1) / BM), (int)ptiles_m, stream);
+                return ptok == 128 ? launch_pair<128, true, 2>(pw2, px2, pa, (int)rows_t, (int)ptiles_m, stream)
+                                   : launch_pair<256, true, 2>(pw2, px2, pa, (int)rows_t, (int)ptiles_m, stream);
             }
-            return launch_pair<256, false, 2>(pw, px2, pa, (int)((N + 2 * BM - 1) / (2 * BM)), (int)ptiles_m, stream);
+            return ptok == 128 ? launch_pair<128, false, 2>(pw, px2, pa, (int)rows_t, (int)ptiles_m, stream)
+                               : launch_pair<256, false, 2>(pw, px2, pa, (int)rows_t, (int)ptiles_m, stream);
         }
         return nacc == 2 ? launch_persistent<128, 2>(pw, px, pa, (int)tiles_n, (int)tiles_m, stream)
                          : launch_persistent<256, 1>(pw, px, pa, (int)tiles_n, (int)tiles_m, stream);

@@ -1,6 +1,6 @@
 // Token selection on the device: greedy pick, and temperature / top-k / top-p / min-p sampling.
 //
-// One block per logits row (float32, [rows, V]).  The meaning of the options is the reference's
+// One block per logits row (float32, [rows, V]), or a cluster of eight for a large vocabulary.  The meaning of the options is the reference's
 // host sampler's (src/sampling.rs:137-181): logits are scaled by 1/max(T, 1e-5); top-k keeps the
 // k largest; the softmax is taken over what top-k kept; top-p keeps the shortest prefix of the
 // descending order whose mass reaches p; min-p drops tokens below min_p times the largest
@@ -11,12 +11,13 @@
 // The draw is an exact Gumbel-max over the kept set, as in the reference's device sampler when no
 // nucleus is asked for (src/kernels/sampling.cu:161-182), with its counter-based uniform numbers
 // (splitmix64 finaliser of seed and index, src/kernels/sampling.cu:30-42).  Unlike the reference,
-// top-p is exact for any distribution: the cut is found by bisection on the logit value with
-// block-wide sums in a fixed order, so no row ever goes back to the host.  Tokens that tie with
+// top-p is exact for any distribution: the cut is found by a search on the logit value (four parts a
+// pass) with sums over the row in a fixed order, so no row ever goes back to the host.  Tokens that tie with
 // the cut value are all kept.
 #include "common.cuh"
 
 #define SMP_THREADS 1024
+#define SMP_MAX_BLOCKS 8        // blocks that may share a row
 
 __device__ __forceinline__ unsigned int smp_key(float f) {   // order-preserving float -> uint
     unsigned int u = (unsigned int)__float_as_int(f);
@@ -56,22 +57,128 @@ __device__ void smp_argmax(float& v, int& i, float* sv, int* si) {
     i = bi;
 }
 
-__device__ unsigned int smp_count_ge(const float* l, int V, float inv_t, unsigned int key, float* scratch) {
-    int c = 0;
-    for (int i = threadIdx.x; i < V; i += SMP_THREADS) c += smp_key(l[i] * inv_t) >= key;
-    // counts are exact in float up to 2^24; V is far below that
-    return (unsigned int)(ce_block_sum((float)c, scratch) + 0.5f);
+// ---- a row is shared by the blocks of a cluster ------------------------------------------------
+// Block `rank` of `nb` takes elements rank*SMP_THREADS + thread, then every nb*SMP_THREADS-th.  A reduction
+// is taken over the block first (fixed order), written to a slot in the block's shared memory, and after a
+// cluster barrier every block adds (or compares) the slots of all blocks in rank order: the same value in
+// every block, the same from run to run.  Slots alternate between two sets, so one barrier a reduction
+// is enough (a set is written again only after the barrier of the reduction in between).
+struct SmpShared {
+    float sv[32];
+    int si[32];
+    float scratch[32];
+    float sw[32];
+    float xf[2][4];
+    int xi[2];
+};
+__device__ __forceinline__ uint32_t smp_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ float smp_peer_f(const float* p, int rank) {
+    uint32_t a;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(a) : "r"(smp_smem(p)), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ int smp_peer_i(const int* p, int rank) {
+    uint32_t a;
+    int v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(a) : "r"(smp_smem(p)), "r"(rank));
+    asm volatile("ld.shared::cluster.s32 %0, [%1];" : "=r"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ void smp_cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
-__device__ float smp_mass_ge(const float* l, int V, float inv_t, unsigned int key, unsigned int floor_key, float zmax,
-                             float* scratch) {
-    float s = 0.f;
-    for (int i = threadIdx.x; i < V; i += SMP_THREADS) {
+// (largest value, lowest index) over the row
+__device__ void smp_row_argmax(float& v, int& i, SmpShared& sh, int nb, int& set) {
+    smp_argmax(v, i, sh.sv, sh.si);
+    if (nb > 1) {
+        if (threadIdx.x == 0) { sh.xf[set][0] = v; sh.xi[set] = i; }
+        smp_cluster_sync();
+        float pv[SMP_MAX_BLOCKS];
+        int pi[SMP_MAX_BLOCKS];
+#pragma unroll
+        for (int r = 0; r < SMP_MAX_BLOCKS; ++r) {         // all loads on their way before the first is used
+            pv[r] = r < nb ? smp_peer_f(&sh.xf[set][0], r) : -INFINITY;
+            pi[r] = r < nb ? smp_peer_i(&sh.xi[set], r) : 0x7fffffff;
+        }
+        float bv = pv[0];
+        int bi = pi[0];
+#pragma unroll
+        for (int r = 1; r < SMP_MAX_BLOCKS; ++r)
+            if (r < nb && (pv[r] > bv || (pv[r] == bv && pi[r] < bi))) { bv = pv[r]; bi = pi[r]; }
+        v = bv; i = bi;
+        set ^= 1;
+    }
+}
+// sums of three values over the row: warps by shuffles, the block's warps in index order, the blocks in rank order
+__device__ void smp_row_sum3(float (&v)[3], SmpShared& sh, int nb, int& set) {
+#pragma unroll
+    for (int j = 0; j < 3; ++j)
+        for (int o = 16; o > 0; o >>= 1) v[j] += __shfl_down_sync(0xffffffffu, v[j], o);
+    int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    __syncthreads();
+    if (lane == 0) { sh.sv[warp] = v[0]; sh.scratch[warp] = v[1]; sh.sw[warp] = v[2]; }
+    __syncthreads();
+    float t[3] = {0.f, 0.f, 0.f};
+    for (int w = 0; w < SMP_THREADS / 32; ++w) { t[0] += sh.sv[w]; t[1] += sh.scratch[w]; t[2] += sh.sw[w]; }
+    if (nb > 1) {
+        if (threadIdx.x == 0) { sh.xf[set][0] = t[0]; sh.xf[set][1] = t[1]; sh.xf[set][2] = t[2]; }
+        smp_cluster_sync();
+        float pv[3][SMP_MAX_BLOCKS];
+#pragma unroll
+        for (int j = 0; j < 3; ++j)
+#pragma unroll
+            for (int r = 0; r < SMP_MAX_BLOCKS; ++r) pv[j][r] = r < nb ? smp_peer_f(&sh.xf[set][j], r) : 0.f;
+#pragma unroll
+        for (int j = 0; j < 3; ++j) {
+            t[j] = 0.f;
+#pragma unroll
+            for (int r = 0; r < SMP_MAX_BLOCKS; ++r) t[j] += pv[j][r];
+        }
+        set ^= 1;
+    }
+#pragma unroll
+    for (int j = 0; j < 3; ++j) v[j] = t[j];
+}
+
+// how many elements of the row have a key >= each of three keys (exact in float: V < 2^24)
+__device__ void smp_count_ge3(const float* l, int V, float inv_t, const unsigned int (&key)[3], unsigned int (&cnt)[3],
+                              SmpShared& sh, int first, int stride, int nb, int& set) {
+    int c[3] = {0, 0, 0};
+    for (int i = first; i < V; i += stride) {
+        unsigned int k = smp_key(l[i] * inv_t);
+        c[0] += k >= key[0]; c[1] += k >= key[1]; c[2] += k >= key[2];
+    }
+    float f[3] = {(float)c[0], (float)c[1], (float)c[2]};
+    smp_row_sum3(f, sh, nb, set);
+#pragma unroll
+    for (int j = 0; j < 3; ++j) cnt[j] = (unsigned int)(f[j] + 0.5f);
+}
+// mass exp(z - zmax) of the elements with key >= max(key[j], floor_key), for three keys
+__device__ void smp_mass_ge3(const float* l, int V, float inv_t, const unsigned int (&key)[3], unsigned int floor_key,
+                             float zmax, float (&mass)[3], SmpShared& sh, int first, int stride, int nb, int& set) {
+    float s[3] = {0.f, 0.f, 0.f};
+    for (int i = first; i < V; i += stride) {
         float z = l[i] * inv_t;
         unsigned int k = smp_key(z);
-        if (k >= key && k >= floor_key) s += expf(z - zmax);
+        if (k >= floor_key && k >= key[0]) {          // key[0] <= key[1] <= key[2]
+            float e = expf(z - zmax);
+            s[0] += e;
+            if (k >= key[1]) s[1] += e;
+            if (k >= key[2]) s[2] += e;
+        }
     }
-    return ce_block_sum(s, scratch);
+    smp_row_sum3(s, sh, nb, set);
+#pragma unroll
+    for (int j = 0; j < 3; ++j) mass[j] = s[j];
+}
+// The three keys that cut (lo, hi] into four parts: lo < m1 <= m2 <= m3 <= hi
+__device__ __forceinline__ void smp_cuts(unsigned int lo, unsigned int hi, unsigned int (&m)[3]) {
+    unsigned long long w = (unsigned long long)hi - lo;
+#pragma unroll
+    for (int j = 0; j < 3; ++j) m[j] = lo + (unsigned int)((w * (j + 1) + 3) / 4);
 }
 
 // params per row: temperature, top_p, min_p (float), top_k (int), seed (u64)
@@ -81,14 +188,15 @@ struct SampleRow {
     unsigned long long seed;
 };
 
+// grid: rows x nb blocks, the nb blocks of a row form a cluster
 __global__ void __launch_bounds__(SMP_THREADS) sample_kernel(const float* __restrict__ logits, int V,
                                                             const SampleRow* __restrict__ params,
-                                                            int* __restrict__ out) {
+                                                            int* __restrict__ out, int nb) {
     ce_pdl_begin();
-    __shared__ float sv[32];
-    __shared__ int si[32];
-    __shared__ float scratch[32];
-    int r = blockIdx.x;
+    __shared__ SmpShared sh;
+    int r = blockIdx.x / nb, rank = blockIdx.x - r * nb;
+    int first = rank * SMP_THREADS + threadIdx.x, stride = nb * SMP_THREADS;
+    int set = 0;
     const float* l = logits + (size_t)r * V;
     SampleRow p = params[r];
     bool greedy = p.temperature <= 0.f || p.top_k == 1;
@@ -96,35 +204,50 @@ __global__ void __launch_bounds__(SMP_THREADS) sample_kernel(const float* __rest
 
     float bv = -INFINITY;
     int bi = 0x7fffffff;
-    for (int i = threadIdx.x; i < V; i += SMP_THREADS) {
+    for (int i = first; i < V; i += stride) {
         float z = l[i] * inv_t;
         if (z > bv) { bv = z; bi = i; }
     }
-    smp_argmax(bv, bi, sv, si);
+    smp_row_argmax(bv, bi, sh, nb, set);
     if (greedy) {
-        if (threadIdx.x == 0) out[r] = bi == 0x7fffffff ? 0 : bi;
+        if (rank == 0 && threadIdx.x == 0) out[r] = bi == 0x7fffffff ? 0 : bi;
+        if (nb > 1) smp_cluster_sync();     // nobody's slots go away while another block may still read them
         return;
     }
     float zmax = bv;
     unsigned int floor_key = 0;       // tokens with key < floor_key are dropped
 
     if (p.top_k > 0 && p.top_k < V) {
-        // largest key with count(key' >= key) >= k : bisection over the 32-bit key space
+        // largest key with count(key' >= key) >= k: search over the 32-bit key space, four parts a pass
         unsigned int lo = 0, hi = smp_key(zmax);
         while (lo < hi) {
-            unsigned int mid = lo + (hi - lo + 1) / 2;
-            if (smp_count_ge(l, V, inv_t, mid, scratch) >= (unsigned int)p.top_k) lo = mid; else hi = mid - 1;
+            unsigned int m[3], c[3];
+            smp_cuts(lo, hi, m);
+            smp_count_ge3(l, V, inv_t, m, c, sh, first, stride, nb, set);
+            unsigned int k = (unsigned int)p.top_k;
+            if (c[2] >= k) lo = m[2];
+            else if (c[1] >= k) { lo = m[1]; hi = m[2] - 1; }
+            else if (c[0] >= k) { lo = m[0]; hi = m[1] - 1; }
+            else hi = m[0] - 1;
         }
         floor_key = lo;
     }
     if (p.top_p < 1.0f) {
-        float total = smp_mass_ge(l, V, inv_t, 0u, floor_key, zmax, scratch);
-        float target = p.top_p * total;
+        unsigned int zero[3] = {0u, 0u, 0u};
+        float tot[3];
+        smp_mass_ge3(l, V, inv_t, zero, floor_key, zmax, tot, sh, first, stride, nb, set);
+        float target = p.top_p * tot[0];
         // largest key with mass(key' >= key) >= target
         unsigned int lo = floor_key, hi = smp_key(zmax);
         while (lo < hi) {
-            unsigned int mid = lo + (hi - lo + 1) / 2;
-            if (smp_mass_ge(l, V, inv_t, mid, floor_key, zmax, scratch) >= target) lo = mid; else hi = mid - 1;
+            unsigned int m[3];
+            float ms[3];
+            smp_cuts(lo, hi, m);
+            smp_mass_ge3(l, V, inv_t, m, floor_key, zmax, ms, sh, first, stride, nb, set);
+            if (ms[2] >= target) lo = m[2];
+            else if (ms[1] >= target) { lo = m[1]; hi = m[2] - 1; }
+            else if (ms[0] >= target) { lo = m[0]; hi = m[1] - 1; }
+            else hi = m[0] - 1;
         }
         floor_key = max(floor_key, lo);
     }
@@ -137,22 +260,41 @@ __global__ void __launch_bounds__(SMP_THREADS) sample_kernel(const float* __rest
     }
     float gv = -INFINITY;
     int gi = 0x7fffffff;
-    for (int i = threadIdx.x; i < V; i += SMP_THREADS) {
+    for (int i = first; i < V; i += stride) {
         float z = l[i] * inv_t;
         if (smp_key(z) < floor_key) continue;
         float u = smp_uniform(p.seed, (unsigned long long)i);
         float g = z - logf(-logf(u));
         if (g > gv) { gv = g; gi = i; }
     }
-    smp_argmax(gv, gi, sv, si);
-    if (threadIdx.x == 0) out[r] = gi == 0x7fffffff ? bi : gi;
+    smp_row_argmax(gv, gi, sh, nb, set);
+    if (rank == 0 && threadIdx.x == 0) out[r] = gi == 0x7fffffff ? bi : gi;
+    if (nb > 1) smp_cluster_sync();
 }
 
 extern "C" int ce_sample(const float* logits, int rows, int V, const void* params, int* out, cudaStream_t stream) {
     if (rows == 0) return CE_OK;
     if (!logits || !params || !out) return ce_fail(CE_ERR_ARG, "ce_sample: null pointer");
     if (V <= 0 || V >= (1 << 24)) return ce_fail(CE_ERR_SIZE, "ce_sample: vocabulary %d not in 1..2^24", V);
-    ce_launch(sample_kernel, rows, SMP_THREADS, 0, stream, logits, V, (const SampleRow*)params, out);
+    // a large vocabulary is shared by the 8 blocks of a cluster (8 SMs a row)
+    // (as many blocks a row as leave every row a place on the 148 SMs at once)
+    int nb = 1;
+    if (V >= 16384)
+        while (nb < SMP_MAX_BLOCKS && (long long)rows * nb * 2 <= ce_sm_count()) nb *= 2;
+    if ((long long)rows * nb > 2147483647LL) return ce_fail(CE_ERR_SIZE, "ce_sample: %d rows", rows);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(rows * nb));
+    cfg.blockDim = dim3(SMP_THREADS);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = nb; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ce_pdl_enabled() ? 2 : 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, sample_kernel, logits, V, (const SampleRow*)params, out, nb);
+    if (e != cudaSuccess) return ce_fail(CE_ERR_CUDA, "ce_sample: %s", cudaGetErrorString(e));
     return ce_check_launch("ce_sample");
 }
 

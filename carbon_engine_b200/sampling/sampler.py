@@ -41,6 +41,26 @@ def fresh_seed() -> int:
 class Sampler:
     def __init__(self, device: torch.device):
         self.device = device
+        self._rows_host = None      # pinned staging for the per-row parameters: the copy never blocks the host
+        self._rows_dev = None
+        self._rows_free = None      # recorded after the copy: the staging buffer may be rewritten once it has passed
+
+    def _upload_rows(self, blob: bytes) -> torch.Tensor:
+        n = len(blob)
+        if self._rows_host is None or self._rows_host.numel() < n:
+            size = max(4096, 2 * n)
+            self._rows_host = torch.empty(size, dtype=torch.uint8, pin_memory=self.device.type == "cuda")
+            self._rows_dev = torch.empty(size, dtype=torch.uint8, device=self.device)
+            self._rows_free = None
+        if self._rows_free is not None:
+            self._rows_free.synchronize()
+        self._rows_host[:n] = torch.frombuffer(bytearray(blob), dtype=torch.uint8)
+        self._rows_dev[:n].copy_(self._rows_host[:n], non_blocking=True)
+        if self.device.type == "cuda":
+            if self._rows_free is None:
+                self._rows_free = torch.cuda.Event()
+            self._rows_free.record()
+        return self._rows_dev[:n]
 
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], seeds: Sequence[int],
                steps: Sequence[int], prompts: Optional[Sequence[Sequence[int]]] = None,
@@ -62,9 +82,7 @@ class Sampler:
             return out
         rows = [(p.temperature, p.top_p, p.min_p, p.top_k if p.top_k > 0 else 0, step_seed(s, st))
                 for p, s, st in zip(params, seeds, steps)]
-        blob = np.frombuffer(ops.pack_sample_rows(rows), dtype=np.uint8)
-        dev = torch.from_numpy(blob.copy()).to(self.device)
-        ops.sample(logits, dev, out)
+        ops.sample(logits, self._upload_rows(ops.pack_sample_rows(rows)), out)
         return out
 
     def _penalties(self, logits, params, prompts, outputs) -> None:

@@ -167,14 +167,14 @@ def main() -> int:
     need = decode_bytes(cfg, args.layers, args.batch, args.context + args.warmup + args.steps // 2)
     achieved = need / (ms / 1e3) / 1e9
     out = {
-        "metric": "decode tok/s at batch 8 (Qwen3-8B sizes, bf16, 2048-token contexts)", "value": round(main_run["tokens_per_s"], 1),
+        "metric": f"decode tok/s at batch {args.batch} (Qwen3-8B sizes, bf16, {args.context}-token contexts)", "value": round(main_run["tokens_per_s"], 1),
         "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 4),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic: seeded random weights, seeded uniform-random token ids", "impl": "ours",
         "config": {"model": "Qwen3-8B sizes", "layers": args.layers, "layers_of_model": SIZES_8B["num_hidden_layers"],
                    "hidden_size": cfg["hidden_size"], "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
                    "head_dim": cfg["head_dim"], "intermediate_size": cfg["intermediate_size"], "vocab_size": cfg["vocab_size"],
-                   "global_batch": args.batch, "seq_len": args.context, "max_seq_len": 4096, "new_tokens": args.steps,
+                   "global_batch": args.batch, "seq_len": args.context, "max_seq_len": h.max_seq_len, "new_tokens": args.steps,
                    "page_size": h.page_size, "parallelism": "single GPU", "cuda_graphs": h.graphs,
                    "l2": "inputs larger than L2 (weights over 15 GB per step)", "peaks": pk["source"]},
         "clocks": clocks.summary(t0, t1),

@@ -22,8 +22,9 @@ class BenchHarness:
         self.config = Qwen3Config.from_dict(raw)
         self.context, self.new_tokens, self.page_size, self.max_batch = context, new_tokens, page_size, max_batch
         per_seq = (context + new_tokens + page_size - 1) // page_size * page_size
+        self.max_seq_len = max(4096, per_seq)
         self.engine = Engine(config=self.config, dtype="bfloat16", dummy_weight=True, seed=seed,
-                             kv_tokens=max_batch * per_seq + 4096, page_size=page_size, max_seq_len=4096,
+                             kv_tokens=max_batch * per_seq + 4096, page_size=page_size, max_seq_len=max(4096, per_seq),
                              max_running_requests=max_batch, max_prefill_tokens=4096, cuda_graphs=graphs)
         self.graphs = bool(graphs and self.engine.runner.graphs_enabled)
         self.rng = np.random.default_rng(seed)

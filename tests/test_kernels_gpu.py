@@ -297,23 +297,29 @@ def gumbel_reference(logits_row, temperature, kept, seed):
     return best_i
 
 
-def test_sampler_options_follow_the_host_rules(ops):
+@pytest.mark.parametrize("V,copies", [(1000, 1), (16384 + 37, 1), (40009, 4), (40009, 20)])
+def test_sampler_options_follow_the_host_rules(ops, V, copies):
+    """Small vocabularies take one block a row; from 16,384 entries on a cluster of up to 8 blocks shares
+    a row (8, 4 or 1 blocks a row here, by the number of rows).  The rules and the draws are the same."""
     rng = np.random.default_rng(5)
-    V = 1000
-    logits = torch.from_numpy(rng.normal(size=(6, V)).astype(np.float32) * 3).to(dev())
-    rows = [(0.0, 1.0, 0.0, 0, 1), (0.8, 1.0, 0.0, 1, 2), (0.8, 1.0, 0.0, 5, 3), (1.3, 0.6, 0.0, 0, 4),
+    base = [(0.0, 1.0, 0.0, 0, 1), (0.8, 1.0, 0.0, 1, 2), (0.8, 1.0, 0.0, 5, 3), (1.3, 0.6, 0.0, 0, 4),
             (0.7, 1.0, 0.2, 0, 5), (1.0, 0.9, 0.05, 50, 6)]
+    rows = [(t, p, m, k, seed + 10 * c) for c in range(copies) for (t, p, m, k, seed) in base]
+    logits = torch.from_numpy(rng.normal(size=(len(rows), V)).astype(np.float32) * 3).to(dev())
     got = run_sampler(ops, logits, rows)
     host = logits.cpu().numpy()
-    assert got[0] == int(host[0].argmax()) and got[1] == int(host[1].argmax())     # temperature 0, top_k 1: greedy
-    for r in range(2, 6):
-        t, p, m, k, seed = rows[r]
+    for r, (t, p, m, k, seed) in enumerate(rows):
+        if r % 6 < 2:                                                              # temperature 0, top_k 1: greedy
+            assert got[r] == int(host[r].argmax())
+            continue
+        if copies > 1 and r >= 12:                                                 # (the host loop is slow: two copies are checked in full)
+            continue
         kept, _ = plain.sample_kept_set(host[r], t, k, p, m)
         assert got[r] in set(kept.tolist()), r
         assert got[r] == gumbel_reference(host[r], t, kept, seed), r
     assert run_sampler(ops, logits, rows) == got                                    # same seeds, same tokens
-    other = run_sampler(ops, logits, [(t, p, m, k, s + 100) for (t, p, m, k, s) in rows])
-    assert other[:2] == got[:2] and other[2:] != got[2:]
+    other = run_sampler(ops, logits, [(t, p, m, k, s + 1000) for (t, p, m, k, s) in rows])
+    assert other[:2] == got[:2] and other[2:6] != got[2:6]
 
 
 def test_sampler_draws_from_the_softmax(ops):

@@ -99,9 +99,10 @@ def step_meta(seqs):
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("nh,nkv,d,rd,ps", [(6, 3, 48, 48, 8), (4, 1, 16, 16, 16), (5, 5, 80, 32, 4), (2, 2, 256, 256, 64),
                                             (8, 2, 128, 128, 64), (3, 1, 64, 64, 16), (4, 2, 192, 192, 8), (2, 1, 128, 64, 16)])
-def test_qk_norm_rope_and_cache_write(ops, dtype, nh, nkv, d, rd, ps):
+@pytest.mark.parametrize("first", [9, 270])        # few tokens: a warp a head; from 256 tokens on a warp takes several heads of a token
+def test_qk_norm_rope_and_cache_write(ops, dtype, nh, nkv, d, rd, ps, first):
     torch.manual_seed(1)
-    seqs = [(5, 9), (0, 3), (30, 1)]
+    seqs = [(5, first), (0, 3), (30, 1)]
     T = sum(n for _, n in seqs)
     table, kp, vp = paged_layout([c + n for c, n in seqs], ps, nkv, d, dtype)
     qkv = (torch.randn(T, (nh + 2 * nkv) * d, device=dev()) * 2).to(dtype)
@@ -110,7 +111,7 @@ def test_qk_norm_rope_and_cache_write(ops, dtype, nh, nkv, d, rd, ps):
     positions, sot, slots = step_meta(seqs)
     half = rd // 2
     inv = theta ** (-torch.arange(half, dtype=torch.float64) * 2 / rd)
-    ang = torch.arange(64, dtype=torch.float64)[:, None] * inv[None]
+    ang = torch.arange(320, dtype=torch.float64)[:, None] * inv[None]
     cos, sin = ang.cos().float().to(dev()), ang.sin().float().to(dev())
     src = qkv.clone()
     st = status()

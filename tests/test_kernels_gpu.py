@@ -438,7 +438,8 @@ def run_mma_attention(seqs, nh, nkv, d, ps, window, scale, seed=0, far=None, ext
 
 
 @pytest.mark.parametrize("nh,nkv,d,ps,window", [(32, 8, 128, 64, 0), (6, 3, 48, 8, 0), (8, 2, 32, 16, 0), (4, 4, 16, 4, 0),
-                                                 (3, 1, 256, 32, 0), (40, 2, 64, 16, 0), (6, 2, 64, 8, 37), (4, 1, 80, 16, 300)])
+                                                 (3, 1, 256, 32, 0), (40, 2, 64, 16, 0), (6, 2, 64, 8, 37), (4, 1, 80, 16, 300),
+                                                 (4, 2, 192, 16, 0), (2, 1, 128, 128, 150)])
 def test_mma_attention_decode_and_prefill_mixed(nh, nkv, d, ps, window):
     # decode rows at contexts around the split (256) and tile (64) edges, portions with and without a cached prefix
     seqs = [(0, 19), (255, 1), (256, 1), (700, 1), (61, 7), (0, 2), (126, 130), (0, 1), (63, 1), (300, 65)]

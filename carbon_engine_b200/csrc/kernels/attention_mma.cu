@@ -895,7 +895,8 @@ extern "C" long long ce_attention_decode_scratch(int n_seqs, int nh, int d, int 
 }
 
 // The first n_seqs sequences of the step bring one token each (tokens 0 .. n_seqs-1).
-// max_splits >= ceil(longest context / AM_SPLIT); it fixes the grid, not the result.
+// max_splits >= ceil(longest context / AM_SPLIT): the grid's upper bound; the split size is chosen from it
+// and from the number of sequences (see below), so results differ in rounding between bounds, not more.
 extern "C" int ce_attention_decode_split() { return AM_SPLIT; }
 // Kernels one decode attention call launches: 1 when the last block merges the splits, else 2.
 // (of the call before: the in-cluster merge needs one kernel, the merge kernel a second)

@@ -130,7 +130,6 @@ struct TcArgs {
     int* status;
     int M, N, K, ldo, mode, splits, kblocks_per_split, kblocks, trace;
     int cluster;             // 1: the splits of a tile form a cluster and add their partial sums through shared memory
-    int l2_ahead;            // pair kernel: weights are requested into L2 this many rounds before their copy (0: off)
 };
 
 __device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + __expf(-g)) * u; }
@@ -684,11 +683,6 @@ __device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* m
     asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
                  ::"r"(smem_u32(dst)), "l"(map), "r"(cluster_bar), "r"(x), "r"(y) : "memory");
 }
-// Ask for a box to be brought into L2 (no shared memory, no barrier): weights that come from DRAM are
-// requested a few rounds before the copy that needs them.
-__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* map, int x, int y) {
-    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(map), "r"(x), "r"(y) : "memory");
-}
 __device__ __forceinline__ void umma2_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
     asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}"
                  ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
@@ -756,14 +750,6 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_pair_kernel(const __grid_cons
             for (int tile = pair; tile < total && ok; tile += n_pairs) {
                 int n0 = (tile / tiles_m) * (2 * ROWS_N) + rank * ROWS_N, m0 = (tile % tiles_m) * BN + rank * HALF_N;
                 for (int r = 0; r < rounds; ++r) {
-                    if (a.l2_ahead > 0 && r + a.l2_ahead < rounds) {
-#pragma unroll
-                        for (int j = 0; j < KSUB; ++j) {
-                            int kx = ((r + a.l2_ahead) * KSUB + j) * BK;
-                            tma_prefetch_2d(&map_w, kx, n0);
-                            if (GU) tma_prefetch_2d(&map_w, kx, a.N + n0);
-                        }
-                    }
                     if (wrapped) ok = mbar_wait_cluster(&empty_bar[s], ph ^ 1);
                     if (!ok) break;
                     uint32_t bar = map_to_cta(smem_u32(&full_bar[s]), 0);
@@ -1055,8 +1041,7 @@ extern "C" int ce_gemm_tc_splits(int M, int N, int K) {
     // up to 16 tokens: about two CTAs per SM, each with half an SM of shared memory; more tokens: one per SM
     int s = (target ? target : (bn <= 16 ? 296 : 148)) / tiles;
     if (s > kblocks / 4) s = kblocks / 4;      // at least four k-blocks per split
-    static double traffic = getenv("CE_GEMM_TRAFFIC") ? atof(getenv("CE_GEMM_TRAFFIC")) : 0.3;
-    int by_traffic = (int)(traffic * K / (4.0 * bn));   // partial sums cost S * bn * 4 / K of the weight bytes
+    int by_traffic = (int)(0.3 * K / (4.0 * bn));       // partial sums cost S * bn * 4 / K of the weight bytes: at most 30 %
     if (s > by_traffic) s = by_traffic;
     if (s > 8 && bn <= 16) s = 8;              // the last block of a tile then adds all partial sums in one trip to L2
     if (s > 16) s = 16;
@@ -1074,9 +1059,7 @@ extern "C" int ce_gemm_tc_trace(unsigned long long* out, unsigned int* count, un
 }
 
 extern "C" int ce_gemm_tc_tile_tokens(int M) {
-    static int max_bn = getenv("CE_GEMM_MAX_BN") ? atoi(getenv("CE_GEMM_MAX_BN")) : 256;
-    int bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
-    return bn > max_bn ? max_bn : bn;
+    return M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
 }
 
 // Scratch floats a product needs (0 without split-K).
@@ -1114,8 +1097,7 @@ extern "C" int ce_gemm_tc(const void* A, const void* W, void* C, int M, int N, i
         if (prc) return prc;
         if ((prc = get_map(A, M, K, lda, pbn, &px))) return prc;
         static int ptrace = getenv("CE_GEMM_TRACE") ? 1 : 0;
-        static int l2_ahead = getenv("CE_GEMM_L2_AHEAD") ? atoi(getenv("CE_GEMM_L2_AHEAD")) : 0;
-        TcArgs pa{C, scratch, counters, status, M, N, K, ldc, mode, 1, kblocks, kblocks, ptrace, 0, l2_ahead};
+        TcArgs pa{C, scratch, counters, status, M, N, K, ldc, mode, 1, kblocks, kblocks, ptrace, 0};
         static int use_pairs = getenv("CE_GEMM_NO_PAIRS") ? 0 : 1;
         if (use_pairs && N >= 2 * BM) {     // CTA pairs: 256 weight rows a tile, each CTA loads half of the tokens
             // SwiGLU: 128 gate rows and their 128 up rows a pair tile (boxes of 64 rows), 256 tokens as well
@@ -1125,8 +1107,7 @@ extern "C" int ce_gemm_tc(const void* A, const void* W, void* C, int M, int N, i
             long long n_pairs = ce_sm_count() / 2;
             long long t256 = rows_t * ((M + 255) / 256), t128 = rows_t * ((M + 127) / 128);
             double c256 = (double)((t256 + n_pairs - 1) / n_pairs), c128 = (double)((t128 + n_pairs - 1) / n_pairs) * 0.75;
-            static int force_tok = getenv("CE_GEMM_PAIR_TOKENS") ? atoi(getenv("CE_GEMM_PAIR_TOKENS")) : 0;
-            int ptok = force_tok ? force_tok : (c128 < c256 ? 128 : 256);
+            int ptok = c128 < c256 ? 128 : 256;
             CUtensorMap px2, pw2;
             if ((prc = get_map(A, M, K, lda, ptok / 2, &px2))) return prc;
             long long ptiles_m = (M + ptok - 1) / ptok;
@@ -1164,7 +1145,7 @@ extern "C" int ce_gemm_tc(const void* A, const void* W, void* C, int M, int N, i
     size_t budget_b = (bn <= 16 || nacc == 2) ? 100 * 1024 : 200 * 1024;
     size_t n_st = budget_b / stage_b > 8 ? 8 : (budget_b / stage_b < 2 ? 2 : budget_b / stage_b);
     int cluster = cluster_split_k() && splits > 1 && splits <= 8 && (size_t)bn * BM * 4 <= n_st * stage_b;
-    TcArgs a{C, scratch, counters, status, M, N, K, ldc, mode, splits, (kblocks + splits - 1) / splits, kblocks, trace, cluster, 0};
+    TcArgs a{C, scratch, counters, status, M, N, K, ldc, mode, splits, (kblocks + splits - 1) / splits, kblocks, trace, cluster};
 #define TC_CASE(BN_)                                                                  \
     case BN_:                                                                         \
         return nacc == 2 ? launch<BN_, 2>(mw, mx, a, grid, stream) : launch<BN_, 1>(mw, mx, a, grid, stream);

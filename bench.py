@@ -30,6 +30,8 @@ sys.path.insert(0, ROOT)
 SIZES_8B = dict(num_hidden_layers=36, hidden_size=4096, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
                 intermediate_size=12288, vocab_size=151936, rope_theta=1e6, rms_norm_eps=1e-6,
                 tie_word_embeddings=False, max_position_embeddings=40960)
+SIZES_14B = dict(SIZES_8B, num_hidden_layers=40, hidden_size=5120, num_attention_heads=40, intermediate_size=17408)
+SIZES_32B = dict(SIZES_8B, num_hidden_layers=64, hidden_size=5120, num_attention_heads=64, intermediate_size=25600)
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 
 
@@ -109,6 +111,41 @@ def prefill_flops(cfg, layers, T):
     return layers * (linear + attn) + 2 * V * H
 
 
+def serve_workload(args, BenchHarness) -> int:
+    """The two serving workloads of the larger model sizes, through the engine's public entry point."""
+    import numpy as np
+    if args.workload == "mixed-14b":
+        sizes, name, n_req, new_tokens, budget = SIZES_14B, "Qwen3-14B sizes", 32, 128, 2048
+        lens = np.random.default_rng(1).integers(128, 3073, size=n_req).tolist()
+    else:
+        sizes, name, n_req, new_tokens, budget = SIZES_32B, "Qwen3-32B sizes", 16, 256, 4096
+        lens = [1024] * n_req
+    layers = args.layers if args.layers != SIZES_8B["num_hidden_layers"] else sizes["num_hidden_layers"]
+    h = BenchHarness(dict(sizes, num_hidden_layers=layers), max_batch=n_req, context=max(lens), new_tokens=new_tokens,
+                     graphs=not args.no_graphs, step_tokens=budget)
+    h.serve(lens, new_tokens)                      # once untimed: kernels, graphs and allocations are warm afterwards
+    clocks = ClockSampler()
+    clocks.start()
+    time.sleep(0.3)
+    t0 = clocks.mark()
+    r = h.serve(lens, new_tokens)
+    t1 = clocks.mark()
+    clocks.stop()
+    print(json.dumps({
+        "metric": f"tokens/s (prompt + generated) of the {args.workload} workload ({name}, bf16)", "value": round(r["tokens_per_s"], 1),
+        "unit": "tokens/s", "n_gpus": 1, "generated_tokens_per_s": round(r["generated_per_s"], 1), "seconds": round(r["seconds"], 3),
+        "steps": r["steps"], "ms_per_step": round(r["seconds"] / r["steps"] * 1e3, 3), "prompt_tokens": r["prompt_tokens"],
+        "generated_tokens": r["generated_tokens"], "higher_is_better": True, "dtype": "bf16", "impl": "ours",
+        "data": "synthetic: seeded random weights, seeded uniform-random token ids",
+        "config": {"model": name, "layers": layers, "layers_of_model": sizes["num_hidden_layers"], "hidden_size": sizes["hidden_size"],
+                   "heads": sizes["num_attention_heads"], "kv_heads": sizes["num_key_value_heads"], "head_dim": sizes["head_dim"],
+                   "intermediate_size": sizes["intermediate_size"], "vocab_size": sizes["vocab_size"], "requests": n_req,
+                   "prompt_tokens_min": int(min(lens)), "prompt_tokens_max": int(max(lens)), "new_tokens": new_tokens,
+                   "step_token_budget": budget, "page_size": h.page_size, "cuda_graphs": h.graphs},
+        "clocks": clocks.summary(t0, t1), "gpu_launches": r["launches"]}))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -122,6 +159,11 @@ def main() -> int:
     ap.add_argument("--no-graphs", action="store_true")
     ap.add_argument("--prefill-only", action="store_true",
                     help="run only the 2,048-token prefill (for profiling) and print its time")
+    ap.add_argument("--workload", default="decode", choices=["decode", "mixed-14b", "batch16-32b"],
+                    help="decode: the contract's line (default).  mixed-14b: 32 requests with prompts of 128 to 3,072 tokens at "
+                         "Qwen3-14B sizes, prompts cut under a 2,048-token step budget beside the decoding requests, 128 new "
+                         "tokens each.  batch16-32b: 16 prompts of 1,024 tokens at Qwen3-32B sizes, 256 new tokens each.  Both "
+                         "run through the scheduler and print a line of their own")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": "the reference is a Rust crate on the candle library: no "
@@ -136,6 +178,8 @@ def main() -> int:
     import torch
     from carbon_engine_b200.bench_support import BenchHarness
     pk = peaks()
+    if args.workload != "decode":
+        return serve_workload(args, BenchHarness)
     cfg = dict(SIZES_8B, num_hidden_layers=args.layers)
     h = BenchHarness(cfg, max_batch=2 if args.prefill_only else max(64 if not args.no_points else args.batch, args.batch),
                      context=args.context,

@@ -17,7 +17,7 @@ from .sampling.params import SamplingParams
 
 class BenchHarness:
     def __init__(self, cfg: Dict, max_batch: int, context: int, new_tokens: int, graphs: bool = True,
-                 page_size: int = 64, seed: int = 0):
+                 page_size: int = 64, seed: int = 0, step_tokens: int = 4096):
         raw = dict(cfg, architectures=["Qwen3ForCausalLM"], model_type="qwen3")
         self.config = Qwen3Config.from_dict(raw)
         self.context, self.new_tokens, self.page_size, self.max_batch = context, new_tokens, page_size, max_batch
@@ -25,7 +25,7 @@ class BenchHarness:
         self.max_seq_len = max(4096, per_seq)
         self.engine = Engine(config=self.config, dtype="bfloat16", dummy_weight=True, seed=seed,
                              kv_tokens=max_batch * per_seq + 4096, page_size=page_size, max_seq_len=max(4096, per_seq),
-                             max_running_requests=max_batch, max_prefill_tokens=4096, cuda_graphs=graphs)
+                             max_running_requests=max_batch, max_prefill_tokens=step_tokens, cuda_graphs=graphs)
         self.graphs = bool(graphs and self.engine.runner.graphs_enabled)
         self.rng = np.random.default_rng(seed)
         self._next = 1 << 40
@@ -102,6 +102,28 @@ class BenchHarness:
             eng.step()
         return {"ms_per_step": dt / steps * 1e3, "tokens_per_s": batch * steps / dt, "h2d_bytes": h2d // steps,
                 "d2h_bytes": d2h // steps}
+
+    def serve(self, prompt_lens: List[int], new_tokens: int) -> Dict:
+        """A whole workload through Engine.add_request / Engine.step: all requests are queued at once, the
+        scheduler admits them, cuts their prompts into portions under the step's token budget beside the
+        decoding requests, and frees them as they finish.  Timed on the host clock between two
+        synchronisations."""
+        eng = self.engine
+        sp = SamplingParams(max_tokens=new_tokens, ignore_eos=True)
+        for n in prompt_lens:
+            eng.add_request(self._tokens(n), sp)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        steps, l0 = 0, ops.launch_count()
+        while eng.has_unfinished():
+            eng.step()
+            steps += 1
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        eng.runner.check_status()
+        prompt, gen = int(sum(prompt_lens)), len(prompt_lens) * new_tokens
+        return {"seconds": dt, "steps": steps, "prompt_tokens": prompt, "generated_tokens": gen,
+                "tokens_per_s": (prompt + gen) / dt, "generated_per_s": gen / dt, "launches": ops.launch_count() - l0}
 
     def prefill(self, tokens: int, reps: int, warmup: int) -> Dict:
         runner = self.engine.runner

@@ -187,9 +187,8 @@ class Engine:
                     if self.host_lookahead and all(e.sample and e.count == 1 for e in plan):
                         # the step is on its way: lay out the next one on the host while it runs
                         self.runner.prepare_decode_ahead(sampled_ids)
-                    host = dev.cpu()
-                    self.d2h_bytes_last = host.numel() * 4
-                    tokens = host.tolist()
+                    tokens = self.runner.read_back(dev)          # (waits for the step; the status word comes along)
+                    self.d2h_bytes_last = (len(tokens) + 1) * 4
                     for j, i in enumerate(want_lp):
                         lives[i].logprobs.append(top_logprobs(base[j], tokens[i], lives[i].params.logprobs))
                 self.runner.check_status()

@@ -52,6 +52,8 @@ class ModelRunner:
         self._ahead = None                   # a next step laid out on the host in advance (prepare_decode_ahead)
         self._graph_pool = None
         self.h2d_bytes_last = 0
+        self._back = None                    # pinned int32 buffer of read_back
+        self._status_read = None             # the status word read_back brought along, until check_status takes it
         self.kernel_launches = 0
 
     # -- requests -------------------------------------------------------------------------------
@@ -268,9 +270,25 @@ class ModelRunner:
         ops.add_launches(launches)
         return logits
 
+    def read_back(self, values: torch.Tensor) -> List[int]:
+        """A step's small int32 result (the sampled tokens) and the device status word in ONE wait: both are
+        copied to pinned memory behind the step on its stream, then the stream is waited for once.  The
+        status is kept for the next :meth:`check_status`, which then does not wait again."""
+        n = values.numel()
+        if self._back is None or self._back.numel() < n + 1:
+            self._back = torch.empty(max(n + 1, 257), dtype=torch.int32, pin_memory=True)
+        self._back[:n].copy_(values.reshape(-1), non_blocking=True)
+        self._back[n:n + 1].copy_(self.bufs.status.reshape(-1)[:1], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        self._status_read = int(self._back[n])
+        return self._back[:n].tolist()
+
     def check_status(self) -> None:
-        """Raise if a kernel of an earlier step flagged a bad index (this synchronises)."""
-        code = int(self.bufs.status.item())
+        """Raise if a kernel of an earlier step flagged a bad index (this waits for the device, unless
+        :meth:`read_back` has just brought the status word along)."""
+        code, self._status_read = self._status_read, None
+        if code is None:
+            code = int(self.bufs.status.item())
         if code != 0:
             self.bufs.status.zero_()
             raise StepError(f"device status {code}: {_STATUS.get(code, 'unknown')}")

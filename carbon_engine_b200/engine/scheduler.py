@@ -50,6 +50,7 @@ class Scheduler:
         self.max_step_tokens = max(max_step_tokens, self.max_running)
         self._entries = np.zeros(5 * (self.max_running + 1), dtype=np.int64)
         self._tokens = np.zeros(self.max_step_tokens + 1, dtype=np.int32)
+        self._fin = None                     # buffers of pop_finished, made at its first call
 
     def __del__(self):
         h, self._h = getattr(self, "_h", None), None
@@ -73,10 +74,12 @@ class Scheduler:
                                  len(self._tokens), ctypes.byref(n_tok))
         if n < 0:
             raise RuntimeError("the scheduler's plan does not fit its buffers")
+        ent = self._entries[:5 * n].tolist()             # (one conversion each: this runs between two steps)
+        toks = self._tokens[:n_tok.value].tolist()
         out, off = [], 0
         for i in range(n):
-            rid, slot, start, count, sample = (int(v) for v in self._entries[5 * i:5 * i + 5])
-            out.append(PlanEntry(rid, slot, start, count, bool(sample), self._tokens[off:off + count].tolist()))
+            rid, slot, start, count, sample = ent[5 * i:5 * i + 5]
+            out.append(PlanEntry(rid, slot, start, count, bool(sample), toks[off:off + count]))
             off += count
         return out
 
@@ -92,10 +95,12 @@ class Scheduler:
         return self._lib.sched_abort(self._h, request_id) == 0
 
     def pop_finished(self) -> List[Tuple[int, str]]:
-        ids = np.zeros(4096, dtype=np.int64)
-        reasons = np.zeros(4096, dtype=np.int32)
-        n = self._lib.sched_pop_finished(self._h, ids.ctypes.data_as(ctypes.POINTER(ctypes.c_int64)),
-                                         reasons.ctypes.data_as(ctypes.POINTER(ctypes.c_int)), len(ids))
+        if self._fin is None:
+            ids, reasons = np.zeros(4096, dtype=np.int64), np.zeros(4096, dtype=np.int32)
+            self._fin = (ids, reasons, ids.ctypes.data_as(ctypes.POINTER(ctypes.c_int64)),
+                         reasons.ctypes.data_as(ctypes.POINTER(ctypes.c_int)))
+        ids, reasons, p_ids, p_reasons = self._fin
+        n = self._lib.sched_pop_finished(self._h, p_ids, p_reasons, len(ids))
         return [(int(ids[i]), FINISH_REASONS.get(int(reasons[i]), "error")) for i in range(n)]
 
     def tokens_of(self, request_id: int) -> List[int]:

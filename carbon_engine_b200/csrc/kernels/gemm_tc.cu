@@ -130,6 +130,7 @@ struct TcArgs {
     int* status;
     int M, N, K, ldo, mode, splits, kblocks_per_split, kblocks, trace;
     int cluster;             // 1: the splits of a tile form a cluster and add their partial sums through shared memory
+    int coop;                // 1: every split of a tile adds the partial sums for a share of the tile's tokens (more than 8 tokens)
 };
 
 __device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + __expf(-g)) * u; }
@@ -144,8 +145,8 @@ __device__ __forceinline__ void epilogue_store(const TcArgs& a, int m, int n, fl
     else ((__nv_bfloat16*)a.out)[o] = __float2bfloat16_rn(silu_mul(v, up));
 }
 
-template <int BN, int NACC>
-__global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,
+template <int BN, int NACC, bool COOP>
+__global__ void __launch_bounds__(THREADS, 2) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,
                                                          const __grid_constant__ CUtensorMap map_x, TcArgs a, int stages) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     __shared__ __align__(8) uint64_t full_bar[8], empty_bar[8], acc_bar;
@@ -389,9 +390,37 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
             asm volatile("bar.sync 1, 128;" ::: "memory");
             if (tracing && threadIdx.x == 64) s_rec[5] = gtime();
             if (a.trace && threadIdx.x == 64) atomicMax(&g_trace_all[(a.trace & 255) * 4 + 1], gtime());
-            if (threadIdx.x == 64) s_ticket = atomicAdd(&a.counters[tile], 1);
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            if (s_ticket == a.splits - 1) {
+            // Who adds the partial sums.  Few tokens: the block of a tile that arrives last, all of them in one trip
+            // to L2.  More tokens (coop): a single block would make a trip per 8 tokens, one after the other (11 us
+            // for 64 tokens), so EVERY split of the tile waits until all partial sums are there (all splits of a
+            // launch are resident at once: the grid is sized for that) and then adds them for its own share of the
+            // tokens.  Either way each result is one sum in split order.
+            int m_lo = 0, m_hi = m_valid;
+            bool adds = false;
+            if (COOP) {
+                if (threadIdx.x == 64) {
+                    atomicAdd(&a.counters[tile], 1);
+                    bool there = false;
+                    for (uint32_t i = 0; i < SPIN_LIMIT && !there; ++i) {
+                        int v;
+                        asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(a.counters + tile) : "memory");
+                        there = v >= a.splits;
+                        if (!there && i > 32) __nanosleep(i > 4096 ? 1024 : 64);
+                    }
+                    if (!there) { atomicExch(a.status, 5); atomicExch(&s_abort, 1); }
+                    s_ticket = there ? 1 : 0;
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                int per = ((m_valid + a.splits - 1) / a.splits + 7) & ~7;      // whole batches of 8 tokens
+                m_lo = min(m_valid, split * per);
+                m_hi = min(m_valid, m_lo + per);
+                adds = s_ticket != 0;
+            } else {
+                if (threadIdx.x == 64) s_ticket = atomicAdd(&a.counters[tile], 1);
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                adds = s_ticket == a.splits - 1;
+            }
+            if (adds) {
                 __threadfence();
                 if (n < a.N && s_abort == 0) {
                     // A batch of tokens at a time, with the loads of up to eight splits (and of the residual
@@ -400,12 +429,12 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
                     constexpr int TB = 8;
                     size_t split_stride = (size_t)n_tiles * BN * BM;
                     const float* p0 = a.scratch + (size_t)tile * BN * BM + row;
-                    for (int mb = 0; mb < m_valid; mb += TB) {
+                    for (int mb = m_lo; mb < m_hi; mb += TB) {
                         float g[TB], xv[TB];
 #pragma unroll
                         for (int j = 0; j < TB; ++j) {
                             g[j] = 0.f;
-                            xv[j] = (a.mode == TC_ACCUM_F32 && mb + j < m_valid)
+                            xv[j] = (a.mode == TC_ACCUM_F32 && mb + j < m_hi)
                                         ? __ldcg((const float*)a.out + (size_t)(m0 + mb + j) * a.ldo + n) : 0.f;
                         }
                         for (int s0 = 0; s0 < a.splits; s0 += 8) {
@@ -415,7 +444,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
                                 const float* p = p0 + (size_t)(s0 + s) * split_stride;
 #pragma unroll
                                 for (int j = 0; j < TB; ++j) {
-                                    bool in = s0 + s < a.splits && mb + j < m_valid;
+                                    bool in = s0 + s < a.splits && mb + j < m_hi;
                                     tg[s][j] = in ? __ldcg(p + (size_t)(mb + j) * BM) : 0.f;
                                 }
                             }
@@ -427,12 +456,21 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
                         }
 #pragma unroll
                         for (int j = 0; j < TB; ++j) {
-                            if (mb + j >= m_valid) continue;
+                            if (mb + j >= m_hi) continue;
                             if (a.mode == TC_ACCUM_F32) ((float*)a.out)[(size_t)(m0 + mb + j) * a.ldo + n] = xv[j] + g[j];
                             else epilogue_store(a, m0 + mb + j, n, g[j], 0.f);
                         }
                     }
                 }
+            }
+            if (COOP) {
+                // the split that finishes last puts both counters back for the next launch (everyone has passed its wait by then)
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (threadIdx.x == 64 && atomicAdd(&a.counters[n_tiles + tile], 1) == a.splits - 1) {
+                    a.counters[tile] = 0;
+                    a.counters[n_tiles + tile] = 0;
+                }
+            } else if (adds) {
                 if (threadIdx.x == 64) a.counters[tile] = 0;      // ready for the next launch
             }
         }
@@ -913,7 +951,7 @@ int get_map(const void* ptr, long long rows, long long cols, long long ld, int b
     return ce_tensor_map_bf16(ptr, rows, cols, ld, box_rows, out, "ce_gemm_tc");
 }
 
-template <int BN, int NACC>
+template <int BN, int NACC, bool COOP>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, const TcArgs& a, dim3 grid, cudaStream_t stream) {
     constexpr size_t stage = BM * BK * 2 + BN * BK * 2;
     // small tiles: at most half an SM's shared memory, so that the blocks of the next kernel (launched
@@ -928,7 +966,7 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, const TcArgs& a, dim3 g
     size_t smem = stages * stage + 1024;
     static bool attr_set = false;
     if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, NACC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, NACC, COOP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return ce_fail(CE_ERR_CUDA, "ce_gemm_tc: %s", cudaGetErrorString(e));
         attr_set = true;
     }
@@ -947,11 +985,11 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, const TcArgs& a, dim3 g
         attr[1].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr;
         cfg.numAttrs = ce_pdl_enabled() ? 2 : 1;
-        cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, NACC>, mw, mx, a, stages);
+        cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, NACC, COOP>, mw, mx, a, stages);
         if (e != cudaSuccess) return ce_fail(CE_ERR_CUDA, "ce_gemm_tc (cluster of %d): %s", (int)grid.z, cudaGetErrorString(e));
         return ce_check_launch("ce_gemm_tc");
     }
-    ce_launch(gemm_tc_kernel<BN, NACC>, grid, THREADS, smem, stream, mw, mx, a, stages);
+    ce_launch(gemm_tc_kernel<BN, NACC, COOP>, grid, THREADS, smem, stream, mw, mx, a, stages);
     return ce_check_launch("ce_gemm_tc");
 }
 
@@ -1145,10 +1183,16 @@ extern "C" int ce_gemm_tc(const void* A, const void* W, void* C, int M, int N, i
     size_t budget_b = (bn <= 16 || nacc == 2) ? 100 * 1024 : 200 * 1024;
     size_t n_st = budget_b / stage_b > 8 ? 8 : (budget_b / stage_b < 2 ? 2 : budget_b / stage_b);
     int cluster = cluster_split_k() && splits > 1 && splits <= 8 && (size_t)bn * BM * 4 <= n_st * stage_b;
-    TcArgs a{C, scratch, counters, status, M, N, K, ldc, mode, splits, (kblocks + splits - 1) / splits, kblocks, trace, cluster};
+    // every split adds a share of the tokens only if all blocks of the launch are resident at once (they wait for one another)
+    long long resident = (long long)ce_sm_count() * ((bn <= 16 || nacc == 2) ? 2 : 1);
+    static int coop_off = getenv("CE_GEMM_NO_COOP") ? 1 : 0;
+    int coop = !coop_off && splits > 1 && !cluster && M > 8 && (long long)grid.x * grid.y * grid.z <= resident &&
+               n_counters >= 2 * (int)(grid.x * grid.y);
+    TcArgs a{C, scratch, counters, status, M, N, K, ldc, mode, splits, (kblocks + splits - 1) / splits, kblocks, trace, cluster, coop};
 #define TC_CASE(BN_)                                                                  \
     case BN_:                                                                         \
-        return nacc == 2 ? launch<BN_, 2>(mw, mx, a, grid, stream) : launch<BN_, 1>(mw, mx, a, grid, stream);
+        return nacc == 2 ? launch<BN_, 2, false>(mw, mx, a, grid, stream)                  \
+                         : a.coop ? launch<BN_, 1, true>(mw, mx, a, grid, stream) : launch<BN_, 1, false>(mw, mx, a, grid, stream);
     switch (bn) {
         TC_CASE(16)
         TC_CASE(32)

@@ -14,7 +14,9 @@
 // Warp 0 issues the TMA loads, warp 1 owns tensor memory and issues the MMAs, warps 2-5 read the
 // accumulators back (tcgen05.ld) and run the epilogue.  With split-K every CTA writes its partial
 // sums to scratch memory; the CTA that arrives last for a tile adds the partials in split order
-// (a fixed order, so the result does not depend on which CTA came last) and runs the epilogue.
+// (a fixed order, so the result does not depend on which CTA came last) and runs the epilogue.  With
+// more than 8 tokens every CTA of the tile does that for its share of the tokens, once all partials
+// are there (the CTAs of such a launch are resident together; the wait is bounded like the others).
 // No load uses cluster multicast.  Every wait on an mbarrier is bounded: on a timeout the kernel sets
 // status 5, waits (bounded) for its own copies in flight, frees its tensor memory and returns.
 //

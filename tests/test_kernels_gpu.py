@@ -524,6 +524,23 @@ def test_tcgen05_product_all_epilogues(ops, M, N, K):
     assert rel_err(tc_product(a, w2, ops.GEMM_SWIGLU, N), g * torch.sigmoid(g) * u) < 1e-2
 
 
+@pytest.mark.parametrize("M,N,K", [(9, 256, 4096), (48, 520, 4096), (128, 256, 8192), (200, 384, 12288)])
+def test_tcgen05_split_k_with_more_than_eight_tokens(ops, M, N, K):
+    """Above 8 tokens every split of a tile adds the partial sums for its share of the tokens (the blocks
+    wait for one another's partials): all epilogues against float64, at sizes that do split K."""
+    from carbon_engine_b200.csrc.kernel_lib import kernels
+    assert kernels().ce_gemm_tc_splits(M, N, K) > 1
+    torch.manual_seed(M + N + K)
+    a = torch.randn(M, K, device=dev()).to(torch.bfloat16)
+    w = (torch.randn(N, K, device=dev()) / math.sqrt(K)).to(torch.bfloat16)
+    ref = a.double().cpu() @ w.double().cpu().T
+    for _ in range(3):        # the counters go back to zero after every launch
+        assert rel_err(tc_product(a, w, ops.GEMM_STORE_F32, N), ref) < 2e-5
+    assert rel_err(tc_product(a, w, ops.GEMM_STORE, N), ref) < 1e-2
+    x0 = torch.randn(M, N, device=dev())
+    assert rel_err(tc_product(a, w, ops.GEMM_ACCUM_F32, N, x0), x0.double().cpu() + ref) < 2e-5
+
+
 def test_tcgen05_product_is_repeatable_and_rows_stand_alone(ops):
     """Split-K adds the partial sums in a fixed order: the same bits every time, and a token's row does
     not depend on how many other tokens share the step (while they fit one tile of tokens)."""

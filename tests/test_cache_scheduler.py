@@ -294,3 +294,83 @@ def test_stats_count_tokens():
     run_all(s, lambda e: 5)
     st = s.stats()
     assert st["prefill_tokens"] == 11 and st["decode_tokens"] == 2 and st["steps"] == 4 and st["finished"] == 1
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_workloads_keep_the_schedulers_promises(seed):
+    """Random arrivals, prompt lengths, budgets, pool sizes, stop tokens, aborts and failed steps: every step
+    keeps the token budget and carries every decoding request once, positions follow on without a gap,
+    the pool is never overdrawn, and at the end every request has finished with what it was promised."""
+    rng = random.Random(seed)
+    page_size = rng.choice([2, 4, 8])
+    max_running = rng.randint(1, 5)
+    budget = rng.randint(max_running, 12)
+    max_seq_len = rng.choice([32, 64])
+    pages = rng.randint(max_seq_len // page_size, 3 * max_seq_len // page_size)
+    cm, s = make(pages=pages, page_size=page_size, max_running=max_running, budget=budget, max_seq_len=max_seq_len, eos=(99,))
+    todo = list(range(1, 25))
+    want, stops, aborted, failed = {}, {}, set(), set()
+    pos = {}                                   # request -> tokens the scheduler has handed out so far
+    decoding = set()
+    finished = {}
+    for step in range(4000):
+        while todo and rng.random() < 0.4:     # arrivals
+            rid = todo.pop(0)
+            n_prompt = rng.randint(1, max_seq_len - 2)
+            max_tokens = rng.randint(1, 12)
+            stop = [98] if rng.random() < 0.3 else []
+            s.submit(rid, [rng.randrange(90) for _ in range(n_prompt)], max_tokens=max_tokens,
+                     ignore_eos=rng.random() < 0.2, stop_token_ids=stop)
+            want[rid] = (n_prompt, min(max_tokens, max_seq_len - n_prompt))
+            stops[rid] = stop
+            pos[rid] = 0
+        if s.idle():
+            if not todo:
+                break
+            continue
+        if rng.random() < 0.03 and pos:        # an abort now and then
+            rid = rng.choice(list(pos))
+            if rid not in finished and s.abort(rid):
+                aborted.add(rid)
+                decoding.discard(rid)
+        plan = s.plan()
+        assert sum(e.count for e in plan) <= budget
+        ids = [e.request_id for e in plan]
+        assert len(ids) == len(set(ids)) and len(ids) <= max_running
+        assert decoding <= set(ids)            # nobody who decodes is left out of a step
+        for e in plan:
+            assert e.start == pos[e.request_id] and e.count == len(e.tokens) and e.count >= 1
+            if e.request_id in decoding:
+                assert e.count == 1 and e.sample
+        assert cm.free_pages() >= 0
+        cm.check()
+        if plan and rng.random() < 0.03:       # the step fails: its requests end with an error, the pool gets their pages back
+            s.fail_step()
+            for e in plan:
+                failed.add(e.request_id)
+                decoding.discard(e.request_id)
+        elif plan:
+            for e in plan:
+                pos[e.request_id] += e.count
+                if e.sample:
+                    decoding.add(e.request_id)
+            s.commit([rng.choice([5, 6, 7, 98, 99]) for e in plan if e.sample])
+        for rid, reason in s.pop_finished():
+            finished[rid] = reason
+            decoding.discard(rid)
+            toks = s.tokens_of(rid)
+            n_prompt, max_new = want[rid]
+            gen = toks[n_prompt:]
+            if reason == "length":
+                assert len(gen) == max_new
+            elif reason == "stop":
+                assert 1 <= len(gen) <= max_new and (gen[-1] == 99 or gen[-1] in stops[rid])
+            elif reason == "abort":
+                assert rid in aborted
+            else:
+                assert reason == "error" and (rid in failed or n_prompt + max_new - 1 > pages * page_size)
+            s.forget(rid)
+    assert not todo and s.idle()
+    assert set(finished) == set(want)
+    cm.check()
+    assert cm.free_pages() == pages and cm.free_slots() == max_running

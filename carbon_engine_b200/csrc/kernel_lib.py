@@ -17,6 +17,9 @@ _i, _f, _ll, _p = ctypes.c_int, ctypes.c_float, ctypes.c_longlong, ctypes.c_void
 _SIGNATURES = {
     "ce_last_error": (ctypes.c_char_p, []),
     "ce_build_arch": (_i, []),
+    "ce_kernel_counts": (_i, [ctypes.c_char_p, _i]),
+    "ce_kernel_counts_reset": (None, []),
+    "ce_last_kernel": (ctypes.c_char_p, []),
     # table, dtype, tokens, x, T, H, V, status, stream
     "ce_embed": (_i, [_p, _i, _p, _p, _i, _i, _i, _p, _p]),
     # x, w, out, out_dtype, rows, R, H, eps, stream

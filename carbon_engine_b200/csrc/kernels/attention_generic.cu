@@ -123,9 +123,9 @@ extern "C" int ce_attention_generic(const void* q, const void* k_pool, const voi
     size_t smem = (d + ATT_THREADS + 32) * sizeof(float) + ATT_THREADS * sizeof(long long);
     dim3 grid(T, nh);
     if (dtype == CE_F32)
-        ce_launch(attention_generic_kernel<float>, grid, ATT_THREADS, smem, stream, a);
+        { ce_note("attention_generic_kernel"); ce_launch(attention_generic_kernel<float>, grid, ATT_THREADS, smem, stream, a); }
     else if (dtype == CE_BF16)
-        ce_launch(attention_generic_kernel<__nv_bfloat16>, grid, ATT_THREADS, smem, stream, a);
+        { ce_note("attention_generic_kernel"); ce_launch(attention_generic_kernel<__nv_bfloat16>, grid, ATT_THREADS, smem, stream, a); }
     else
         return ce_fail(CE_ERR_ARG, "ce_attention_generic: unknown dtype %d", dtype);
     return ce_check_launch("ce_attention_generic");

@@ -997,6 +997,7 @@ extern "C" int ce_attention_decode_bf16(const void* q, const void* k_pool, const
         cfg.attrs = attr;
         cfg.numAttrs = n_attr;
         cudaError_t le = cudaSuccess;
+        ce_note(a.cluster_merge ? "attention_decode_tma_kernel (merge in the cluster)" : "attention_decode_tma_kernel");
 #define AMT_CASE(DM)                                                                                                   \
         if (deep3) {                                                                                                   \
             if ((rc = set_smem(attention_decode_tma_kernel<DM, 3>, tsmem, "ce_attention_decode_bf16"))) return rc;     \
@@ -1011,7 +1012,7 @@ extern "C" int ce_attention_decode_bf16(const void* q, const void* k_pool, const
         if ((rc = ce_check_launch("ce_attention_decode_bf16"))) return rc;
         g_decode_launches = a.cluster_merge ? 1 : 2;
         if (a.cluster_merge) return CE_OK;
-        ce_launch(attention_merge_kernel, dim3(n_seqs, nh), d >= 128 ? 128 : (d + 31) / 32 * 32, max_splits * sizeof(float), stream, a);
+        { ce_note("attention_merge_kernel"); ce_launch(attention_merge_kernel, dim3(n_seqs, nh), d >= 128 ? 128 : (d + 31) / 32 * 32, max_splits * sizeof(float), stream, a); }
         return ce_check_launch("ce_attention_decode_bf16 (merge)");
     }
     size_t smem = stage_bytes(d);
@@ -1026,17 +1027,17 @@ extern "C" int ce_attention_decode_bf16(const void* q, const void* k_pool, const
 #define AM_DECODE_CASE(DM)                                                                                        \
     if (deep) {                                                                                                   \
         if ((rc = set_smem(attention_decode_kernel<DM, 3>, smem, "ce_attention_decode_bf16"))) return rc;         \
-        ce_launch(attention_decode_kernel<DM, 3>, grid, AM_THREADS, smem, stream, a);                             \
+        { ce_note("attention_decode_kernel"); ce_launch(attention_decode_kernel<DM, 3>, grid, AM_THREADS, smem, stream, a); }                             \
     } else {                                                                                                      \
         if ((rc = set_smem(attention_decode_kernel<DM, 2>, smem, "ce_attention_decode_bf16"))) return rc;         \
-        ce_launch(attention_decode_kernel<DM, 2>, grid, AM_THREADS, smem, stream, a);                             \
+        { ce_note("attention_decode_kernel"); ce_launch(attention_decode_kernel<DM, 2>, grid, AM_THREADS, smem, stream, a); }                             \
     }
     if (d <= 64) { AM_DECODE_CASE(64) } else if (d <= 128) { AM_DECODE_CASE(128) } else { AM_DECODE_CASE(256) }
 #undef AM_DECODE_CASE
     if ((rc = ce_check_launch("ce_attention_decode_bf16"))) return rc;
     g_decode_launches = a.fused_merge ? 1 : 2;
     if (a.fused_merge) return CE_OK;
-    ce_launch(attention_merge_kernel, dim3(n_seqs, nh), d >= 128 ? 128 : (d + 31) / 32 * 32, max_splits * sizeof(float), stream, a);
+    { ce_note("attention_merge_kernel"); ce_launch(attention_merge_kernel, dim3(n_seqs, nh), d >= 128 ? 128 : (d + 31) / 32 * 32, max_splits * sizeof(float), stream, a); }
     return ce_check_launch("ce_attention_decode_bf16 (merge)");
 }
 
@@ -1063,13 +1064,13 @@ extern "C" int ce_attention_prefill_bf16(const void* q, const void* k_pool, cons
     size_t smem = stage_bytes(d, AM_PF_STAGES);
     if (d <= 64) {
         if ((rc = set_smem(attention_prefill_kernel<64>, smem, "ce_attention_prefill_bf16"))) return rc;
-        ce_launch(attention_prefill_kernel<64>, grid, AM_THREADS, smem, stream, a);
+        { ce_note("attention_prefill_kernel"); ce_launch(attention_prefill_kernel<64>, grid, AM_THREADS, smem, stream, a); }
     } else if (d <= 128) {
         if ((rc = set_smem(attention_prefill_kernel<128>, smem, "ce_attention_prefill_bf16"))) return rc;
-        ce_launch(attention_prefill_kernel<128>, grid, AM_THREADS, smem, stream, a);
+        { ce_note("attention_prefill_kernel"); ce_launch(attention_prefill_kernel<128>, grid, AM_THREADS, smem, stream, a); }
     } else {
         if ((rc = set_smem(attention_prefill_kernel<256>, smem, "ce_attention_prefill_bf16"))) return rc;
-        ce_launch(attention_prefill_kernel<256>, grid, AM_THREADS, smem, stream, a);
+        { ce_note("attention_prefill_kernel"); ce_launch(attention_prefill_kernel<256>, grid, AM_THREADS, smem, stream, a); }
     }
     return ce_check_launch("ce_attention_prefill_bf16");
 }

@@ -457,7 +457,7 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
         if (e != cudaSuccess) return ce_fail(CE_ERR_CUDA, "ce_attention_prefill_tc: %s", cudaGetErrorString(e));
         attr_set = true;
     }
-    ce_launch(attention_prefill_tc_kernel<D>, grid, THREADS, smem, stream, mq, mk, mv, a);
+    { ce_note("attention_prefill_tc_kernel"); ce_launch(attention_prefill_tc_kernel<D>, grid, THREADS, smem, stream, mq, mk, mv, a); }
     return ce_check_launch("ce_attention_prefill_tc");
 }
 

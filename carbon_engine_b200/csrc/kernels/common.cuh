@@ -45,6 +45,9 @@ inline cudaError_t ce_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, si
     return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
 }
 int ce_fail(int code, const char* fmt, ...);
+// Counts a launch under the kernel's name (ce_kernel_counts() lists them), so that a test or a
+// measurement can see WHICH kernel took a shape.  Called by the launchers once per launch.
+void ce_note(const char* kernel_name);
 int ce_check_launch(const char* what);
 int ce_sm_count();
 

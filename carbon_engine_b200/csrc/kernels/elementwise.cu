@@ -31,9 +31,9 @@ extern "C" int ce_embed(const void* table, int dtype, const int* tokens, float* 
     if (T == 0) return CE_OK;
     if (!table || !tokens || !x || !status) return ce_fail(CE_ERR_ARG, "ce_embed: null pointer");
     if (dtype == CE_F32)
-        ce_launch(embed_kernel<float>, T, H >= 1024 ? 1024 : 256, 0, stream, (const float*)table, tokens, x, H, V, status);
+        { ce_note("embed_kernel"); ce_launch(embed_kernel<float>, T, H >= 1024 ? 1024 : 256, 0, stream, (const float*)table, tokens, x, H, V, status); }
     else if (dtype == CE_BF16)
-        ce_launch(embed_kernel<__nv_bfloat16>, T, H >= 1024 ? 1024 : 256, 0, stream, (const __nv_bfloat16*)table, tokens, x, H, V, status);
+        { ce_note("embed_kernel"); ce_launch(embed_kernel<__nv_bfloat16>, T, H >= 1024 ? 1024 : 256, 0, stream, (const __nv_bfloat16*)table, tokens, x, H, V, status); }
     else
         return ce_fail(CE_ERR_ARG, "ce_embed: unknown dtype %d", dtype);
     return ce_check_launch("ce_embed");
@@ -129,11 +129,11 @@ extern "C" int ce_rmsnorm(const float* x, const float* w, void* out, int out_dty
     if (H <= 0) return ce_fail(CE_ERR_SIZE, "ce_rmsnorm: width %d", H);
     int vt = rmsnorm_vec_threads(H, x, w, out);
     if (out_dtype == CE_F32) {
-        if (vt) ce_launch(rmsnorm_vec_kernel<float>, R, vt, 0, stream, x, w, (float*)out, rows, H, eps);
-        else ce_launch(rmsnorm_kernel<float>, R, 256, 0, stream, x, w, (float*)out, rows, H, eps);
+        if (vt) { ce_note("rmsnorm_vec_kernel"); ce_launch(rmsnorm_vec_kernel<float>, R, vt, 0, stream, x, w, (float*)out, rows, H, eps); }
+        else { ce_note("rmsnorm_kernel"); ce_launch(rmsnorm_kernel<float>, R, 256, 0, stream, x, w, (float*)out, rows, H, eps); }
     } else if (out_dtype == CE_BF16) {
-        if (vt) ce_launch(rmsnorm_vec_kernel<__nv_bfloat16>, R, vt, 0, stream, x, w, (__nv_bfloat16*)out, rows, H, eps);
-        else ce_launch(rmsnorm_kernel<__nv_bfloat16>, R, 256, 0, stream, x, w, (__nv_bfloat16*)out, rows, H, eps);
+        if (vt) { ce_note("rmsnorm_vec_kernel"); ce_launch(rmsnorm_vec_kernel<__nv_bfloat16>, R, vt, 0, stream, x, w, (__nv_bfloat16*)out, rows, H, eps); }
+        else { ce_note("rmsnorm_kernel"); ce_launch(rmsnorm_kernel<__nv_bfloat16>, R, 256, 0, stream, x, w, (__nv_bfloat16*)out, rows, H, eps); }
     } else
         return ce_fail(CE_ERR_ARG, "ce_rmsnorm: unknown dtype %d", out_dtype);
     return ce_check_launch("ce_rmsnorm");
@@ -402,10 +402,10 @@ static bool launch_rope_warp(const QkRopeArgs& a, cudaStream_t stream) {
     if ((warps + 3) / 4 > 2147483647LL) return false;
     unsigned blocks = (unsigned)((warps + 3) / 4);
     switch (a.d / 64) {
-        case 1: ce_launch(qk_rope_kvwrite_warp_kernel<T, 1>, blocks, 128, 0, stream, a, hpw); return true;
-        case 2: ce_launch(qk_rope_kvwrite_warp_kernel<T, 2>, blocks, 128, 0, stream, a, hpw); return true;
-        case 3: ce_launch(qk_rope_kvwrite_warp_kernel<T, 3>, blocks, 128, 0, stream, a, hpw); return true;
-        case 4: ce_launch(qk_rope_kvwrite_warp_kernel<T, 4>, blocks, 128, 0, stream, a, hpw); return true;
+        case 1: { ce_note("qk_rope_kvwrite_warp_kernel"); ce_launch(qk_rope_kvwrite_warp_kernel<T, 1>, blocks, 128, 0, stream, a, hpw); } return true;
+        case 2: { ce_note("qk_rope_kvwrite_warp_kernel"); ce_launch(qk_rope_kvwrite_warp_kernel<T, 2>, blocks, 128, 0, stream, a, hpw); } return true;
+        case 3: { ce_note("qk_rope_kvwrite_warp_kernel"); ce_launch(qk_rope_kvwrite_warp_kernel<T, 3>, blocks, 128, 0, stream, a, hpw); } return true;
+        case 4: { ce_note("qk_rope_kvwrite_warp_kernel"); ce_launch(qk_rope_kvwrite_warp_kernel<T, 4>, blocks, 128, 0, stream, a, hpw); } return true;
     }
     return false;
 }
@@ -428,10 +428,10 @@ extern "C" int ce_qk_rope_kvwrite(void* qkv, void* k_pool, void* v_pool, int dty
     dim3 grid(T, nh + 2 * nkv);
     size_t smem = (d + 32) * sizeof(float);
     if (dtype == CE_F32) {
-        if (!launch_rope_warp<float>(a, stream)) ce_launch(qk_rope_kvwrite_kernel<float>, grid, threads, smem, stream, a);
+        if (!launch_rope_warp<float>(a, stream)) { ce_note("qk_rope_kvwrite_kernel"); ce_launch(qk_rope_kvwrite_kernel<float>, grid, threads, smem, stream, a); }
     } else if (dtype == CE_BF16) {
         if (!launch_rope_warp<__nv_bfloat16>(a, stream))
-            ce_launch(qk_rope_kvwrite_kernel<__nv_bfloat16>, grid, threads, smem, stream, a);
+            { ce_note("qk_rope_kvwrite_kernel"); ce_launch(qk_rope_kvwrite_kernel<__nv_bfloat16>, grid, threads, smem, stream, a); }
     } else
         return ce_fail(CE_ERR_ARG, "ce_qk_rope_kvwrite: unknown dtype %d", dtype);
     return ce_check_launch("ce_qk_rope_kvwrite");
@@ -453,9 +453,9 @@ extern "C" int ce_add_residual(float* x, const void* delta, int dtype, long long
     if (!x || !delta) return ce_fail(CE_ERR_ARG, "ce_add_residual: null pointer");
     int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
     if (dtype == CE_F32)
-        ce_launch(add_residual_kernel<float>, blocks, 256, 0, stream, x, (const float*)delta, (size_t)n);
+        { ce_note("add_residual_kernel"); ce_launch(add_residual_kernel<float>, blocks, 256, 0, stream, x, (const float*)delta, (size_t)n); }
     else if (dtype == CE_BF16)
-        ce_launch(add_residual_kernel<__nv_bfloat16>, blocks, 256, 0, stream, x, (const __nv_bfloat16*)delta, (size_t)n);
+        { ce_note("add_residual_kernel"); ce_launch(add_residual_kernel<__nv_bfloat16>, blocks, 256, 0, stream, x, (const __nv_bfloat16*)delta, (size_t)n); }
     else
         return ce_fail(CE_ERR_ARG, "ce_add_residual: unknown dtype %d", dtype);
     return ce_check_launch("ce_add_residual");
@@ -484,9 +484,9 @@ extern "C" int ce_swiglu(const void* gu, void* out, int dtype, int T, int I, cud
     if (!gu || !out) return ce_fail(CE_ERR_ARG, "ce_swiglu: null pointer");
     int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
     if (dtype == CE_F32)
-        ce_launch(swiglu_kernel<float>, blocks, 256, 0, stream, (const float*)gu, (float*)out, I, total);
+        { ce_note("swiglu_kernel"); ce_launch(swiglu_kernel<float>, blocks, 256, 0, stream, (const float*)gu, (float*)out, I, total); }
     else if (dtype == CE_BF16)
-        ce_launch(swiglu_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, I, total);
+        { ce_note("swiglu_kernel"); ce_launch(swiglu_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, I, total); }
     else
         return ce_fail(CE_ERR_ARG, "ce_swiglu: unknown dtype %d", dtype);
     return ce_check_launch("ce_swiglu");
@@ -509,6 +509,6 @@ __global__ void scatter_i32_kernel(int* __restrict__ dst, const int* __restrict_
 extern "C" int ce_scatter_i32(int* dst, const int* idx, const int* val, int n, long long dst_len, cudaStream_t stream) {
     if (n == 0) return CE_OK;
     if (!dst || !idx || !val) return ce_fail(CE_ERR_ARG, "ce_scatter_i32: null pointer");
-    ce_launch(scatter_i32_kernel, (n + 255) / 256, 256, 0, stream, dst, idx, val, n, dst_len);
+    { ce_note("scatter_i32_kernel"); ce_launch(scatter_i32_kernel, (n + 255) / 256, 256, 0, stream, dst, idx, val, n, dst_len); }
     return ce_check_launch("ce_scatter_i32");
 }

@@ -92,10 +92,10 @@ static int launch_plain(const void* A, const void* W, void* C, int M, int N, int
                         cudaStream_t stream) {
     dim3 grid((N + GP_BN - 1) / GP_BN, (M + GP_BM - 1) / GP_BM);
     switch (mode) {
-        case GP_STORE: ce_launch(gemm_plain_kernel<T, GP_STORE>, grid, 256, 0, stream, (const T*)A, (const T*)W, C, M, N, K, lda, ldc); break;
-        case GP_STORE_F32: ce_launch(gemm_plain_kernel<T, GP_STORE_F32>, grid, 256, 0, stream, (const T*)A, (const T*)W, C, M, N, K, lda, ldc); break;
-        case GP_ACCUM_F32: ce_launch(gemm_plain_kernel<T, GP_ACCUM_F32>, grid, 256, 0, stream, (const T*)A, (const T*)W, C, M, N, K, lda, ldc); break;
-        case GP_SWIGLU: ce_launch(gemm_plain_kernel<T, GP_SWIGLU>, grid, 256, 0, stream, (const T*)A, (const T*)W, C, M, N, K, lda, ldc); break;
+        case GP_STORE: { ce_note("gemm_plain_kernel"); ce_launch(gemm_plain_kernel<T, GP_STORE>, grid, 256, 0, stream, (const T*)A, (const T*)W, C, M, N, K, lda, ldc); } break;
+        case GP_STORE_F32: { ce_note("gemm_plain_kernel"); ce_launch(gemm_plain_kernel<T, GP_STORE_F32>, grid, 256, 0, stream, (const T*)A, (const T*)W, C, M, N, K, lda, ldc); } break;
+        case GP_ACCUM_F32: { ce_note("gemm_plain_kernel"); ce_launch(gemm_plain_kernel<T, GP_ACCUM_F32>, grid, 256, 0, stream, (const T*)A, (const T*)W, C, M, N, K, lda, ldc); } break;
+        case GP_SWIGLU: { ce_note("gemm_plain_kernel"); ce_launch(gemm_plain_kernel<T, GP_SWIGLU>, grid, 256, 0, stream, (const T*)A, (const T*)W, C, M, N, K, lda, ldc); } break;
         default: return ce_fail(CE_ERR_ARG, "ce_gemm_plain: unknown epilogue %d", mode);
     }
     return ce_check_launch("ce_gemm_plain");

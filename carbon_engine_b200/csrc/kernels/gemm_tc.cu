@@ -987,11 +987,12 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, const TcArgs& a, dim3 g
         attr[1].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr;
         cfg.numAttrs = ce_pdl_enabled() ? 2 : 1;
+        ce_note("gemm_tc_kernel (split-K in a cluster)");
         cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, NACC, COOP>, mw, mx, a, stages);
         if (e != cudaSuccess) return ce_fail(CE_ERR_CUDA, "ce_gemm_tc (cluster of %d): %s", (int)grid.z, cudaGetErrorString(e));
         return ce_check_launch("ce_gemm_tc");
     }
-    ce_launch(gemm_tc_kernel<BN, NACC, COOP>, grid, THREADS, smem, stream, mw, mx, a, stages);
+    { ce_note(COOP ? "gemm_tc_kernel (split-K, splits add together)" : a.splits > 1 ? "gemm_tc_kernel (split-K)" : "gemm_tc_kernel"); ce_launch(gemm_tc_kernel<BN, NACC, COOP>, grid, THREADS, smem, stream, mw, mx, a, stages); }
     return ce_check_launch("ce_gemm_tc");
 }
 
@@ -1009,7 +1010,7 @@ int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, const TcArgs
     }
     long long total = (long long)tiles_n * tiles_m;
     int grid = (int)(total < ce_sm_count() ? total : ce_sm_count());
-    ce_launch(gemm_tc_persistent_kernel<BN, NACC>, grid, THREADS, smem, stream, mw, mx, a, stages, tiles_n, tiles_m);
+    { ce_note("gemm_tc_persistent_kernel"); ce_launch(gemm_tc_persistent_kernel<BN, NACC>, grid, THREADS, smem, stream, mw, mx, a, stages, tiles_n, tiles_m); }
     return ce_check_launch("ce_gemm_tc (persistent)");
 }
 
@@ -1053,6 +1054,7 @@ int launch_pair(const CUtensorMap& mw, const CUtensorMap& mx, const TcArgs& a, i
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = ce_pdl_enabled() ? 2 : 1;
+    ce_note("gemm_tc_pair_kernel");
     cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel<BN, GU, KSUB>, mw, mx, a, stages, tiles_n, tiles_m);
     if (e != cudaSuccess) return ce_fail(CE_ERR_CUDA, "ce_gemm_tc (pairs): %s", cudaGetErrorString(e));
     return ce_check_launch("ce_gemm_tc (pairs)");

@@ -293,6 +293,7 @@ extern "C" int ce_sample(const float* logits, int rows, int V, const void* param
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = ce_pdl_enabled() ? 2 : 1;
+    ce_note("sample_kernel");
     cudaError_t e = cudaLaunchKernelEx(&cfg, sample_kernel, logits, V, (const SampleRow*)params, out, nb);
     if (e != cudaSuccess) return ce_fail(CE_ERR_CUDA, "ce_sample: %s", cudaGetErrorString(e));
     return ce_check_launch("ce_sample");
@@ -329,7 +330,7 @@ extern "C" int ce_argmax(const float* logits, int rows, int V, int* out, cudaStr
     if (rows == 0) return CE_OK;
     if (!logits || !out) return ce_fail(CE_ERR_ARG, "ce_argmax: null pointer");
     if (V <= 0) return ce_fail(CE_ERR_SIZE, "ce_argmax: vocabulary %d", V);
-    ce_launch(argmax_kernel, rows, SMP_THREADS, 0, stream, logits, V, out);
+    { ce_note("argmax_kernel"); ce_launch(argmax_kernel, rows, SMP_THREADS, 0, stream, logits, V, out); }
     return ce_check_launch("ce_argmax");
 }
 
@@ -356,6 +357,6 @@ extern "C" int ce_apply_penalties(float* logits, int V, const int* entries, int 
                                   cudaStream_t stream) {
     if (n == 0) return CE_OK;
     if (!logits || !entries || !row_params) return ce_fail(CE_ERR_ARG, "ce_apply_penalties: null pointer");
-    ce_launch(penalties_kernel, (n + 255) / 256, 256, 0, stream, logits, V, entries, n, row_params);
+    { ce_note("penalties_kernel"); ce_launch(penalties_kernel, (n + 255) / 256, 256, 0, stream, logits, V, entries, n, row_params); }
     return ce_check_launch("ce_apply_penalties");
 }

@@ -10,7 +10,7 @@ keep reading the same addresses), and the block tables stay resident on the devi
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import List, Optional, Sequence
+from typing import Any, Dict, List, Optional, Sequence, Tuple
 
 import numpy as np
 import torch
@@ -26,13 +26,16 @@ class StepEntry:
 class StepBuffers:
     """The pinned host buffer and its device twin, with fixed sections."""
 
-    def __init__(self, max_tokens: int, max_seqs: int, num_groups: int, device: torch.device):
+    def __init__(self, max_tokens: int, max_seqs: int, num_groups: int, device: torch.device,
+                 extra_sections: Sequence[Tuple[str, int]] = ()):
+        """``extra_sections``: (name, int32 count) of what the model's mixers lay out per step for their
+        own kernels (see ``Mixer.step_sections``)."""
         self.max_tokens, self.max_seqs = int(max_tokens), int(max_seqs)
         T, B = self.max_tokens, self.max_seqs
         upd = T + 2 * B + 8                      # the most table entries one step can add per group
         sizes = [("tokens", T), ("positions", T), ("seq_of_token", T), ("seq_slot", B), ("q_start", B + 1),
-                 ("ctx_len", B), ("rows", T), ("tiles", 2 * (B + T // 64 + 1)),
-                 ("tiles128", 2 * (B + T // 128 + 1))]
+                 ("ctx_len", B), ("rows", T)]
+        sizes += [(str(n), int(c)) for n, c in extra_sections]
         for g in range(num_groups):
             sizes += [(f"upd_idx{g}", upd), (f"upd_val{g}", upd)]
         self.offsets = {}
@@ -45,7 +48,13 @@ class StepBuffers:
             else torch.zeros(self.total, dtype=torch.int32)
         self.host_np = self.host.numpy()
         self.dev = torch.zeros(self.total, dtype=torch.int32, device=device)
-        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        # The device status word: kernels flag a bad index or a wait that gave up here.  On a GPU it is the
+        # word the tensor-core products report to as well, so one read covers every kernel of a step.
+        if torch.device(device).type == "cuda":
+            from .. import ops_tensor
+            self.status = ops_tensor.gemm_workspace(torch.device(device)).status
+        else:
+            self.status = torch.zeros(1, dtype=torch.int32, device=device)
         self._uploaded = None
 
     def host_section(self, name: str) -> np.ndarray:
@@ -89,11 +98,9 @@ class StepContext:
         self.h_slots: List[int] = []
         self.h_q_start: List[int] = []       # B + 1 entries
         self.h_ctx_before: List[int] = []    # tokens of each sequence already in the cache
-        self.tiles = bufs.dev_section("tiles")
-        self.n_tiles = 0                     # 64-token tiles of the sequences that bring more than one token
-        self.tiles128 = bufs.dev_section("tiles128")
-        self.n_tiles128 = 0                  # the same in tiles of 128 tokens (tcgen05 attention)
-        self.decode_splits = 1               # grid size of the split-KV decode kernel: >= ceil(longest decode context / positions per split)
+        self.bufs = bufs
+        #: what each kind of mixer laid out for this step (``Mixer.plan_step``), by the mixer's ``plan_key``
+        self.plans: Dict[str, Any] = {}
         self._scratch = {}
         self.n_decode = 0                    # the first n_decode sequences bring exactly one token
         self.max_position = 0

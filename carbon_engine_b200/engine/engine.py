@@ -23,7 +23,9 @@ from ..sampling.params import SamplingParams
 from ..sampling.sampler import Sampler, fresh_seed, top_logprobs
 from ..weights.loader import load_from_folder, load_random
 from .batch import StepEntry
-from .runner import ModelRunner
+from ..cache.manager import CacheError
+from ..csrc.kernel_lib import KernelError
+from .runner import ModelRunner, StepError
 from .scheduler import Scheduler, SubmitError
 
 DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "f32": torch.float32,
@@ -118,6 +120,7 @@ class Engine:
         self._done: Dict[int, RequestOutput] = {}
         self._next_id = 0
         self.d2h_bytes_last = 0
+        self._last_error: Optional[str] = None
         # while a decode step runs, the next one is laid out on the host on the guess that the same requests go on
         self.host_lookahead = bool(host_lookahead)
 
@@ -158,6 +161,7 @@ class Engine:
     def step(self) -> List[RequestOutput]:
         """Run one scheduler step; returns the requests that finished in it."""
         plan = self.scheduler.plan()
+        self._last_error = None
         if plan:
             entries = []
             for e in plan:
@@ -193,11 +197,12 @@ class Engine:
                         lives[i].logprobs.append(top_logprobs(base[j], tokens[i], lives[i].params.logprobs))
                 self.runner.check_status()
                 self.scheduler.commit(tokens)
-            except Exception as exc:       # the step failed: its requests end with an error, others go on
+            except (StepError, KernelError, CacheError, torch.OutOfMemoryError) as exc:
+                # the step failed on the device or for want of memory: its requests end with an error and
+                # give their pages back, the others go on (src/scheduler.rs:1436-1463).  Anything else is
+                # a fault of the program and is raised.
                 self._last_error = str(exc)
                 self.scheduler.fail_step()
-                if isinstance(exc, (KeyboardInterrupt, MemoryError)):
-                    raise
         return self._collect()
 
     def _collect(self) -> List[RequestOutput]:
@@ -208,7 +213,7 @@ class Engine:
             n = len(live.prompt)
             err = None
             if reason == "error":
-                err = getattr(self, "_last_error", None) or "request does not fit in the KV cache"
+                err = self._last_error or "request does not fit in the KV cache"
             ro = RequestOutput(rid, toks[:n], toks[n:], reason, err, live.logprobs or None)
             self.scheduler.forget(rid)
             out.append(ro)

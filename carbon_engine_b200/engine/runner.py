@@ -26,16 +26,8 @@ _STATUS = {
     2: "a token was to be written to a page its request does not hold",
     3: "a position beyond the rotary table (raise max_seq_len)",
     4: "attention read a page its request does not hold",
+    5: "a bounded wait inside a tensor-core kernel gave up (the step's results are not valid)",
 }
-
-
-def _split_bucket(splits: int) -> int:
-    """Round a split count up to the next value with at most three significant bits (1..8, 10, 12, 14,
-    16, 20, ...): a graph per bucket, and a grid at most a quarter larger than the contexts need."""
-    step = 1
-    while splits > 8 * step:
-        step *= 2
-    return (splits + step - 1) // step * step
 
 
 class ModelRunner:
@@ -43,12 +35,17 @@ class ModelRunner:
         self.model, self.storage = model, storage
         self.device, self.dtype = model.device, model.dtype
         self.max_step_tokens = int(max_step_tokens)
-        self.bufs = StepBuffers(self.max_step_tokens, storage.max_requests, len(storage.groups), self.device)
+        # one planner per kind of mixer that lays out tables of its own for a step
+        self._planners = {}
+        for block in model.blocks:
+            key = getattr(block.mixer, "plan_key", None)
+            if key is not None and key not in self._planners:
+                self._planners[key] = block.mixer
+        sections = [s for m in self._planners.values() for s in m.step_sections(self.max_step_tokens, storage.max_requests)]
+        self.bufs = StepBuffers(self.max_step_tokens, storage.max_requests, len(storage.groups), self.device, sections)
         self.fast_attention = True
         self.graphs_enabled = False
         self._graphs = {}
-        from .. import ops_tensor
-        self._decode_split = ops_tensor.decode_split()
         self._ahead = None                   # a next step laid out on the host in advance (prepare_decode_ahead)
         self._graph_pool = None
         self.h2d_bytes_last = 0
@@ -89,7 +86,14 @@ class ModelRunner:
                 ctx.h_tokens = tokens
                 return self._send(ctx, n_rows, commits, n_upd)
             self.storage._synced[:] = ahead["synced"]        # its table updates were never sent
-        return self._send(*self._layout(entries))
+        synced = self.storage._synced.copy()
+        try:
+            layout = self._layout(entries)
+        except Exception:
+            # entries laid out before the faulty one took table updates that will never be sent
+            self.storage._synced[:] = synced
+            raise
+        return self._send(*layout)
 
     def prepare_decode_ahead(self, request_ids: Sequence[int]) -> None:
         """Lay out the NEXT step on the host while the current one runs, on the guess that these requests
@@ -140,6 +144,8 @@ class ModelRunner:
         if T > self.max_step_tokens:
             raise StepError(f"{T} tokens in one step, but the engine was built for {self.max_step_tokens}")
         seen = set()
+        if sum(len(e.want) for e in entries) > T:
+            raise StepError("more wanted places than tokens in the step (a place is named twice)")
         for e in entries:
             if len(e.tokens) == 0:
                 raise StepError(f"request {e.request_id}: an entry needs at least one token")
@@ -188,24 +194,8 @@ class ModelRunner:
             off += n
         h_qs[len(entries)] = off
         ctx.h_q_start.append(off)
-        h_tiles = b.host_section("tiles")
-        h_tiles128 = b.host_section("tiles128")
-        nt = nt128 = 0
-        dec_ctx = 1
-        for bi, i in enumerate(order):
-            n = len(entries[i].tokens)
-            if bi < ctx.n_decode:
-                dec_ctx = max(dec_ctx, int(h_ctx[bi]))
-                continue
-            for q0 in range(0, n, 64):
-                h_tiles[2 * nt], h_tiles[2 * nt + 1] = bi, q0
-                nt += 1
-            for q0 in range(0, n, 128):
-                h_tiles128[2 * nt128], h_tiles128[2 * nt128 + 1] = bi, q0
-                nt128 += 1
-        ctx.n_tiles = nt
-        ctx.n_tiles128 = nt128
-        ctx.decode_splits = (dec_ctx + self._decode_split - 1) // self._decode_split
+        for key, mixer in self._planners.items():
+            ctx.plans[key] = mixer.plan_step(ctx)
         ctx.h_tokens = h_tok[:T].tolist()
 
         rows: List[int] = []
@@ -240,16 +230,14 @@ class ModelRunner:
 
     # -- CUDA graphs for decode steps -----------------------------------------------------------
     def enable_graphs(self) -> bool:
-        """Replay pure decode steps as CUDA graphs, one per (batch size, split count), captured at
+        """Replay pure decode steps as CUDA graphs, one per (batch size, the mixers' graph keys), captured at
         first use (the reference does the same per batch size, src/model/graph.rs:50-120).  Only
         models whose mixers read the step from device buffers alone can be captured."""
         self.graphs_enabled = bool(getattr(self.model, "graph_safe", False))
         return self.graphs_enabled
 
     def _replay_decode(self, ctx: StepContext, rows: torch.Tensor) -> torch.Tensor:
-        bucket = _split_bucket(ctx.decode_splits)
-        ctx.decode_splits = bucket          # a larger grid, the same result
-        key = (ctx.B, bucket)
+        key = (ctx.B,) + tuple(getattr(ctx.plans[k], "graph_key", None) for k in self._planners)
         entry = self._graphs.get(key)
         if entry is None:
             # once eagerly, so that lazy initialisation (library handles, kernel attributes) is not captured
@@ -291,4 +279,7 @@ class ModelRunner:
             code = int(self.bufs.status.item())
         if code != 0:
             self.bufs.status.zero_()
+            if self.device.type == "cuda":      # a kernel that gave up may have left its split counters half counted
+                from .. import ops_tensor
+                ops_tensor.reset_counters(self.device)
             raise StepError(f"device status {code}: {_STATUS.get(code, 'unknown')}")

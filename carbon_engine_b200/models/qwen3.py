@@ -40,7 +40,8 @@ def build_qwen3(cfg: Qwen3Config, max_positions: int) -> DecoderModel:
     embedding = Embedding(cfg.vocab_size, cfg.hidden_size, "model.embed_tokens.weight")
     final_norm = build_part("norm", "rmsnorm", width=cfg.hidden_size, eps=cfg.rms_norm_eps, name="model.norm.weight")
     if cfg.tie_word_embeddings:
-        head = LMHead(cfg.vocab_size, cfg.hidden_size, final_norm, None, tied_to=embedding)
+        head = LMHead(cfg.vocab_size, cfg.hidden_size, final_norm, None, tied_to=embedding,
+                      redundant_name="lm_head.weight")
     else:
         head = LMHead(cfg.vocab_size, cfg.hidden_size, final_norm, "lm_head.weight")
     return DecoderModel(cfg, embedding, blocks, head)

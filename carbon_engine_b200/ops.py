@@ -62,6 +62,25 @@ def _ok(code: int, n: int = 1) -> None:
     _launches += n
 
 
+def kernel_counts() -> dict:
+    """Launches so far by kernel name (a launch captured in a CUDA graph counts once, at capture): shows
+    WHICH kernel took each shape."""
+    import ctypes
+    k = kernels()
+    need = k.ce_kernel_counts(None, 0)
+    buf = ctypes.create_string_buffer(need + 64)
+    k.ce_kernel_counts(buf, len(buf))
+    out = {}
+    for line in buf.value.decode().splitlines():
+        name, _, n = line.rpartition("=")
+        out[name] = int(n)
+    return out
+
+
+def reset_kernel_counts() -> None:
+    kernels().ce_kernel_counts_reset()
+
+
 def embed(table: torch.Tensor, tokens: torch.Tensor, x: torch.Tensor, status: torch.Tensor) -> None:
     """x[t, :] = table[tokens[t], :] as float32."""
     _need(table, "table"); _need(tokens, "tokens", torch.int32); _need(x, "x", torch.float32)

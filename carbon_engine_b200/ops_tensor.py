@@ -57,15 +57,27 @@ class _Workspace:
 
 
 def gemm_workspace(device) -> _Workspace:
+    device = torch.device(device)
+    if device.type == "cuda" and device.index is None:
+        device = torch.device("cuda", torch.cuda.current_device())
     ws = _workspaces.get(device)
     if ws is None:
         ws = _workspaces[device] = _Workspace(device)
     return ws
 
 
+def reset_counters(device) -> None:
+    """Zero the split-K and split-KV counters (after a step that failed: its kernels may have stopped
+    half way through a count)."""
+    ws = _workspaces.get(torch.device(device))
+    if ws is not None:
+        ws.counters.zero_()
+        ws.attn_counters.zero_()
+
+
 def gemm_status(device) -> int:
     """0, or the code a tensor-core product left behind (5: a wait inside the kernel timed out)."""
-    ws = _workspaces.get(device)
+    ws = _workspaces.get(torch.device(device))
     return 0 if ws is None else int(ws.status.item())
 
 
@@ -94,15 +106,16 @@ def attention_supported(d: int, q_stride: int) -> bool:
     return 16 <= d <= 256 and d % 16 == 0 and q_stride % 2 == 0
 
 
-def attention_bf16(ctx, qkv, out, cache, table, nh, nkv, d, window, scale) -> bool:
-    """Decode kernel for the leading one-token sequences, flash kernel for the portions."""
+def attention_bf16(ctx, plan, qkv, out, cache, table, nh, nkv, d, window, scale) -> bool:
+    """Decode kernel for the leading one-token sequences, flash kernel for the portions.  ``plan``: the
+    step's tile lists and split bound (``parts.attention.AttentionPlan``)."""
     if not attention_supported(d, qkv.shape[1]):
         return False
     k = kernels()
     stream = torch.cuda.current_stream().cuda_stream
     args = (cache.page_size, table.shape[1], cache.k_pool.shape[0], int(window), float(scale))
     if ctx.n_decode > 0:
-        splits = ctx.decode_splits
+        splits = plan.decode_splits
         need = k.ce_attention_decode_scratch(ctx.n_decode, nh, d, splits)
         scratch = ctx.scratch("attention_decode", need)
         ws = gemm_workspace(qkv.device)
@@ -111,16 +124,16 @@ def attention_bf16(ctx, qkv, out, cache, table, nh, nkv, d, window, scale) -> bo
             ws.attn_counters.data_ptr(), ws.attn_counters.numel(), ctx.positions.data_ptr(), ctx.seq_slot.data_ptr(), ctx.q_start.data_ptr(), ctx.ctx_len.data_ptr(),
             table.data_ptr(), ctx.status.data_ptr(), ctx.n_decode, nh, nkv, d, qkv.shape[1], *args, splits, stream),
                 k.ce_attention_decode_kernels())
-    if ctx.n_tiles > 0 and USE_TENSOR_ATTENTION and getattr(ctx, "n_tiles128", 0) > 0 and \
+    if plan.n_tiles > 0 and USE_TENSOR_ATTENTION and plan.n_tiles128 > 0 and \
             k.ce_attention_prefill_tc_supported(d, cache.page_size, qkv.shape[1]):
         ops._ok(k.ce_attention_prefill_tc(
             qkv.data_ptr(), cache.k_pool.data_ptr(), cache.v_pool.data_ptr(), out.data_ptr(), ctx.seq_slot.data_ptr(),
-            ctx.q_start.data_ptr(), ctx.ctx_len.data_ptr(), table.data_ptr(), ctx.tiles128.data_ptr(),
-            ctx.status.data_ptr(), ctx.n_tiles128, qkv.shape[0], nh, nkv, d, qkv.shape[1], *args, stream))
-    elif ctx.n_tiles > 0:
+            ctx.q_start.data_ptr(), ctx.ctx_len.data_ptr(), table.data_ptr(), plan.tiles128.data_ptr(),
+            ctx.status.data_ptr(), plan.n_tiles128, qkv.shape[0], nh, nkv, d, qkv.shape[1], *args, stream))
+    elif plan.n_tiles > 0:
         ops._ok(k.ce_attention_prefill_bf16(
             qkv.data_ptr(), cache.k_pool.data_ptr(), cache.v_pool.data_ptr(), out.data_ptr(),
             ctx.positions.data_ptr(), ctx.seq_slot.data_ptr(), ctx.q_start.data_ptr(), ctx.ctx_len.data_ptr(),
-            table.data_ptr(), ctx.tiles.data_ptr(), ctx.status.data_ptr(), ctx.n_tiles, nh, nkv, d, qkv.shape[1],
+            table.data_ptr(), plan.tiles.data_ptr(), ctx.status.data_ptr(), plan.n_tiles, nh, nkv, d, qkv.shape[1],
             *args, stream))
     return True

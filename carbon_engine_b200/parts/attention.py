@@ -22,8 +22,31 @@ from .linear import ACCUM, STORE, Linear
 from .rope import PositionEncoding
 
 
+def split_bucket(splits: int) -> int:
+    """Round a split count up to the next value with at most three significant bits (1..8, 10, 12, 14,
+    16, 20, ...): few distinct grids (a captured graph per bucket), and a grid at most a quarter larger
+    than the contexts need."""
+    step = 1
+    while splits > 8 * step:
+        step *= 2
+    return (splits + step - 1) // step * step
+
+
+class AttentionPlan:
+    """What the attention kernels need of a step beyond the common tables: the tiles of the sequences
+    that bring more than one token, 64 and 128 tokens at a time, as (sequence, first token) pairs on
+    the device, and the grid bound of the split-KV decode kernel."""
+
+    def __init__(self, tiles, n_tiles, tiles128, n_tiles128, decode_splits):
+        self.tiles, self.n_tiles, self.tiles128, self.n_tiles128 = tiles, n_tiles, tiles128, n_tiles128
+        self.decode_splits = decode_splits       # >= ceil(longest one-token sequence's context / positions per split)
+        self.graph_key = decode_splits
+
+
 class PagedAttention(Mixer):
     graph_safe = True       # reads positions, tables and lengths from device buffers only
+    plan_key = "paged_attention"
+    TILE, TILE_TC = 64, 128         # tokens per tile of the mma.sync and of the tcgen05 flash kernel
 
     def __init__(self, hidden: int, heads: int, kv_heads: int, head_dim: int, prefix: str,
                  position: Optional[PositionEncoding] = None, qk_norm_eps: Optional[float] = None,
@@ -48,6 +71,10 @@ class PagedAttention(Mixer):
         return [TensorSpec(f"{self.prefix}.q_norm.weight", (self.head_dim,), "norm"),
                 TensorSpec(f"{self.prefix}.k_norm.weight", (self.head_dim,), "norm")]
 
+    def ignorable_tensors(self) -> List[str]:
+        # older checkpoints store the rotary frequencies, which are recomputed from the configuration
+        return [f"{self.prefix}.rotary_emb.inv_freq"] if self.position is not None else []
+
     def load(self, get: TensorGetter, device, dtype) -> None:
         if self.qk_norm_eps is not None:
             self.q_norm_weight = get(f"{self.prefix}.q_norm.weight").to(device).to(torch.float32).contiguous()
@@ -57,6 +84,34 @@ class PagedAttention(Mixer):
 
     def cache_spec(self) -> PagedCacheSpec:
         return PagedCacheSpec(self.kv_heads, self.head_dim, self.window)
+
+    def step_sections(self, max_tokens: int, max_seqs: int):
+        return [("paged_attention.tiles", 2 * (max_seqs + max_tokens // self.TILE + 1)),
+                ("paged_attention.tiles_tc", 2 * (max_seqs + max_tokens // self.TILE_TC + 1))]
+
+    def plan_step(self, ctx) -> AttentionPlan:
+        """Tile lists for the flash kernels and the decode kernel's split bound.  The bound is rounded up
+        to a bucket whether or not the step is replayed as a graph, so that both ways run the same grid."""
+        from .. import ops_tensor
+        h_tiles = ctx.bufs.host_section("paged_attention.tiles")
+        h_tiles_tc = ctx.bufs.host_section("paged_attention.tiles_tc")
+        nt = nt_tc = 0
+        longest = 1
+        for b in range(ctx.B):
+            n = ctx.h_q_start[b + 1] - ctx.h_q_start[b]
+            if b < ctx.n_decode:
+                longest = max(longest, ctx.h_ctx_before[b] + 1)
+                continue
+            for q0 in range(0, n, self.TILE):
+                h_tiles[2 * nt], h_tiles[2 * nt + 1] = b, q0
+                nt += 1
+            for q0 in range(0, n, self.TILE_TC):
+                h_tiles_tc[2 * nt_tc], h_tiles_tc[2 * nt_tc + 1] = b, q0
+                nt_tc += 1
+        per_split = ops_tensor.decode_split()
+        return AttentionPlan(ctx.bufs.dev_section("paged_attention.tiles"), nt,
+                             ctx.bufs.dev_section("paged_attention.tiles_tc"), nt_tc,
+                             split_bucket((longest + per_split - 1) // per_split))
 
     def forward(self, ctx, h: torch.Tensor, x: torch.Tensor, cache) -> None:
         T = h.shape[0]
@@ -81,7 +136,8 @@ class PagedAttention(Mixer):
         nh, nkv, d = self.heads, self.kv_heads, self.head_dim
         if qkv.dtype == torch.bfloat16 and ctx.fast_attention:
             from .. import ops_tensor
-            if ops_tensor.attention_bf16(ctx, qkv, out, cache, table, nh, nkv, d, self.window, self.scale):
+            if ops_tensor.attention_bf16(ctx, ctx.plans[self.plan_key], qkv, out, cache, table, nh, nkv, d, self.window,
+                                         self.scale):
                 return
         ops.attention_generic(qkv, qkv.shape[1], cache.k_pool, cache.v_pool, out, ctx.positions, ctx.seq_of_token,
                               ctx.seq_slot, table, ctx.status, nh, nkv, d, cache.page_size, self.window, self.scale)

@@ -9,7 +9,7 @@ part knows which model it is in.  The reference assembles its layers the same wa
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Callable, List, Optional, Tuple, Union
+from typing import Any, Callable, List, Optional, Tuple, Union
 
 import torch
 
@@ -57,6 +57,17 @@ class Part:
     def children(self) -> List["Part"]:
         return []
 
+    def ignorable_tensors(self) -> List[str]:
+        """Names (shell patterns allowed) of tensors a checkpoint may carry for this part although the
+        part does not use them: their presence is no error, they are not read."""
+        return []
+
+    def all_ignorable_tensors(self) -> List[str]:
+        out = list(self.ignorable_tensors())
+        for c in self.children():
+            out.extend(c.all_ignorable_tensors())
+        return out
+
     def all_tensor_specs(self) -> List[TensorSpec]:
         out = list(self.tensor_specs())
         for c in self.children():
@@ -78,7 +89,26 @@ class Norm(Part):
 class Mixer(Part):
     """Mixes information across the tokens of a sequence (attention, or anything with a cache)."""
 
+    #: Mixers whose kernels need per-step tables of their own (tile lists, split counts) name a key
+    #: here; the step function then calls :meth:`plan_step` once per step and key, whatever the
+    #: number of layers that share it, and the mixers find the result in ``ctx.plans[plan_key]``.
+    plan_key: Optional[str] = None
+
     def cache_spec(self) -> CacheSpec:
+        return None
+
+    def step_sections(self, max_tokens: int, max_seqs: int) -> List[Tuple[str, int]]:
+        """(name, int32 count) of the sections this kind of mixer wants in the step's pinned buffer
+        (uploaded with the step in one copy, at addresses that never change)."""
+        return []
+
+    def plan_step(self, ctx) -> Any:
+        """Lay out what this kind of mixer's kernels need for the step described by ``ctx`` (host lists
+        ``h_q_start``, ``h_ctx_before``, ``n_decode``; ``ctx.bufs.host_section(name)`` is the host side of
+        a section asked for in :meth:`step_sections`, ``ctx.bufs.dev_section(name)`` its device side).
+        Nothing may be launched or copied here: the step's one upload follows.  An attribute
+        ``graph_key`` of the result becomes part of the key under which a decode step is captured as a
+        CUDA graph (a grid size that changes with the contexts, for instance)."""
         return None
 
     def forward(self, ctx, h: torch.Tensor, x: torch.Tensor, cache) -> None:

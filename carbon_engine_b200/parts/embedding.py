@@ -34,11 +34,18 @@ class Embedding(Part):
 class LMHead(Part):
     """Final norm + head product for chosen rows.  ``tied_to`` shares an embedding's tensor."""
 
-    def __init__(self, vocab: int, width: int, norm: Norm, name: Optional[str], tied_to: Optional[Embedding] = None):
+    def __init__(self, vocab: int, width: int, norm: Norm, name: Optional[str], tied_to: Optional[Embedding] = None,
+                 redundant_name: Optional[str] = None):
+        """``redundant_name``: with a tied head, the name under which a checkpoint may still store a copy
+        of the head; it is ignored, as the reference ignores it (src/model/mod.rs:725)."""
         if (name is None) == (tied_to is None):
             raise ValueError("the head has either a tensor of its own or an embedding it is tied to")
         self.vocab, self.width, self.norm, self.name, self.tied_to = vocab, width, norm, name, tied_to
+        self.redundant_name = redundant_name if tied_to is not None else None
         self._weight: Optional[torch.Tensor] = None
+
+    def ignorable_tensors(self) -> List[str]:
+        return [self.redundant_name] if self.redundant_name else []
 
     def children(self) -> List[Part]:
         return [self.norm]

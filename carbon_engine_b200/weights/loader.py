@@ -2,7 +2,9 @@
 
 The loader compares what the model declares with what the folder holds BEFORE anything is copied,
 and raises one :class:`WeightError` that lists every missing tensor, every unexpected tensor and
-every wrong shape.  The reference reports a missing tensor by name (src/weights.rs:501-505) and
+every wrong shape.  Tensors that parts declare ignorable (a tied model's redundant ``lm_head.weight``,
+stored ``rotary_emb.inv_freq``) are passed over as the reference passes them over
+(src/model/mod.rs:725).  The reference reports a missing tensor by name (src/weights.rs:501-505) and
 lets shape mismatches surface later as matmul errors; here nothing loads unless all of it fits.
 
 Matrices are held in the compute dtype (bfloat16, or float32 on the 32-bit path); norm weights are
@@ -10,6 +12,7 @@ held in float32 whatever they were stored in, so a tensor stored in 32-bit stays
 """
 from __future__ import annotations
 
+import fnmatch
 import json
 import os
 from typing import Dict, List, Optional, Sequence
@@ -41,11 +44,13 @@ class WeightError(ValueError):
 _FLOATS = (torch.float32, torch.bfloat16, torch.float16)
 
 
-def check_tensors(specs: Sequence[TensorSpec], directory: TensorDirectory) -> None:
+def check_tensors(specs: Sequence[TensorSpec], directory: TensorDirectory, ignorable: Sequence[str] = ()) -> None:
+    """``ignorable``: names or shell patterns of tensors the folder may hold without the model using them
+    (a copy of a tied head, stored rotary frequencies); every other undeclared tensor is an error."""
     expected: Dict[str, TensorSpec] = {s.name: s for s in specs}
     have = set(directory.names())
     missing = [n for n in expected if n not in have]
-    unexpected = sorted(n for n in have if n not in expected)
+    unexpected = sorted(n for n in have if n not in expected and not any(fnmatch.fnmatchcase(n, pat) for pat in ignorable))
     wrong_shape: List[str] = []
     wrong_dtype: List[str] = []
     for n, s in expected.items():
@@ -60,7 +65,7 @@ def check_tensors(specs: Sequence[TensorSpec], directory: TensorDirectory) -> No
 
 def load_from_folder(model, model_dir: str, device: torch.device, dtype: torch.dtype) -> None:
     directory = TensorDirectory(model_dir)
-    check_tensors(model.all_tensor_specs(), directory)
+    check_tensors(model.all_tensor_specs(), directory, model.all_ignorable_tensors())
     model.load_weights(directory.get, device, dtype)
 
 

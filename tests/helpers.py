@@ -14,9 +14,14 @@ import torch
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
-# Three tiny configurations that differ in every size and option: layers, width, head counts and
+# Tiny configurations that differ in every size and option: layers, width, head counts and
 # group size, head size (q width == hidden, != hidden), intermediate and vocabulary sizes that are no
 # powers of two, rope theta, norm eps, tied or untied head, cache page size, and a window.
+# A, B and C have head sizes 16, 32 and 48: in bfloat16 they run the cp.async decode kernel, the
+# mma.sync flash kernel and the one-block tcgen05 product.  D (head size 128) and E (head size 64, one
+# windowed layer) have the head geometry of the real checkpoints and, with prompts of several hundred
+# tokens, run what serving runs: the TMA decode kernel with its merge inside a cluster, the tcgen05
+# flash kernel over a cached prefix, the CTA-pair product (more than 256 tokens) and split-K.
 TINY = {
     "A": dict(config=dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=2, hidden_size=64,
                           num_attention_heads=4, num_key_value_heads=2, head_dim=16, intermediate_size=128,
@@ -35,7 +40,21 @@ TINY = {
                           layer_types=["full_attention", "sliding_attention", "sliding_attention", "full_attention"],
                           sliding_window=37),
               page_size=32, seed=5),
+    "D": dict(config=dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=2, hidden_size=512,
+                          num_attention_heads=8, num_key_value_heads=2, head_dim=128, intermediate_size=1536,
+                          vocab_size=2003, rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False,
+                          max_position_embeddings=4096),
+              page_size=64, seed=41),
+    "E": dict(config=dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=3, hidden_size=384,
+                          num_attention_heads=6, num_key_value_heads=3, head_dim=64, intermediate_size=1000,
+                          vocab_size=1511, rope_theta=10000.0, rms_norm_eps=1e-5, tie_word_embeddings=True,
+                          max_position_embeddings=2048,
+                          layer_types=["full_attention", "sliding_attention", "full_attention"], sliding_window=200),
+              page_size=16, seed=77),
 }
+#: the configurations with small head sizes (quick everywhere) and those with the product's head sizes
+SMALL_HEADS = ("A", "B", "C")
+REAL_HEADS = ("D", "E")
 
 # tolerances, relative to the largest |logit| of the compared rows: the reference's own kernel
 # self-test accepts 1e-4 in float32 and 3e-2 in 16-bit (src/device.rs:776-848)

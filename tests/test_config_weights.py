@@ -123,7 +123,9 @@ def test_one_error_lists_missing_unexpected_and_wrong_shapes(tmp_path):
     del tensors["model.layers.1.mlp.down_proj.weight"]
     del tensors["model.norm.weight"]
     tensors["model.layers.0.self_attn.q_proj.weight"] = torch.zeros(8, 64, dtype=torch.bfloat16)
-    tensors["lm_head.weight"] = torch.zeros(256, 64, dtype=torch.bfloat16)      # tied model: not expected
+    tensors["lm_head.weight"] = torch.zeros(256, 64, dtype=torch.bfloat16)      # tied model: a redundant copy, ignored
+    tensors["model.layers.0.self_attn.rotary_emb.inv_freq"] = torch.zeros(8)    # recomputed, ignored
+    tensors["model.layers.0.self_attn.q_bias"] = torch.zeros(64)                # nobody declares this
     tensors["model.layers.0.self_attn.k_norm.weight"] = torch.zeros(16, dtype=torch.int32)
     bad = tmp_path / "bad"
     bad.mkdir()
@@ -132,14 +134,17 @@ def test_one_error_lists_missing_unexpected_and_wrong_shapes(tmp_path):
     arch, cfg = load_config(str(bad))
     model = arch.build_model(cfg, 64)
     with pytest.raises(WeightError) as ei:
-        check_tensors(model.all_tensor_specs(), TensorDirectory(str(bad)))
+        check_tensors(model.all_tensor_specs(), TensorDirectory(str(bad)), model.all_ignorable_tensors())
     e = ei.value
     assert set(e.missing) == {"model.layers.1.mlp.down_proj.weight", "model.norm.weight"}
-    assert e.unexpected == ["lm_head.weight"]
+    assert e.unexpected == ["model.layers.0.self_attn.q_bias"]
+    with pytest.raises(WeightError) as strict:          # without the parts' list every undeclared tensor is reported
+        check_tensors(model.all_tensor_specs(), TensorDirectory(str(bad)))
+    assert "lm_head.weight" in strict.value.unexpected
     assert len(e.wrong_shape) == 1 and "q_proj" in e.wrong_shape[0] and "[8, 64]" in e.wrong_shape[0]
     assert len(e.wrong_dtype) == 1 and "k_norm" in e.wrong_dtype[0]
     msg = str(e)
-    for word in ("missing", "unexpected", "wrong shapes", "down_proj", "lm_head.weight"):
+    for word in ("missing", "unexpected", "wrong shapes", "down_proj", "q_bias"):
         assert word in msg
 
 

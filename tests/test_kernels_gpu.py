@@ -406,7 +406,6 @@ class FakeCache:
 def run_mma_attention(seqs, nh, nkv, d, ps, window, scale, seed=0, far=None, extra_splits=0):
     """Returns (got [T, nh, d] in the caller's sequence order, want)."""
     from carbon_engine_b200 import ops_tensor
-    torch.manual_seed(seed)
     lens = [c + n for c, n in seqs]
     table, kp, vp = paged_layout(lens, ps, nkv, d, torch.bfloat16, shuffle_seed=seed + 1)
     ctx = FakeCtx(seqs)
@@ -417,9 +416,12 @@ def run_mma_attention(seqs, nh, nkv, d, ps, window, scale, seed=0, far=None, ext
     for bi, i in enumerate(ctx.order):
         c, n = seqs[i]
         L = c + n
-        q_all = (torch.randn(L, nh, d) * 1.5).to(torch.bfloat16)
-        k_all = (torch.randn(L, nkv, d) * 1.5).to(torch.bfloat16)
-        v_all = torch.randn(L, nkv, d).to(torch.bfloat16)
+        # a sequence's numbers depend on the seed and on its own lengths only, so that the same sequence
+        # can be run again in another batch
+        gen = torch.Generator().manual_seed(seed * 1000003 + c * 131 + n)
+        q_all = (torch.randn(L, nh, d, generator=gen) * 1.5).to(torch.bfloat16)
+        k_all = (torch.randn(L, nkv, d, generator=gen) * 1.5).to(torch.bfloat16)
+        v_all = torch.randn(L, nkv, d, generator=gen).to(torch.bfloat16)
         if far is not None and i == far[0]:
             k_all[far[1], 0] = (q_all[L - 1, nh - 1].float() * 3.0).to(torch.bfloat16)     # last head's last query loves this key
         fill_pools(kp, vp, table.cpu().numpy(), i, k_all.to(dev()), v_all.to(dev()), ps)
@@ -427,7 +429,7 @@ def run_mma_attention(seqs, nh, nkv, d, ps, window, scale, seed=0, far=None, ext
         want[i] = plain.causal_attention(q_all.double(), k_all.double(), v_all.double(), scale, window)[c:]
         t += n
     out = torch.full((ctx.T, nh * d), float("nan"), dtype=torch.bfloat16, device=dev())
-    ok = ops_tensor.attention_bf16(ctx, q_step, out, FakeCache(kp, vp, ps), table, nh, nkv, d, window, scale)
+    ok = ops_tensor.attention_bf16(ctx, ctx, q_step, out, FakeCache(kp, vp, ps), table, nh, nkv, d, window, scale)
     assert ok and ctx.status.item() == 0
     got, t = {}, 0
     for bi, i in enumerate(ctx.order):
@@ -462,9 +464,11 @@ def test_mma_decode_result_does_not_depend_on_the_grid():
     for i in range(2):
         assert rel_err(b[i], a[i].double()) < 5e-3
         assert rel_err(b[i], want[i]) < 2e-2
-    alone, _ = run_mma_attention(seqs[1:], 8, 2, 64, 16, 0, 0.125, seed=7)
-    # (not the same random draws as above, so only the shape of the call is checked here)
-    assert alone[0].shape == (1, 8, 64)
+    # the second sequence alone (same numbers): another number of sequences and another longest context,
+    # so other split sizes; again the last bit at most
+    alone, want_alone = run_mma_attention(seqs[1:], 8, 2, 64, 16, 0, 0.125, seed=7)
+    assert torch.equal(want_alone[0], want[1])
+    assert rel_err(alone[0], a[1].double()) < 5e-3 and rel_err(alone[0], want[1]) < 2e-2
 
 
 @pytest.mark.parametrize("far,window,visible", [(0, 0, True), (63, 0, True), (64, 0, True), (255, 0, True), (256, 0, True),

@@ -1,8 +1,12 @@
 """A plain, slow implementation of the Qwen3 dense decoder for tests.
 
-It rests on the reference's FORMULAS (each function cites the file and lines it restates): the
-reference itself is Rust on the candle library and can be neither imported nor compiled on the
-machines these tests run on, so there is no golden output from its model code.  It shares no code
+It restates the reference's FORMULAS (each function cites the file and lines it restates).  The
+reference's model code is Rust on the candle library and can be neither imported nor compiled on
+the machines these tests run on, so there is no golden output of its whole model; but its CUDA
+kernel sources for attention, for the sampler's random numbers and for a key norm + rotation do
+build for the CPU, and tests/test_reference_anchor.py holds ``causal_attention``, ``rms_norm``,
+``apply_rope`` and the sampler's uniforms to their output (tests/golden/).  SwiGLU, the order of a
+layer's operations and the head rest on the formulas alone.  This file shares no code
 with the engine: it reads config.json and model.safetensors itself, processes whole sequences with
 no cache, and has one function per part.  Everything is float64 by default, so that both the
 float32 and the bfloat16 engine can be compared with the same numbers.

@@ -203,7 +203,7 @@ def test_cuda_graphs_give_the_same_tokens_as_eager(models, name, dtype):
     from carbon_engine_b200 import SamplingParams, ops
     d, cfg, w = models[name]
     rng = np.random.default_rng(8)
-    lengths = (30, 3, 250, 77, 12) if name == "B" else (620, 3, 250, 77, 900)
+    lengths = (30, 3, 250, 77, 12) if name == "B" else (620, 3, 250, 900, 77)
     prompts = [random_tokens(rng, n, cfg["vocab_size"]) for n in lengths]
     sps = [SamplingParams(max_tokens=m, ignore_eos=True) for m in (40, 25, 30, 9, 50)]
     kw = dict(max_seq_len=1024) if name == "B" else dict(max_seq_len=2048, kv_tokens=8192)

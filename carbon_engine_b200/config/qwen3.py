@@ -9,14 +9,17 @@ width (src/config.rs:643), ``rms_norm_eps`` to 1e-6 (src/config.rs:649),
 (src/config.rs:653-657), ``hidden_act`` to "silu" (src/config.rs:663-667).  Qwen3 has per-head
 q/k norms and no attention bias (src/config.rs:658-662).
 
-Where the reference warns and continues (an unknown rope scaling, src/config.rs:520-524) this
-class refuses the config: a wrong position encoding gives wrong logits silently.
+``rope_scaling`` (or ``rope_parameters``) of kind "linear", "llama3" or "yarn" is read with the
+reference's keys and defaults (src/config.rs:483-519).  Where the reference warns and continues (an
+unknown kind, src/config.rs:520-524) this class refuses the config: a wrong position encoding gives
+wrong logits silently.
 """
 from __future__ import annotations
 
 from dataclasses import dataclass
 from typing import Any, Dict, Optional, Tuple
 
+from ..parts.rope import RopeScaling, yarn_mscale
 from .base import ConfigError, ModelConfig, token_id_list
 
 FULL_ATTENTION = "full_attention"
@@ -43,6 +46,38 @@ def _opt_float(d: Dict[str, Any], key: str) -> Optional[float]:
     return float(v)
 
 
+def _rope_scaling(r: Dict[str, Any], d: Dict[str, Any]) -> Optional[RopeScaling]:
+    """``rope_scaling`` / ``rope_parameters`` with the reference's keys and defaults (src/config.rs:483-529)."""
+    kind = r.get("rope_type", r.get("type"))
+    kind = "default" if kind is None else kind
+    factor = _opt_float(r, "factor")
+    factor = 1.0 if factor is None else factor
+    if kind == "default":
+        return None
+    if factor <= 0.0:
+        raise ConfigError(f"config.json: rope scaling factor {factor} must be positive")
+
+    def number(key: str, default: float) -> float:
+        v = _opt_float(r, key)
+        return default if v is None else v
+    if kind == "linear":
+        return RopeScaling("linear", factor)
+    if kind == "llama3":
+        return RopeScaling("llama3", factor, low_freq_factor=number("low_freq_factor", 1.0),
+                           high_freq_factor=number("high_freq_factor", 4.0),
+                           original_max_position=_opt_int(r, "original_max_position_embeddings", 8192))
+    if kind == "yarn":
+        ms, ms_all = _opt_float(r, "mscale"), _opt_float(r, "mscale_all_dim")
+        attention = _opt_float(r, "attention_factor")
+        if attention is None:
+            attention = yarn_mscale(factor, ms) / yarn_mscale(factor, ms_all) if ms is not None and ms_all is not None \
+                else yarn_mscale(factor, 1.0)
+        original = _opt_int(r, "original_max_position_embeddings", _opt_int(d, "max_position_embeddings", 4096))
+        return RopeScaling("yarn", factor, original_max_position=original, beta_fast=number("beta_fast", 32.0),
+                           beta_slow=number("beta_slow", 1.0), attention_factor=attention)
+    raise ConfigError(f"config.json: rope scaling '{kind}' is not supported (default, linear, llama3, yarn)")
+
+
 @dataclass(frozen=True)
 class Qwen3Config(ModelConfig):
     hidden_size: int = 0
@@ -55,6 +90,7 @@ class Qwen3Config(ModelConfig):
     rope_theta: float = 10000.0
     tie_word_embeddings: bool = False
     hidden_act: str = "silu"
+    rope_scaling: Optional[RopeScaling] = None
     layer_types: Tuple[str, ...] = ()
     sliding_window: Optional[int] = None
     bos_token_id: Optional[int] = None
@@ -93,10 +129,7 @@ class Qwen3Config(ModelConfig):
         if theta is None and isinstance(rope_params, dict):
             theta = _opt_float(rope_params, "rope_theta")
         theta = 10000.0 if theta is None else theta
-        if isinstance(rope_params, dict):
-            kind = rope_params.get("rope_type", rope_params.get("type", "default"))
-            if kind not in (None, "default"):
-                raise ConfigError(f"config.json: rope scaling '{kind}' is not supported (plain rotary only)")
+        scaling = _rope_scaling(rope_params, d) if isinstance(rope_params, dict) else None
         partial = _opt_float(d, "partial_rotary_factor")
         if partial is not None and partial != 1.0:
             raise ConfigError("config.json: partial_rotary_factor other than 1.0 is not a Qwen3 dense model")
@@ -148,7 +181,7 @@ class Qwen3Config(ModelConfig):
             architecture=str(archs[0]), vocab_size=vocab, max_position_embeddings=max_pos,
             eos_token_ids=tuple(eos), hidden_size=hidden, intermediate_size=inter,
             num_hidden_layers=layers, num_attention_heads=heads, num_key_value_heads=kv_heads,
-            head_dim=head_dim, rms_norm_eps=eps, rope_theta=theta, tie_word_embeddings=tie,
+            head_dim=head_dim, rms_norm_eps=eps, rope_theta=theta, rope_scaling=scaling, tie_word_embeddings=tie,
             hidden_act=act, layer_types=layer_types, sliding_window=window,
             bos_token_id=bos if isinstance(bos, int) and not isinstance(bos, bool) else None,
             torch_dtype=str(dtype),
@@ -173,6 +206,15 @@ class Qwen3Config(ModelConfig):
             "attention_bias": False,
             "torch_dtype": self.torch_dtype,
         }
+        if self.rope_scaling is not None:
+            rs = self.rope_scaling
+            out["rope_scaling"] = {"rope_type": rs.kind, "factor": rs.factor}
+            if rs.kind == "llama3":
+                out["rope_scaling"].update(low_freq_factor=rs.low_freq_factor, high_freq_factor=rs.high_freq_factor,
+                                           original_max_position_embeddings=rs.original_max_position)
+            elif rs.kind == "yarn":
+                out["rope_scaling"].update(original_max_position_embeddings=rs.original_max_position, beta_fast=rs.beta_fast,
+                                           beta_slow=rs.beta_slow, attention_factor=rs.attention_factor)
         if self.eos_token_ids:
             out["eos_token_id"] = list(self.eos_token_ids) if len(self.eos_token_ids) > 1 else self.eos_token_ids[0]
         if self.bos_token_id is not None:

@@ -20,7 +20,7 @@ from ..parts.registry import build_part
 
 def build_qwen3(cfg: Qwen3Config, max_positions: int) -> DecoderModel:
     position = build_part("position", "rotary", head_dim=cfg.head_dim, theta=cfg.rope_theta,
-                          max_positions=max_positions)
+                          max_positions=max_positions, scaling=cfg.rope_scaling)
     blocks = []
     for i in range(cfg.num_hidden_layers):
         p = f"model.layers.{i}"

@@ -49,7 +49,8 @@ TINY = {
                           num_attention_heads=6, num_key_value_heads=3, head_dim=64, intermediate_size=1000,
                           vocab_size=1511, rope_theta=10000.0, rms_norm_eps=1e-5, tie_word_embeddings=True,
                           max_position_embeddings=2048,
-                          layer_types=["full_attention", "sliding_attention", "full_attention"], sliding_window=200),
+                          layer_types=["full_attention", "sliding_attention", "full_attention"], sliding_window=200,
+                          rope_scaling={"rope_type": "yarn", "factor": 4.0, "original_max_position_embeddings": 512}),
               page_size=16, seed=77),
 }
 #: the configurations with small head sizes (quick everywhere) and those with the product's head sizes

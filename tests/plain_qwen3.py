@@ -68,12 +68,52 @@ def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
     return x * torch.rsqrt((x * x).mean(dim=-1, keepdim=True) + eps) * weight
 
 
-def rope_tables(positions: torch.Tensor, rotary_dim: int, theta: float):
-    """inv_freq[i] = theta^(-2i/rd); angle = pos * inv_freq[i] (src/model/layers.rs:169-173, 237-251)."""
-    i = torch.arange(0, rotary_dim // 2, dtype=torch.float64)
-    inv_freq = theta ** (-2.0 * i / rotary_dim)
+def scaled_inv_freq(rotary_dim: int, theta: float, scaling: Optional[dict], max_position_embeddings: int = 4096):
+    """Rotary frequencies with the config.json's ``rope_scaling`` applied (src/model/layers.rs:169-223, keys
+    and defaults of src/config.rs:483-519); returns (inv_freq float64 [rd/2], cos/sin multiplier)."""
+    i = np.arange(0, rotary_dim // 2, dtype=np.float64)
+    inv = 1.0 / theta ** (2.0 * i / rotary_dim)
+    kind = (scaling or {}).get("rope_type", (scaling or {}).get("type", "default"))
+    if not scaling or kind == "default":
+        return torch.from_numpy(inv), 1.0
+    factor = float(scaling.get("factor", 1.0))
+    if kind == "linear":
+        return torch.from_numpy(inv / factor), 1.0
+    if kind == "llama3":
+        lo, hi = float(scaling.get("low_freq_factor", 1.0)), float(scaling.get("high_freq_factor", 4.0))
+        old = float(scaling.get("original_max_position_embeddings", 8192))
+        wl = 2.0 * np.pi / inv
+        smooth = (old / wl - lo) / (hi - lo)
+        blended = (1.0 - smooth) * inv / factor + smooth * inv
+        out = np.where(wl > old / lo, inv / factor, np.where(wl >= old / hi, blended, inv))
+        return torch.from_numpy(out), 1.0
+    if kind == "yarn":
+        old = float(scaling.get("original_max_position_embeddings", max_position_embeddings))
+        fast, slow = float(scaling.get("beta_fast", 32.0)), float(scaling.get("beta_slow", 1.0))
+        corr = lambda rot: rotary_dim * math.log(old / (rot * 2.0 * math.pi)) / (2.0 * math.log(theta))
+        low, high = max(math.floor(corr(fast)), 0.0), min(math.ceil(corr(slow)), rotary_dim - 1.0)
+        if high == low:
+            high += 0.001
+        ramp = np.clip((i - low) / (high - low), 0.0, 1.0)
+        out = inv / factor * ramp + inv * (1.0 - ramp)
+        mscale = lambda m: 1.0 if factor <= 1.0 else 0.1 * m * math.log(factor) + 1.0      # src/config.rs:108-114
+        if "attention_factor" in scaling:
+            att = float(scaling["attention_factor"])
+        elif "mscale" in scaling and "mscale_all_dim" in scaling:
+            att = mscale(float(scaling["mscale"])) / mscale(float(scaling["mscale_all_dim"]))
+        else:
+            att = mscale(1.0)
+        return torch.from_numpy(out), att
+    raise ValueError(kind)
+
+
+def rope_tables(positions: torch.Tensor, rotary_dim: int, theta: float, scaling: Optional[dict] = None,
+                max_position_embeddings: int = 4096):
+    """inv_freq[i] = theta^(-2i/rd), rescaled if the config says so; angle = pos * inv_freq[i]; cos and sin
+    times the scheme's attention factor (src/model/layers.rs:169-173, 237-251)."""
+    inv_freq, att = scaled_inv_freq(rotary_dim, theta, scaling, max_position_embeddings)
     ang = positions.to(torch.float64)[:, None] * inv_freq[None, :]
-    return ang.cos(), ang.sin()
+    return ang.cos() * att, ang.sin() * att
 
 
 def apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
@@ -120,7 +160,8 @@ def attention_block(h: torch.Tensor, w: Dict[str, torch.Tensor], prefix: str, cf
     v = (h @ w[f"{prefix}.v_proj.weight"].T).view(T, nkv, d)
     q = rms_norm(q, w[f"{prefix}.q_norm.weight"], eps)
     k = rms_norm(k, w[f"{prefix}.k_norm.weight"], eps)
-    cos, sin = rope_tables(positions, d, float(cfg.get("rope_theta", 10000.0)))
+    cos, sin = rope_tables(positions, d, float(cfg.get("rope_theta", 10000.0)),
+                           cfg.get("rope_scaling") or cfg.get("rope_parameters"), cfg.get("max_position_embeddings", 4096))
     q, k = apply_rope(q, cos, sin), apply_rope(k, cos, sin)
     a = causal_attention(q, k, v, 1.0 / math.sqrt(d), window)
     return a.reshape(T, nh * d) @ w[f"{prefix}.o_proj.weight"].T

@@ -42,9 +42,62 @@ def test_rope_theta_under_rope_parameters():
     assert c.rope_theta == 5e5
 
 
+def test_rope_scaling_keys_and_defaults():
+    """linear, llama3 and yarn with the reference's keys and defaults (src/config.rs:483-519), and the
+    frequencies they give (src/model/layers.rs:169-234; the values of its own test, :735-751)."""
+    import math
+    import plain_qwen3 as plain
+    from carbon_engine_b200.parts.rope import rope_inv_freq
+    base = dict(BASE, hidden_size=64, num_attention_heads=1, num_key_value_heads=1, head_dim=64, rope_theta=1000000.0,
+                max_position_embeddings=131072)
+    plain_freq = rope_inv_freq(64, 1e6, None)
+    c = Qwen3Config.from_dict(dict(base, rope_scaling={"rope_type": "yarn", "factor": 4.0,
+                                                       "original_max_position_embeddings": 32768}))
+    rs = c.rope_scaling
+    assert (rs.kind, rs.factor, rs.original_max_position, rs.beta_fast, rs.beta_slow) == ("yarn", 4.0, 32768, 32.0, 1.0)
+    assert abs(rs.attention_factor - (0.1 * math.log(4.0) + 1.0)) < 1e-12
+    yarn = rope_inv_freq(64, 1e6, rs)
+    # high-frequency dimensions are left alone, low-frequency ones are divided by the factor
+    assert yarn[0] == plain_freq[0] and abs(yarn[31] - plain_freq[31] / 4.0) < 1e-15
+    assert all(p / 4.0 - 1e-18 <= y <= p for y, p in zip(yarn, plain_freq))
+    assert any(p / 4.0 + 1e-12 < y < p - 1e-12 for y, p in zip(yarn, plain_freq))          # and a ramp between
+    # yarn without original_max_position_embeddings takes max_position_embeddings; mscale pairs give the factor
+    c2 = Qwen3Config.from_dict(dict(base, rope_parameters={"type": "yarn", "factor": 8.0, "mscale": 1.0, "mscale_all_dim": 0.5}))
+    assert c2.rope_scaling.original_max_position == 131072
+    assert abs(c2.rope_scaling.attention_factor - (0.1 * math.log(8) + 1) / (0.05 * math.log(8) + 1)) < 1e-12
+    lin = Qwen3Config.from_dict(dict(base, rope_scaling={"rope_type": "linear", "factor": 2.0})).rope_scaling
+    assert rope_inv_freq(64, 1e6, lin) == [f / 2.0 for f in plain_freq]
+    l3 = Qwen3Config.from_dict(dict(base, rope_scaling={"rope_type": "llama3", "factor": 8.0})).rope_scaling
+    assert (l3.low_freq_factor, l3.high_freq_factor, l3.original_max_position) == (1.0, 4.0, 8192)
+    got = rope_inv_freq(64, 1e6, l3)
+    assert got[0] == plain_freq[0] and abs(got[31] - plain_freq[31] / 8.0) < 1e-18
+    # the engine's frequencies are those of the plain implementation, for every kind
+    for raw in ({"rope_type": "yarn", "factor": 4.0, "original_max_position_embeddings": 32768},
+                {"rope_type": "yarn", "factor": 2.5, "beta_fast": 16, "beta_slow": 2, "attention_factor": 1.3},
+                {"rope_type": "linear", "factor": 3.0},
+                {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                 "original_max_position_embeddings": 8192}):
+        cfg = Qwen3Config.from_dict(dict(base, rope_scaling=raw))
+        want, att = plain.scaled_inv_freq(64, 1e6, raw, 131072)
+        assert torch.allclose(torch.tensor(rope_inv_freq(64, 1e6, cfg.rope_scaling), dtype=torch.float64), want, rtol=1e-14, atol=0)
+        assert abs(att - (cfg.rope_scaling.attention_factor if raw["rope_type"] == "yarn" else 1.0)) < 1e-12
+        again = Qwen3Config.from_dict(cfg.to_json_dict())                 # and the scaling survives the round trip
+        assert again.rope_scaling == cfg.rope_scaling
+    assert Qwen3Config.from_dict(dict(base, rope_scaling={"rope_type": "default"})).rope_scaling is None
+    # the tables of the part: cos and sin carry YaRN's attention factor
+    from carbon_engine_b200.parts.rope import RotaryEmbedding
+    raw = {"rope_type": "yarn", "factor": 4.0, "original_max_position_embeddings": 64}
+    part = RotaryEmbedding(64, 1e6, 300, scaling=Qwen3Config.from_dict(dict(base, rope_scaling=raw)).rope_scaling)
+    part.prepare(torch.device("cpu"))
+    c, s_ = plain.rope_tables(torch.arange(300), 64, 1e6, raw)
+    assert torch.allclose(part.cos.double(), c, atol=1e-7) and torch.allclose(part.sin.double(), s_, atol=1e-7)
+    assert abs(float(part.cos[0, 0]) - (0.1 * math.log(4.0) + 1.0)) < 1e-6
+
+
 @pytest.mark.parametrize("bad,word", [
     (dict(num_key_value_heads=4), "multiple"), (dict(head_dim=7), "even"), (dict(hidden_act="gelu"), "silu"),
-    (dict(rope_scaling={"rope_type": "yarn", "factor": 4.0}), "yarn"), (dict(quantization_config={"bits": 4}), "quantis"),
+    (dict(rope_scaling={"rope_type": "dynamic", "factor": 4.0}), "dynamic"),
+    (dict(rope_scaling={"rope_type": "linear", "factor": 0.0}), "factor"), (dict(quantization_config={"bits": 4}), "quantis"),
     (dict(vocab_size=0), "vocab_size"), (dict(attention_bias=True), "attention_bias"),
     (dict(layer_types=["full_attention"]), "layer_types"),
     (dict(layer_types=["full_attention", "sliding_attention"]), "sliding_window"),

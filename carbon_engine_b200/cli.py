@@ -4,6 +4,7 @@ Sub-commands and option names follow the reference where it has them (src/main.r
 flags, :381-414 ``generate``, :634-661 ``tiny-model``, :51-61 ``devices --selftest``):
 
     python -m carbon_engine_b200 generate --model DIR --prompt-ids 1,2,3 --max-tokens 16 --print-ids
+    python -m carbon_engine_b200 generate --model DIR --prompt-ids 1,2,3 --prompt-ids 7,8 --temperature 0.8 --seed 5
     python -m carbon_engine_b200 tiny-model --out DIR --layers 2 --hidden 64 --seed 1
     python -m carbon_engine_b200 devices --selftest
 
@@ -56,45 +57,54 @@ def _parse_ids(text: str) -> List[int]:
 
 
 def cmd_generate(a) -> int:
+    """Submit the prompt (or prompts) to an engine running on its own thread and print tokens as their
+    events arrive, as the reference's ``generate`` consumes its event stream (src/main.rs:1020-1066)."""
+    from .engine.handle import Done, EngineHandle, Error, Token
     from .sampling.params import SamplingParams
-    if a.prompt_ids is None:
+    if not a.prompt_ids:
         raise SystemExit("--prompt-ids is required (text prompts need a tokenizer, which this engine does not carry)")
-    ids = _parse_ids(a.prompt_ids)
-    eng = _make_engine(a)
-    sp = SamplingParams(temperature=a.temperature, top_p=a.top_p, top_k=a.top_k, min_p=a.min_p, max_tokens=a.max_tokens,
-                        seed=a.seed, ignore_eos=a.ignore_eos)
-    t0 = time.perf_counter()
+    prompts = [_parse_ids(p) for p in a.prompt_ids]
+    handle = EngineHandle(_make_engine(a))
+    failed = False
     try:
-        rid = eng.add_request(ids, sp)
-    except ValueError as exc:
-        raise SystemExit(f"generation failed: {exc}")
-    first: Optional[float] = None
-    seen = 0
-    out = None
-    while eng.has_unfinished():
-        finished = eng.step()
-        toks = eng.scheduler.tokens_of(rid) if not finished else finished[0].prompt_token_ids + finished[0].token_ids
-        new = toks[len(ids) + seen:]
-        if new and first is None:
-            first = time.perf_counter() - t0
-        for t in new:
-            sys.stdout.write(f"{t} ")
-            sys.stdout.flush()
-        seen += len(new)
-        if finished:
-            out = finished[0]
-    total = time.perf_counter() - t0
-    if out is None or out.finish_reason == "error":
-        raise SystemExit(f"generation failed: {out.error if out else 'engine stopped'}")
-    if a.print_ids:
-        print(f"\noutput_ids: {out.token_ids}", file=sys.stderr)
-    ttft = first if first is not None else total
-    n = len(out.token_ids)
-    tps = max(n - 1, 0) / max(total - ttft, 1e-9)
-    # the reference's summary line (src/main.rs:1044-1050)
-    print(f"\n[{out.finish_reason.capitalize()}] prompt {len(ids)} tok, output {n} tok, ttft {ttft:.3f}s, decode {tps:.1f} tok/s",
-          file=sys.stderr)
-    return 0
+        t0 = time.perf_counter()
+        streams = []
+        for i, ids in enumerate(prompts):
+            # a seeded batch gives every prompt a seed of its own, so that equal prompts differ
+            seed = None if a.seed is None else a.seed + i
+            sp = SamplingParams(temperature=a.temperature, top_p=a.top_p, top_k=a.top_k, min_p=a.min_p,
+                                max_tokens=a.max_tokens, seed=seed, ignore_eos=a.ignore_eos)
+            streams.append(handle.submit(ids, sp))
+        for i, (ids, stream) in enumerate(zip(prompts, streams)):
+            first: Optional[float] = None
+            out_ids: List[int] = []
+            tag = f"[{i}] " if len(prompts) > 1 else ""
+            for ev in stream:
+                if isinstance(ev, Token):
+                    if first is None:
+                        first = time.perf_counter() - t0
+                    out_ids.append(ev.token_id)
+                    if len(prompts) == 1:            # one prompt: its tokens as they come
+                        sys.stdout.write(f"{ev.token_id} ")
+                        sys.stdout.flush()
+                elif isinstance(ev, Error):
+                    print(f"\n{tag}generation failed: {ev.message}", file=sys.stderr)
+                    failed = True
+                elif isinstance(ev, Done):
+                    total = time.perf_counter() - t0
+                    if len(prompts) > 1:
+                        print(f"{tag}" + " ".join(str(t) for t in out_ids))
+                    if a.print_ids:
+                        print(f"\n{tag}output_ids: {out_ids}", file=sys.stderr)
+                    ttft = first if first is not None else total
+                    n = ev.usage["completion_tokens"]
+                    tps = max(n - 1, 0) / max(total - ttft, 1e-9)
+                    # the reference's summary line (src/main.rs:1044-1050)
+                    print(f"\n{tag}[{ev.reason.capitalize()}] prompt {ev.usage['prompt_tokens']} tok, output {n} tok, "
+                          f"ttft {ttft:.3f}s, decode {tps:.1f} tok/s", file=sys.stderr)
+    finally:
+        handle.shutdown()
+    return 1 if failed else 0
 
 
 def cmd_tiny_model(a) -> int:
@@ -137,9 +147,10 @@ def main(argv: Optional[List[str]] = None) -> int:
     ap = argparse.ArgumentParser(prog="carbon_engine_b200", description=__doc__,
                                  formatter_class=argparse.RawDescriptionHelpFormatter)
     sub = ap.add_subparsers(dest="cmd", required=True)
-    g = sub.add_parser("generate", help="generate tokens for one prompt")
+    g = sub.add_parser("generate", help="generate tokens for a prompt (or, --prompt-ids given several times, a batch)")
     _engine_flags(g)
-    g.add_argument("--prompt-ids", default=None, help="comma separated prompt token ids")
+    g.add_argument("--prompt-ids", action="append", default=None,
+                   help="comma separated prompt token ids; may be given more than once: the prompts run as one batch")
     g.add_argument("--print-ids", action="store_true", help="print the generated ids once more at the end")
     g.add_argument("--max-tokens", type=int, default=128)
     g.add_argument("--temperature", type=float, default=0.0)

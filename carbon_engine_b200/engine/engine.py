@@ -121,6 +121,8 @@ class Engine:
         self._next_id = 0
         self.d2h_bytes_last = 0
         self._last_error: Optional[str] = None
+        #: (request, token, its log-probability entry or None) of every token the last step sampled
+        self.last_sampled: List[tuple] = []
         # while a decode step runs, the next one is laid out on the host on the guess that the same requests go on
         self.host_lookahead = bool(host_lookahead)
 
@@ -143,10 +145,11 @@ class Engine:
         return max(1, (int(kv_tokens) + self.page_size - 1) // self.page_size)
 
     # -- requests -------------------------------------------------------------------------------
-    def add_request(self, prompt_token_ids: Sequence[int], params: Optional[SamplingParams] = None) -> int:
+    def add_request(self, prompt_token_ids: Sequence[int], params: Optional[SamplingParams] = None,
+                    request_id: Optional[int] = None) -> int:
         params = params or SamplingParams()
-        rid = self._next_id
-        self._next_id += 1
+        rid = self._next_id if request_id is None else int(request_id)
+        self._next_id = max(self._next_id, rid) + 1
         self.scheduler.submit(rid, prompt_token_ids, params.max_tokens, params.ignore_eos, params.stop_token_ids)
         self._live[rid] = _Live(params, params.seed if params.seed is not None else fresh_seed(),
                                 list(prompt_token_ids))
@@ -162,6 +165,7 @@ class Engine:
         """Run one scheduler step; returns the requests that finished in it."""
         plan = self.scheduler.plan()
         self._last_error = None
+        self.last_sampled = []
         if plan:
             entries = []
             for e in plan:
@@ -197,6 +201,8 @@ class Engine:
                         lives[i].logprobs.append(top_logprobs(base[j], tokens[i], lives[i].params.logprobs))
                 self.runner.check_status()
                 self.scheduler.commit(tokens)
+                self.last_sampled = [(r, t, (self._live[r].logprobs[-1] if self._live[r].params.logprobs > 0 else None))
+                                     for r, t in zip(sampled_ids, tokens)]
             except (StepError, KernelError, CacheError, torch.OutOfMemoryError) as exc:
                 # the step failed on the device or for want of memory: its requests end with an error and
                 # give their pages back, the others go on (src/scheduler.rs:1436-1463).  Anything else is

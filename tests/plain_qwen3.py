@@ -59,7 +59,7 @@ def read_model(model_dir: str, dtype=torch.float64):
 # ---- one function per part ----------------------------------------------------------------------
 def embedding(table: torch.Tensor, tokens: List[int]) -> torch.Tensor:
     """x0[t] = E[token[t]], no scaling (src/model/mod.rs:781-784)."""
-    return table[torch.tensor(tokens, dtype=torch.long)]
+    return table[torch.tensor(tokens, dtype=torch.long, device=table.device)]
 
 
 def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
@@ -112,7 +112,7 @@ def rope_tables(positions: torch.Tensor, rotary_dim: int, theta: float, scaling:
     """inv_freq[i] = theta^(-2i/rd), rescaled if the config says so; angle = pos * inv_freq[i]; cos and sin
     times the scheme's attention factor (src/model/layers.rs:169-173, 237-251)."""
     inv_freq, att = scaled_inv_freq(rotary_dim, theta, scaling, max_position_embeddings)
-    ang = positions.to(torch.float64)[:, None] * inv_freq[None, :]
+    ang = positions.to(torch.float64)[:, None] * inv_freq.to(positions.device)[None, :]
     return ang.cos() * att, ang.sin() * att
 
 
@@ -134,7 +134,7 @@ def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: f
     nkv = k.shape[1]
     g = nh // nkv
     out = torch.empty_like(q)
-    idx = torch.arange(T)
+    idx = torch.arange(T, device=q.device)
     allowed = idx[None, :] <= idx[:, None]
     if window > 0:
         allowed &= idx[None, :] > idx[:, None] - window
@@ -194,9 +194,10 @@ def lm_head(x: torch.Tensor, w: Dict[str, torch.Tensor], cfg: dict) -> torch.Ten
 
 
 def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: List[int]) -> torch.Tensor:
-    """Logits [T, vocab] of one whole sequence."""
+    """Logits [T, vocab] of one whole sequence (computed where the weights live: the tests of real layer
+    sizes keep them on the GPU, still in float64 and still with these functions only)."""
     x = embedding(w["model.embed_tokens.weight"], tokens)
-    positions = torch.arange(len(tokens))
+    positions = torch.arange(len(tokens), device=x.device)
     for layer in range(cfg["num_hidden_layers"]):
         x = decoder_layer(x, w, layer, cfg, positions)
     return lm_head(x, w, cfg)

@@ -11,7 +11,10 @@ scheduler, the step function and the sampler): every step copies its inputs from
 to the device and reads the sampled tokens back to the host.  ``prefill`` is one 2,048-token prompt
 in one step; ``roofline`` compares the bytes a decode step has to read (every weight once, and the
 cache of the live requests) with the measured copy bandwidth; ``points`` holds decode at batch 1 and
-64.  Weights are random (seeded), token ids are uniform-random (seeded): no dataset is involved.
+64 and the main batch without the pick; ``check`` (outside every timed region) says whether a short greedy
+continuation by the timed engine is what a float32 engine of the same weights picks, ties apart.
+``--profile`` prints a per-kernel table instead.
+Weights are random (seeded), token ids are uniform-random (seeded): no dataset is involved.
 The weights alone (over 15 GB) exceed the L2 cache many times over, so no flush is needed between
 steps.  Runs on one GPU only.
 """
@@ -159,6 +162,11 @@ def main() -> int:
     ap.add_argument("--no-graphs", action="store_true")
     ap.add_argument("--prefill-only", action="store_true",
                     help="run only the 2,048-token prefill (for profiling) and print its time")
+    ap.add_argument("--profile", action="store_true",
+                    help="instead of the contract's line: time every kernel of a decode step and of a 2,048-token prefill "
+                         "with CUDA events (eager, kernels one after another) and print a table per kernel: launches, "
+                         "microseconds, share, GB/s, TFLOP/s and the fraction of the measured peak")
+    ap.add_argument("--no-check", action="store_true", help="skip the comparison of a short greedy continuation with float32")
     ap.add_argument("--workload", default="decode", choices=["decode", "mixed-14b", "batch16-32b"],
                     help="decode: the contract's line (default).  mixed-14b: 32 requests with prompts of 128 to 3,072 tokens at "
                          "Qwen3-14B sizes, prompts cut under a 2,048-token step budget beside the decoding requests, 128 new "
@@ -188,6 +196,20 @@ def main() -> int:
         pf = h.prefill(2048, 2, 2)
         print(json.dumps({"prefill_ms": round(pf["ms"], 3), "layers": args.layers}))
         return 0
+    if args.profile:
+        prof = h.profile(args.batch, 2048, pk["hbm_gbs"], pk["bf16_tflops"])
+        for part in ("decode", "prefill"):
+            p = prof[part]
+            what = f"decode step, batch {p['batch']}, {args.context}-token contexts" if part == "decode" else f"prefill of {p['tokens']} tokens"
+            print(f"\n{what}, {args.layers} layers: {p['us']:.0f} us with kernels one after another (peaks {pk['source']}: "
+                  f"{pk['hbm_gbs']:.0f} GB/s, {pk['bf16_tflops']:.0f} TFLOP/s)", file=sys.stderr)
+            print(f"{'kernel':58s} {'launches':>8s} {'us':>10s} {'share':>6s} {'GB/s':>8s} {'TFLOP/s':>8s} {'of peak':>8s}", file=sys.stderr)
+            for r in p["kernels"]:
+                frac = "" if r["frac_of_peak"] is None else f"{r['frac_of_peak']:.2f}"
+                print(f"{r['kernel'][:58]:58s} {r['launches']:8d} {r['us']:10.1f} {r['share']:6.3f} {r['gb_s']:8.0f} {r['tflop_s']:8.0f} {frac:>8s}",
+                      file=sys.stderr)
+        print(json.dumps({"profile": prof, "layers": args.layers, "peaks": pk["source"]}))
+        return 0
     clocks = ClockSampler()
     clocks.start()
     time.sleep(0.3)
@@ -205,7 +227,10 @@ def main() -> int:
         for b in (1, 64):
             r = h.decode(b, min(args.steps, 32), 3)
             points[f"decode_b{b}"] = round(r["tokens_per_s"], 1)
+        # the same step without the greedy pick at its end (the logits are the step's result)
+        points[f"decode_b{args.batch}_without_pick"] = round(h.decode(args.batch, min(args.steps, 32), 3, pick=False)["tokens_per_s"], 1)
     clocks.stop()
+    check = None if args.no_check else h.check_against_float32()
 
     ms = main_run["ms_per_step"]
     need = decode_bytes(cfg, args.layers, args.batch, args.context + args.warmup + args.steps // 2)
@@ -231,8 +256,10 @@ def main() -> int:
     if prefill is not None:
         out["prefill"] = prefill
         out["points"] = points
+    if check is not None:
+        out["check"] = check
     print(json.dumps(out))
-    return 0
+    return 0 if check is None or check["ok"] else 1
 
 
 if __name__ == "__main__":

@@ -21,6 +21,7 @@ class BenchHarness:
         raw = dict(cfg, architectures=["Qwen3ForCausalLM"], model_type="qwen3")
         self.config = Qwen3Config.from_dict(raw)
         self.context, self.new_tokens, self.page_size, self.max_batch = context, new_tokens, page_size, max_batch
+        self.seed = seed
         per_seq = (context + new_tokens + page_size - 1) // page_size * page_size
         self.max_seq_len = max(4096, per_seq)
         self.engine = Engine(config=self.config, dtype="bfloat16", dummy_weight=True, seed=seed,
@@ -50,7 +51,9 @@ class BenchHarness:
             ids.append(rid)
         return ids
 
-    def decode(self, batch: int, steps: int, warmup: int) -> Dict:
+    def decode(self, batch: int, steps: int, warmup: int, pick: bool = True) -> Dict:
+        """``steps`` decode steps of ``batch`` sequences timed on the device; ``pick``: each step ends with the
+        greedy pick of every sequence's next token (False: the step ends with the logits)."""
         runner = self.engine.runner
         ids = self._open_with_context(batch)
         out = torch.empty(batch, dtype=torch.int32, device=self.engine.device)
@@ -58,7 +61,8 @@ class BenchHarness:
 
         def one(i):
             logits = runner.step([StepEntry(r, [toks[i][j]], [0]) for j, r in enumerate(ids)])
-            ops.argmax(logits, out)
+            if pick:
+                ops.argmax(logits, out)
 
         for i in range(warmup):
             one(i)
@@ -124,6 +128,80 @@ class BenchHarness:
         prompt, gen = int(sum(prompt_lens)), len(prompt_lens) * new_tokens
         return {"seconds": dt, "steps": steps, "prompt_tokens": prompt, "generated_tokens": gen,
                 "tokens_per_s": (prompt + gen) / dt, "generated_per_s": gen / dt, "launches": ops.launch_count() - l0}
+
+    def profile(self, batch: int, prompt_tokens: int, hbm_gbs: float, tflops: float, repeats: int = 3) -> Dict:
+        """Per-kernel times of a decode step at ``batch`` and of a one-prompt prefill, from CUDA events around
+        every launch (eager, dependent launches off: kernels run one after another, so the sum is longer than a
+        served step; the SHARES and the per-kernel rates are what this is for)."""
+        runner = self.engine.runner
+        graphs, runner.graphs_enabled = runner.graphs_enabled, False
+        try:
+            ids = self._open_with_context(batch)
+            out = torch.empty(batch, dtype=torch.int32, device=self.engine.device)
+
+            def one():
+                logits = runner.step([StepEntry(r, [t], [0]) for r, t in zip(ids, self._tokens(batch))])
+                ops.argmax(logits, out)
+            for _ in range(3):
+                one()
+            with ops.KernelProfile() as prof:
+                for _ in range(repeats):
+                    one()
+            decode_rows, decode_us = prof.table(hbm_gbs, tflops, repeats)
+            for r in ids:
+                runner.close_request(r)
+            rid = self._next
+            self._next += 1
+            prefill_rows, prefill_us = [], 0.0
+            for i in range(2):
+                runner.open_request(rid + i)
+                toks = self._tokens(prompt_tokens)
+                if i == 0:
+                    runner.step([StepEntry(rid + i, toks, [prompt_tokens - 1])])
+                else:
+                    with ops.KernelProfile() as prof:
+                        runner.step([StepEntry(rid + i, toks, [prompt_tokens - 1])])
+                    prefill_rows, prefill_us = prof.table(hbm_gbs, tflops, 1)
+                runner.close_request(rid + i)
+            self._next += 2
+            runner.check_status()
+        finally:
+            runner.graphs_enabled = graphs
+        return {"decode": {"batch": batch, "us": round(decode_us, 1), "kernels": decode_rows},
+                "prefill": {"tokens": prompt_tokens, "us": round(prefill_us, 1), "kernels": prefill_rows}}
+
+    def check_against_float32(self, prompt_tokens: int = 192, new_tokens: int = 8, seed: int = 3) -> Dict:
+        """Outside any timed region: a short greedy continuation by this (bfloat16) engine, and the same
+        tokens fed to a float32 engine of the same sizes and weights.  Every token this engine picked must be
+        the float32 logits' first choice or lie within the tie margin of it (two logits closer than 4e-2 of
+        the row's largest count as a tie, as in the tests); the largest relative difference between the two
+        engines' logits rows is reported too."""
+        eng = self.engine
+        prompt = np.random.default_rng(seed).integers(0, self.config.vocab_size, size=prompt_tokens).tolist()
+        out = eng.generate([prompt], SamplingParams(max_tokens=new_tokens, ignore_eos=True))[0]
+        # this engine's own logits at the same places (teacher-forced, one step)
+        seq = prompt + out.token_ids[:-1]
+        places = list(range(prompt_tokens - 1, len(seq)))
+        rid = self._next
+        self._next += 1
+        eng.runner.open_request(rid)
+        mine = eng.runner.step([StepEntry(rid, seq, places)]).clone()
+        eng.runner.close_request(rid)
+        ref = Engine(config=self.config, dtype="float32", dummy_weight=True, seed=self.seed, kv_tokens=1024,
+                     page_size=self.page_size, max_seq_len=1024, max_running_requests=2, max_prefill_tokens=512)
+        ref.runner.open_request(0)
+        theirs = ref.runner.step([StepEntry(0, seq, places)])
+        ref.runner.check_status()
+        big = theirs.abs().amax(dim=1)
+        err = float(((mine - theirs).abs().amax(dim=1) / big).max())
+        picked = torch.tensor(out.token_ids, device=theirs.device)
+        gap = (theirs.max(dim=1).values - theirs.gather(1, picked[:, None])[:, 0]) / big
+        first = int((theirs.argmax(dim=1) == picked).sum())
+        ties = int(((gap > 0) & (gap <= 4e-2)).sum())
+        del ref
+        torch.cuda.empty_cache()
+        return {"prompt_tokens": prompt_tokens, "new_tokens": new_tokens, "first_choice_of_float32": first, "ties": ties,
+                "ok": first + ties == new_tokens, "max_logit_diff_rel": round(err, 5)}
 
     def prefill(self, tokens: int, reps: int, warmup: int) -> Dict:
         runner = self.engine.runner

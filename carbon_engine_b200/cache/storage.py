@@ -2,7 +2,7 @@
 per-request state, and the device copies of the block tables.
 
 The model's cache layout (one entry per cache of its layer schedule) decides what is allocated.
-Paged caches with the same window share a *group*: one pool of page ids and one block table, so a
+Paged caches with the same window and page size share a *group*: one pool of page ids and one block table, so a
 page id addresses the same page in every cache of the group, as one slot id does in every layer
 of the reference (src/model/mod.rs:443-461).  Each cache still has K and V tensors of its own,
 shaped [num_pages, kv_heads, page_size, head_dim].  State caches are tensors
@@ -39,26 +39,30 @@ class CacheStorage:
                  max_requests: int, max_seq_len: int, window_pages: Optional[int] = None, poison: bool = False):
         self.device, self.dtype, self.page_size = device, dtype, int(page_size)
         self.max_requests = int(max_requests)
-        self.max_pages_per_request = (int(max_seq_len) + page_size - 1) // page_size
         layout = model.cache_layout()
-        group_of_window: Dict[int, int] = {}
+        # the block tables of all groups have one width: what the smallest page size needs
+        smallest = min([page_size] + [s.page_size for _, s in layout if isinstance(s, PagedCacheSpec) and s.page_size])
+        self.max_pages_per_request = (int(max_seq_len) + smallest - 1) // smallest
+        group_of: Dict[tuple, int] = {}
         groups: List[GroupSpec] = []
         self._entries: Dict[int, LayerCacheView] = {}
         for cache_id, spec in layout:
             if isinstance(spec, PagedCacheSpec):
-                if spec.window not in group_of_window:
-                    group_of_window[spec.window] = len(groups)
+                ps = int(spec.page_size or page_size)
+                if (spec.window, ps) not in group_of:
+                    group_of[(spec.window, ps)] = len(groups)
                     n = num_pages if spec.window == 0 or window_pages is None else window_pages
-                    groups.append(GroupSpec(page_size, int(n), int(spec.window)))
-                g = group_of_window[spec.window]
-                shape = (groups[g].num_pages, spec.kv_heads, page_size, spec.head_dim)
+                    # ``num_pages`` counts pages of the engine's size: a group with other pages holds as many tokens
+                    groups.append(GroupSpec(ps, max(1, int(n) * int(page_size) // ps), int(spec.window)))
+                g = group_of[(spec.window, ps)]
+                shape = (groups[g].num_pages, spec.kv_heads, ps, spec.head_dim)
                 k = torch.empty(shape, dtype=dtype, device=device)
                 v = torch.empty(shape, dtype=dtype, device=device)
                 if poison:          # stale reads then show up as NaN in the logits
                     k.fill_(float("nan")); v.fill_(float("nan"))
                 else:
                     k.zero_(); v.zero_()
-                self._entries[cache_id] = LayerCacheView("paged", g, page_size, k, v)
+                self._entries[cache_id] = LayerCacheView("paged", g, ps, k, v)
             elif isinstance(spec, StateCacheSpec):
                 st = torch.zeros((max_requests, *spec.shape), dtype=spec.dtype or dtype, device=device)
                 self._entries[cache_id] = LayerCacheView("state", state=st)
@@ -93,7 +97,8 @@ class CacheStorage:
 
     def pending_table_updates(self, group: int, slot: int, new_len: int):
         """(flat indices, page ids) of the table entries of ``slot`` the device does not have yet."""
-        hi = (new_len + self.page_size - 1) // self.page_size
+        ps = self.groups[group].page_size
+        hi = (new_len + ps - 1) // ps
         lo = int(self._synced[group, slot])
         if hi <= lo:
             return None
@@ -101,6 +106,10 @@ class CacheStorage:
         idx = np.arange(lo, hi, dtype=np.int32) + slot * self.max_pages_per_request
         self._synced[group, slot] = hi
         return idx, row
+
+    def state_bytes(self) -> int:
+        """Bytes of the fixed-size per-request state tensors (all slots)."""
+        return sum(e.state.numel() * e.state.element_size() for e in self._entries.values() if e.kind == "state")
 
     def zero_state(self, slot: int) -> None:
         """Reset the fixed-size state of a slot for a new request."""

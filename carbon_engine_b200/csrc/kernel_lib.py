@@ -20,14 +20,15 @@ _SIGNATURES = {
     "ce_kernel_counts": (_i, [ctypes.c_char_p, _i]),
     "ce_kernel_counts_reset": (None, []),
     "ce_last_kernel": (ctypes.c_char_p, []),
+    "ce_set_pdl": (None, [_i]),
     # table, dtype, tokens, x, T, H, V, status, stream
     "ce_embed": (_i, [_p, _i, _p, _p, _i, _i, _i, _p, _p]),
     # x, w, out, out_dtype, rows, R, H, eps, stream
     "ce_rmsnorm": (_i, [_p, _p, _p, _i, _p, _i, _i, _f, _p]),
     # qkv, k_pool, v_pool, dtype, qw, kw, cos, sin, positions, seq_of_token, seq_slot, block_table, status,
-    # T, nh, nkv, d, rd, page_size, max_pages, num_pages, max_pos, write_kv, eps, stream
+    # T, nh, nkv, d, rd, page_size, max_pages, num_pages, max_pos, write_kv, eps, pairing, stream
     "ce_qk_rope_kvwrite": (_i, [_p, _p, _p, _i, _p, _p, _p, _p, _p, _p, _p, _p, _p,
-                                _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _p]),
+                                _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _p]),
     "ce_add_residual": (_i, [_p, _p, _i, _ll, _p]),
     "ce_swiglu": (_i, [_p, _p, _i, _i, _i, _p]),
     # q, k_pool, v_pool, out, dtype, positions, seq_of_token, seq_slot, block_table, status,

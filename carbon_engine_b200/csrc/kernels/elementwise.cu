@@ -150,7 +150,8 @@ extern "C" int ce_rmsnorm(const float* x, const float* w, void* out, int out_dty
 //
 // Order follows the reference: norm over the head (weight shared by all heads) BEFORE the
 // rotation (src/model/attention.rs:884-889); rotate-half pairing (i, i + rd/2)
-// (src/model/layers.rs:159, spelled out in src/kernels/qsa.cu:107-116); K is stored after norm and
+// (src/model/layers.rs:159, spelled out in src/kernels/qsa.cu:107-116), or, as a parameter for other
+// position encodings, the interleaved pairing (2i, 2i + 1); K is stored after norm and
 // rotation, V as projected (src/model/attention.rs:890).
 // ---------------------------------------------------------------------------------------------
 struct QkRopeArgs {
@@ -168,6 +169,7 @@ struct QkRopeArgs {
     int* status;
     int T, nh, nkv, d, rd, page_size, max_pages, num_pages, max_pos, write_kv;
     float eps;
+    int pairing;             // partners of a rotation: 0 = (i, i + rd/2) ("rotate-half"), 1 = (2i, 2i + 1) (interleaved)
 };
 
 template <typename T>
@@ -218,7 +220,12 @@ __global__ void qk_rope_kvwrite_kernel(QkRopeArgs a) {
         int half = a.rd / 2;
         const float* c = a.cos_table + (size_t)pos * half;
         const float* s = a.sin_table + (size_t)pos * half;
-        if (j < half)
+        if (a.pairing == 1) {           // interleaved: elements 2f and 2f + 1 turn by angle f
+            if (j < a.rd) {
+                int f = j >> 1;
+                v = (j & 1) ? vals[j] * c[f] + vals[j - 1] * s[f] : vals[j] * c[f] - vals[j + 1] * s[f];
+            }
+        } else if (j < half)
             v = vals[j] * c[j] - vals[j + half] * s[j];
         else if (j < a.rd)
             v = vals[j] * c[j - half] + vals[j - half] * s[j - half];
@@ -395,7 +402,7 @@ __global__ void __launch_bounds__(128) qk_rope_kvwrite_warp_kernel(QkRopeArgs a,
 template <typename T>
 static bool launch_rope_warp(const QkRopeArgs& a, cudaStream_t stream) {
     int heads_per_token = a.nh + 2 * a.nkv;
-    if (a.d % 64 || a.d > 256 || (a.cos_table && a.rd != a.d)) return false;
+    if (a.d % 64 || a.d > 256 || (a.cos_table && (a.rd != a.d || a.pairing != 0))) return false;
     // few tokens: a warp per head; many: four warps share a token's heads
     int hpw = a.T >= 256 ? (heads_per_token + 3) / 4 : 1;
     long long warps = (long long)a.T * ((heads_per_token + hpw - 1) / hpw);
@@ -415,15 +422,16 @@ extern "C" int ce_qk_rope_kvwrite(void* qkv, void* k_pool, void* v_pool, int dty
                                   const int* positions, const int* seq_of_token, const int* seq_slot,
                                   const int* block_table, int* status, int T, int nh, int nkv, int d, int rd,
                                   int page_size, int max_pages, int num_pages, int max_pos, int write_kv, float eps,
-                                  cudaStream_t stream) {
+                                  int pairing, cudaStream_t stream) {
     if (T == 0) return CE_OK;
     if (d <= 0 || d > 1024) return ce_fail(CE_ERR_SIZE, "ce_qk_rope_kvwrite: head_dim %d not in 1..1024", d);
     if (rd < 0 || rd > d || (rd & 1)) return ce_fail(CE_ERR_SIZE, "ce_qk_rope_kvwrite: rotary_dim %d must be even and <= head_dim %d", rd, d);
+    if (pairing != 0 && pairing != 1) return ce_fail(CE_ERR_ARG, "ce_qk_rope_kvwrite: pairing %d (0: halves, 1: interleaved)", pairing);
     if (!qkv || !positions || !status) return ce_fail(CE_ERR_ARG, "ce_qk_rope_kvwrite: null pointer");
     if (write_kv && (!k_pool || !v_pool || !seq_of_token || !seq_slot || !block_table))
         return ce_fail(CE_ERR_ARG, "ce_qk_rope_kvwrite: cache pointers missing");
     QkRopeArgs a{qkv, k_pool, v_pool, q_weight, k_weight, cos_table, sin_table, positions, seq_of_token, seq_slot,
-                 block_table, status, T, nh, nkv, d, rd, page_size, max_pages, num_pages, max_pos, write_kv, eps};
+                 block_table, status, T, nh, nkv, d, rd, page_size, max_pages, num_pages, max_pos, write_kv, eps, pairing};
     int threads = (d + 31) / 32 * 32;
     dim3 grid(T, nh + 2 * nkv);
     size_t smem = (d + 32) * sizeof(float);

@@ -133,14 +133,36 @@ class Engine:
         return sum(2 * s.kv_heads * s.head_dim * el for _, s in self.model.cache_layout()
                    if isinstance(s, PagedCacheSpec))
 
+    def _state_bytes(self) -> int:
+        """Bytes of the fixed-size per-request state of every slot (src/model/mod.rs:129-145 counts them too)."""
+        from ..parts.base import StateCacheSpec
+        el = 2 if self.dtype == torch.bfloat16 else 4
+        total = 0
+        for _, s in self.model.cache_layout():
+            if isinstance(s, StateCacheSpec):
+                n = 1
+                for dim in s.shape:
+                    n *= int(dim)
+                total += n * (torch.empty((), dtype=s.dtype).element_size() if s.dtype is not None else el)
+        return total * self.max_running
+
+    def _workspace_bytes(self) -> int:
+        """What has to stay free beside the cache: the activations of the largest step (a quarter more, for the
+        allocator's rounding), the split-K and split-KV scratch, and a margin for the CUDA context's own needs."""
+        from .. import ops_tensor
+        el = 2 if self.dtype == torch.bfloat16 else 4
+        step = self.model.step_bytes(self.max_step_tokens, el, rows=self.max_running)
+        return step + step // 4 + 4 * ops_tensor.GEMM_SCRATCH_FLOATS + (256 << 20)
+
     def _size_cache(self, kv_tokens: Optional[int], memory_ratio: float) -> int:
-        """Pages of the cache: ``kv_tokens`` if given, else what ``memory_ratio`` of the free memory
-        holds, at least 1024 tokens and at most eight contexts (src/engine.rs:317-329)."""
+        """Pages of the cache: ``kv_tokens`` if given, else what ``memory_ratio`` of the free memory holds
+        beside the per-request state and the step's workspace, at least 1024 tokens and at most eight
+        contexts (src/engine.rs:317-329, src/model/mod.rs:406-439)."""
         if kv_tokens is None:
             free, _ = torch.cuda.mem_get_info(self.device)
             per_token = max(self._bytes_per_token(), 1)
-            reserve = 2 << 30           # activations of the largest step
-            kv_tokens = int(max(free * memory_ratio - reserve, 0) // per_token)
+            room = free * memory_ratio - self._workspace_bytes() - self._state_bytes()
+            kv_tokens = int(max(room, 0) // per_token)
             kv_tokens = max(1024, min(kv_tokens, 8 * self.max_seq_len))
         return max(1, (int(kv_tokens) + self.page_size - 1) // self.page_size)
 

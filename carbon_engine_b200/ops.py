@@ -15,6 +15,7 @@ from .csrc.kernel_lib import KernelError, kernels
 
 F32, BF16 = 0, 1
 GEMM_STORE, GEMM_STORE_F32, GEMM_ACCUM_F32, GEMM_SWIGLU = 0, 1, 2, 3
+ROPE_PAIRINGS = {"half": 0, "interleaved": 1}
 
 
 def dtype_code(dt: torch.dtype) -> int:
@@ -55,11 +56,81 @@ def add_launches(n: int) -> None:
     _launches += n
 
 
+class KernelProfile:
+    """Times every launch that goes through this module with CUDA events, one after each launch on the
+    launching stream, while dependent launches are switched off so that kernels do not overlap: the time
+    between two events is then the time of the kernel between them (plus its launch gap).  ``work`` that a
+    caller notes before a launch (bytes it has to move, floating-point operations) is kept with it, so that
+    :meth:`table` can set each kernel against the memory or arithmetic peak.  For measurement only: a
+    profiled step is slower than a served one."""
+
+    def __init__(self):
+        self.records = []            # (kernel name, event after it, bytes, flops)
+        self._work = (0, 0)
+        self._start = None
+
+    def __enter__(self):
+        global _profile
+        import torch
+        kernels().ce_set_pdl(0)
+        torch.cuda.synchronize()
+        self._start = torch.cuda.Event(enable_timing=True)
+        self._start.record()
+        _profile = self
+        return self
+
+    def __exit__(self, *exc):
+        global _profile
+        import torch
+        _profile = None
+        torch.cuda.synchronize()
+        kernels().ce_set_pdl(1)
+
+    def note_work(self, nbytes: int, flops: int) -> None:
+        self._work = (int(nbytes), int(flops))
+
+    def _launched(self, n: int) -> None:
+        import torch
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record()
+        name = kernels().ce_last_kernel().decode() or "?"
+        self.records.append((name if n == 1 else f"{name} (+{n - 1})", ev, *self._work))
+        self._work = (0, 0)
+
+    def table(self, hbm_gbs: float, tflops: float, repeats: int = 1):
+        """Rows (name, launches, microseconds per repeat, share, GB/s, TFLOP/s, fraction of the nearer
+        peak) by kernel name, slowest first."""
+        agg, prev, total = {}, self._start, 0.0
+        for name, ev, nbytes, flops in self.records:
+            us = prev.elapsed_time(ev) * 1e3
+            prev = ev
+            a = agg.setdefault(name, [0, 0.0, 0, 0])
+            a[0] += 1; a[1] += us; a[2] += nbytes; a[3] += flops
+            total += us
+        rows = []
+        for name, (n, us, nbytes, flops) in sorted(agg.items(), key=lambda kv: -kv[1][1]):
+            gbs = nbytes / us / 1e3 if us > 0 else 0.0
+            tf = flops / us / 1e6 if us > 0 else 0.0
+            frac = max(gbs / hbm_gbs, tf / tflops) if (nbytes or flops) else None
+            rows.append({"kernel": name, "launches": n // repeats, "us": round(us / repeats, 1), "share": round(us / total, 4),
+                         "gb_s": round(gbs, 1), "tflop_s": round(tf, 1), "frac_of_peak": None if frac is None else round(frac, 3)})
+        return rows, total / repeats
+
+
+_profile: Optional[KernelProfile] = None
+
+
+def profiling() -> Optional[KernelProfile]:
+    return _profile
+
+
 def _ok(code: int, n: int = 1) -> None:
     global _launches
     if code != 0:
         raise KernelError(kernels().ce_last_error().decode())
     _launches += n
+    if _profile is not None:
+        _profile._launched(n)
 
 
 def kernel_counts() -> dict:
@@ -104,8 +175,12 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float
 
 def qk_rope_kvwrite(qkv, k_pool, v_pool, q_weight, k_weight, cos, sin, positions, seq_of_token, seq_slot,
                     block_table, status, nh: int, nkv: int, d: int, rotary_dim: int, page_size: int,
-                    eps: float, write_kv: bool = True) -> None:
+                    eps: float, write_kv: bool = True, pairing: str = "half") -> None:
+    """Per-head q/k RMSNorm, rotation, and the write of K and V into the pages.  ``pairing``: which elements
+    of a head turn together, "half" (i with i + rotary_dim/2) or "interleaved" (2i with 2i + 1)."""
     _need(qkv, "qkv")
+    if pairing not in ROPE_PAIRINGS:
+        raise KernelError(f"qk_rope_kvwrite: unknown pairing '{pairing}' (half, interleaved)")
     T = qkv.shape[0]
     if qkv.shape[1] != (nh + 2 * nkv) * d:
         raise KernelError(f"qk_rope_kvwrite: qkv width {qkv.shape[1]} != (nh + 2 nkv) d = {(nh + 2 * nkv) * d}")
@@ -125,7 +200,7 @@ def qk_rope_kvwrite(qkv, k_pool, v_pool, q_weight, k_weight, cos, sin, positions
         _ptr(qkv), _ptr(k_pool), _ptr(v_pool), dtype_code(qkv.dtype), _ptr(q_weight), _ptr(k_weight), _ptr(cos),
         _ptr(sin), _ptr(positions), _ptr(seq_of_token), _ptr(seq_slot), _ptr(block_table), _ptr(status),
         T, nh, nkv, d, rotary_dim, page_size, max_pages, num_pages, max_pos, 1 if write_kv else 0, float(eps),
-        _stream()))
+        ROPE_PAIRINGS[pairing], _stream()))
 
 
 def add_residual(x: torch.Tensor, delta: torch.Tensor) -> None:

@@ -50,12 +50,13 @@ class PagedAttention(Mixer):
 
     def __init__(self, hidden: int, heads: int, kv_heads: int, head_dim: int, prefix: str,
                  position: Optional[PositionEncoding] = None, qk_norm_eps: Optional[float] = None,
-                 window: int = 0, scale: Optional[float] = None):
+                 window: int = 0, scale: Optional[float] = None, page_size: Optional[int] = None):
         if heads % kv_heads:
             raise ValueError(f"{heads} heads are not a multiple of {kv_heads} kv heads")
         self.hidden, self.heads, self.kv_heads, self.head_dim = hidden, heads, kv_heads, head_dim
         self.prefix, self.position, self.qk_norm_eps, self.window = prefix, position, qk_norm_eps, int(window)
         self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(head_dim)
+        self.page_size = page_size          # None: the engine's; else this layer's cache has pages of its own size
         self.qkv = Linear(hidden, [heads * head_dim, kv_heads * head_dim, kv_heads * head_dim],
                           [f"{prefix}.q_proj.weight", f"{prefix}.k_proj.weight", f"{prefix}.v_proj.weight"])
         self.o = Linear(heads * head_dim, [hidden], [f"{prefix}.o_proj.weight"])
@@ -83,7 +84,10 @@ class PagedAttention(Mixer):
             self.position.prepare(device)
 
     def cache_spec(self) -> PagedCacheSpec:
-        return PagedCacheSpec(self.kv_heads, self.head_dim, self.window)
+        return PagedCacheSpec(self.kv_heads, self.head_dim, self.window, self.page_size)
+
+    def step_bytes(self, tokens: int, element_size: int) -> int:
+        return tokens * (2 * self.heads + 2 * self.kv_heads) * self.head_dim * element_size      # q|k|v and the heads' outputs
 
     def step_sections(self, max_tokens: int, max_seqs: int):
         return [("paged_attention.tiles", 2 * (max_seqs + max_tokens // self.TILE + 1)),
@@ -127,13 +131,22 @@ class PagedAttention(Mixer):
         ops.qk_rope_kvwrite(qkv, cache.k_pool, cache.v_pool, self.q_norm_weight, self.k_norm_weight, cos, sin,
                             ctx.positions, ctx.seq_of_token, ctx.seq_slot, table, ctx.status, nh, nkv, d,
                             pos.rotary_dim if cos is not None else 0, cache.page_size,
-                            self.qk_norm_eps if self.qk_norm_eps is not None else 0.0, write_kv=cache.writes)
+                            self.qk_norm_eps if self.qk_norm_eps is not None else 0.0, write_kv=cache.writes,
+                            pairing=pos.pairing if pos is not None else "half")
         out = ctx.buffer((T, nh * d))
         self.attend(ctx, qkv, out, cache, table)
         self.o.forward(out, x, ACCUM)
 
     def attend(self, ctx, qkv: torch.Tensor, out: torch.Tensor, cache, table: torch.Tensor) -> None:
         nh, nkv, d = self.heads, self.kv_heads, self.head_dim
+        prof = ops.profiling()
+        if prof is not None:         # keys and values of every sequence once, queries and outputs; causal flops
+            el, keys, pairs = qkv.element_size(), 0, 0
+            for b in range(ctx.B):
+                n, before = ctx.h_q_start[b + 1] - ctx.h_q_start[b], ctx.h_ctx_before[b]
+                keys += before + n
+                pairs += n * before + n * (n + 1) // 2
+            prof.note_work((2 * keys * nkv * d + 2 * ctx.T * nh * d) * el, 4 * pairs * nh * d)
         if qkv.dtype == torch.bfloat16 and ctx.fast_attention:
             from .. import ops_tensor
             if ops_tensor.attention_bf16(ctx, ctx.plans[self.plan_key], qkv, out, cache, table, nh, nkv, d, self.window,

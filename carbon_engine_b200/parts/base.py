@@ -13,9 +13,14 @@ from typing import Any, Callable, List, Optional, Tuple, Union
 
 import torch
 
-#: how random weights are drawn for a tensor: N(0, 0.02) for "linear" and "embedding",
-#: 1 + N(0, 0.1) for "norm"
-INIT_KINDS = ("linear", "embedding", "norm")
+#: How random weights are drawn for a tensor, by the ``init`` of its :class:`TensorSpec`: kind -> (mean,
+#: standard deviation, kept in float32).  N(0, 0.02) for "linear" and "embedding", 1 + N(0, 0.1) for "norm"
+#: (norm weights are small and are stored in 32-bit).  A part with other needs registers a kind of its own.
+INIT_KINDS = {"linear": (0.0, 0.02, False), "embedding": (0.0, 0.02, False), "norm": (1.0, 0.1, True)}
+
+
+def register_init_kind(name: str, mean: float, std: float, keep_float32: bool = False) -> None:
+    INIT_KINDS[name] = (float(mean), float(std), bool(keep_float32))
 
 
 @dataclass(frozen=True)
@@ -27,10 +32,12 @@ class TensorSpec:
 
 @dataclass(frozen=True)
 class PagedCacheSpec:
-    """A mixer that stores per-token keys and values in pages.  window 0 keeps all keys."""
+    """A mixer that stores per-token keys and values in pages.  window 0 keeps all keys.  ``page_size``
+    None takes the engine's page size; caches with the same window and page size share their pages' ids."""
     kv_heads: int
     head_dim: int
     window: int = 0
+    page_size: Optional[int] = None
 
 
 @dataclass(frozen=True)
@@ -67,6 +74,11 @@ class Part:
         for c in self.children():
             out.extend(c.all_ignorable_tensors())
         return out
+
+    def step_bytes(self, tokens: int, element_size: int) -> int:
+        """Bytes of activations this part allocates while a step of ``tokens`` tokens runs through it (its
+        children's included), for sizing the cache beside them.  0: nothing worth counting."""
+        return 0
 
     def all_tensor_specs(self) -> List[TensorSpec]:
         out = list(self.tensor_specs())

@@ -16,6 +16,10 @@ class PreNormBlock(Block):
     def children(self) -> List[Part]:
         return [self.mixer_norm, self.mixer, self.ffn_norm, self.ffn]
 
+    def step_bytes(self, tokens: int, element_size: int) -> int:
+        h = tokens * self.mixer_norm.width * element_size if hasattr(self.mixer_norm, "width") else 0
+        return h + max(self.mixer.step_bytes(tokens, element_size), self.ffn.step_bytes(tokens, element_size))
+
     def forward(self, ctx, x: torch.Tensor, cache) -> None:
         h = ctx.buffer(tuple(x.shape))
         self.mixer_norm.forward(x, h)

@@ -32,6 +32,11 @@ def matmul_nt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int, sc
     """out (op)= a @ w.T with the epilogue ``mode``; a [M, K], w [N or 2N, K]."""
     if a.shape[0] == 0:
         return
+    prof = ops.profiling()
+    if prof is not None:
+        M, K = a.shape
+        R = w.shape[0]          # weight rows: N, or 2N for SwiGLU
+        prof.note_work((M * K + R * K) * a.element_size() + M * out.shape[1] * out.element_size(), 2 * M * R * K)
     if a.dtype == torch.float32 or BF16_BACKEND == "plain":
         ops.gemm_plain(a, w, out, mode)
         return

@@ -23,6 +23,9 @@ class GatedMLP(FeedForward):
     def children(self) -> List[Part]:
         return [self.gate_up, self.down]
 
+    def step_bytes(self, tokens: int, element_size: int) -> int:
+        return tokens * self.intermediate * element_size
+
     def forward(self, ctx, h: torch.Tensor, x: torch.Tensor) -> None:
         act = ctx.buffer((h.shape[0], self.intermediate))
         self.gate_up.forward(h, act, SWIGLU)

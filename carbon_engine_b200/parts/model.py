@@ -66,6 +66,12 @@ class DecoderModel(Part):
             out.append((cache_id, spec))
         return out
 
+    def step_bytes(self, tokens: int, element_size: int, rows: int = 0) -> int:
+        """Activations of a step of ``tokens`` tokens with logits at ``rows`` places: the float32 residual
+        stream, the largest block's buffers (blocks run one after another), the normed rows and the logits."""
+        blocks = max((b.step_bytes(tokens, element_size) for b in self.blocks), default=0)
+        return tokens * self.embedding.width * 4 + blocks + rows * (self.head.width * element_size + self.head.vocab * 4)
+
     def load_weights(self, get, device: torch.device, dtype: torch.dtype) -> None:
         self.device, self.dtype = device, dtype
         self.load_all(get, device, dtype)

@@ -81,6 +81,9 @@ class PositionEncoding:
     cos: Optional[torch.Tensor] = None     # float32 [max_positions, rotary_dim / 2]
     sin: Optional[torch.Tensor] = None
     max_positions: int = 0
+    #: which elements of a head turn together by angle i: "half" (i and i + rotary_dim/2, the reference's
+    #: layout, src/model/layers.rs:159) or "interleaved" (2i and 2i + 1)
+    pairing: str = "half"
 
     def prepare(self, device: torch.device) -> None:
         """Build the tables on ``device``."""
@@ -88,8 +91,11 @@ class PositionEncoding:
 
 class RotaryEmbedding(PositionEncoding):
     def __init__(self, head_dim: int, theta: float, max_positions: int, rotary_dim: Optional[int] = None,
-                 scaling: Optional[RopeScaling] = None):
+                 scaling: Optional[RopeScaling] = None, pairing: str = "half"):
         rd = head_dim if rotary_dim is None else rotary_dim
+        if pairing not in ("half", "interleaved"):
+            raise ValueError(f"unknown pairing '{pairing}' (half, interleaved)")
+        self.pairing = pairing
         if rd % 2 or rd > head_dim or rd <= 0:
             raise ValueError(f"rotary_dim {rd} must be even and within head_dim {head_dim}")
         self.head_dim, self.theta, self.max_positions, self.rotary_dim = head_dim, float(theta), int(max_positions), rd

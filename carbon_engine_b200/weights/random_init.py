@@ -14,11 +14,9 @@ from typing import Dict, Sequence
 
 import torch
 
-from ..parts.base import TensorSpec
+from ..parts.base import INIT_KINDS, TensorSpec
 
 _M64 = (1 << 64) - 1
-LINEAR_STD = 0.02
-NORM_STD = 0.1
 
 
 def _fnv1a(name: str) -> int:
@@ -61,14 +59,15 @@ def random_tensor(spec: TensorSpec, seed: int, device, dtype: torch.dtype, chunk
     for s in spec.shape:
         numel *= s
     out = torch.empty(numel, dtype=dtype, device=device)
+    try:
+        mean, std, _ = INIT_KINDS[spec.init]
+    except KeyError:
+        raise ValueError(f"{spec.name}: unknown init kind '{spec.init}' (known: {', '.join(sorted(INIT_KINDS))}; "
+                         f"parts.base.register_init_kind adds one)") from None
     for lo in range(0, numel, chunk):
         n = min(chunk, numel - lo)
         z = standard_normal(spec.name, n, seed, device, lo)
-        if spec.init == "norm":
-            z = 1.0 + NORM_STD * z
-        else:
-            z = LINEAR_STD * z
-        out[lo:lo + n] = z.to(dtype)
+        out[lo:lo + n] = (mean + std * z).to(dtype)
     return out.view(spec.shape)
 
 
@@ -82,5 +81,5 @@ class RandomWeights:
     def __call__(self, name: str) -> torch.Tensor:
         spec = self.specs[name]
         # norm weights are small and are kept in 32-bit; matrices are rounded to the stored dtype
-        dt = torch.float32 if spec.init == "norm" else self.matrix_dtype
+        dt = torch.float32 if INIT_KINDS.get(spec.init, (0, 0, False))[2] else self.matrix_dtype
         return random_tensor(spec, self.seed, self.device, dt)

@@ -138,6 +138,35 @@ def test_qk_norm_rope_and_cache_write(ops, dtype, nh, nkv, d, rd, ps, first):
     assert int((~torch.isnan(kp.float())).sum()) == written and int((~torch.isnan(vp.float())).sum()) == written
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,d,rd", [(4, 2, 64, 64), (3, 1, 48, 32), (2, 2, 128, 128)])
+def test_qk_rotation_with_interleaved_pairs(ops, dtype, nh, nkv, d, rd):
+    """The pairing is a parameter: elements 2i and 2i + 1 turn together by angle i."""
+    torch.manual_seed(4)
+    seqs, ps = [(7, 5), (0, 1)], 8
+    T = 6
+    table, kp, vp = paged_layout([c + n for c, n in seqs], ps, nkv, d, dtype)
+    qkv = torch.randn(T, (nh + 2 * nkv) * d, device=dev()).to(dtype)
+    positions, sot, slots = step_meta(seqs)
+    c, s = plain.rope_tables(torch.arange(32), rd, 500.0)
+    src = qkv.clone()
+    st = status()
+    ops.qk_rope_kvwrite(qkv, kp, vp, None, None, c.float().to(dev()), s.float().to(dev()), positions, sot, slots, table, st,
+                        nh, nkv, d, rd, ps, 0.0, pairing="interleaved")
+    assert st.item() == 0
+    q = src.double().cpu()[:, :nh * d].view(T, nh, d)
+    cp, sp = c[positions.cpu().long()][:, None, :], s[positions.cpu().long()][:, None, :]
+    want = q.clone()
+    want[..., 0:rd:2] = q[..., 0:rd:2] * cp - q[..., 1:rd:2] * sp
+    want[..., 1:rd:2] = q[..., 1:rd:2] * cp + q[..., 0:rd:2] * sp
+    assert rel_err(qkv[:, :nh * d].view(T, nh, d), want) < TOL[dtype]
+    halves = plain.apply_rope(q, c[positions.cpu().long()], s[positions.cpu().long()])
+    assert rel_err(qkv[:, :nh * d].view(T, nh, d), halves) > 0.1           # and it is not the other pairing
+    with pytest.raises(Exception, match="pairing"):
+        ops.qk_rope_kvwrite(qkv, kp, vp, None, None, None, None, positions, sot, slots, table, st, nh, nkv, d, 0, ps, 0.0,
+                            pairing="pairs")
+
+
 def test_qk_kernel_flags_a_page_the_request_does_not_hold(ops):
     table, kp, vp = paged_layout([4], 4, 1, 16, torch.float32)
     qkv = torch.randn(1, 3 * 16, device=dev())

@@ -180,7 +180,8 @@ def test_block_embedding_and_tied_head(dtype):
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_layer_order_is_data_a_block_twice_and_a_shared_cache(dtype):
     """Schedule: block 0 (cache 0), block 1 (cache 1), block 0 again (cache 2), block 1 reading cache 1.
-    The last call writes no keys: its queries attend to the keys and values its first call stored."""
+    The last call writes no keys: its queries attend to the keys and values its first call stored.
+    Block 1's cache has pages of a size of its own, so its page ids and block table are a group apart."""
     from carbon_engine_b200.parts.attention import PagedAttention
     from carbon_engine_b200.parts.block import PreNormBlock
     from carbon_engine_b200.parts.embedding import Embedding, LMHead
@@ -192,7 +193,8 @@ def test_layer_order_is_data_a_block_twice_and_a_shared_cache(dtype):
     H, nh, nkv, d, V = 48, 3, 1, 32, 77
     rope = RotaryEmbedding(d, 1e4, 256)
     blocks = [PreNormBlock(RMSNorm(H, 1e-6, f"model.layers.{i}.input_layernorm.weight"),
-                           PagedAttention(H, nh, nkv, d, f"model.layers.{i}.self_attn", rope, qk_norm_eps=1e-6),
+                           PagedAttention(H, nh, nkv, d, f"model.layers.{i}.self_attn", rope, qk_norm_eps=1e-6,
+                                          page_size=4 if i == 1 else None),
                            RMSNorm(H, 1e-6, f"model.layers.{i}.post_attention_layernorm.weight"),
                            GatedMLP(H, 64, f"model.layers.{i}.mlp")) for i in range(2)]
     emb = Embedding(V, H, "model.embed_tokens.weight")
@@ -203,6 +205,7 @@ def test_layer_order_is_data_a_block_twice_and_a_shared_cache(dtype):
     get, w = weights_for(model, seed=3, gain=3.0)
     model.load_weights(get, torch.device(DEV), dtype)
     runner = make_runner(model, dtype)
+    assert [g.page_size for g in runner.storage.groups] == [runner.storage.page_size, 4]
     runner.open_request(5)
     toks = np.random.default_rng(0).integers(0, V, 40).tolist()
     got = [runner.step([StepEntry(5, toks[:23], list(range(23)))]), runner.step([StepEntry(5, toks[23:], list(range(17)))])]

@@ -32,7 +32,9 @@ def define_toy():
     from carbon_engine_b200.parts.rope import PositionEncoding
 
     class LinearAngles(PositionEncoding):
-        """angle(position, i) = position * step * (i + 1), for the first rotary_dim elements of a head."""
+        """angle(position, i) = position * step * (i + 1), for the first rotary_dim elements of a head; elements
+        2i and 2i + 1 turn together (the package's own encoding pairs i with i + rotary_dim / 2)."""
+        pairing = "interleaved"
 
         def __init__(self, head_dim: int, rotary_dim: int, step: float, max_positions: int):
             self.head_dim, self.rotary_dim, self.step, self.max_positions = head_dim, rotary_dim, step, max_positions
@@ -125,6 +127,16 @@ def define_toy():
     return ToyConfig, build
 
 
+def rotate_interleaved(x, cos, sin):
+    """Elements 2i and 2i + 1 of the first 2 * cos.shape[-1] of every head turn by angle i.  x [T, heads, d]."""
+    rd = 2 * cos.shape[-1]
+    c, s = cos[:, None, :], sin[:, None, :]
+    out = x.clone()
+    out[..., 0:rd:2] = x[..., 0:rd:2] * c - x[..., 1:rd:2] * s
+    out[..., 1:rd:2] = x[..., 1:rd:2] * c + x[..., 0:rd:2] * s
+    return out
+
+
 def plain_toy_forward(cfg: dict, w, tokens):
     """Whole sequence, no cache: the plain functions, with the toy angles and the routing written out."""
     T = len(tokens)
@@ -140,7 +152,7 @@ def plain_toy_forward(cfg: dict, w, tokens):
         q = plain.rms_norm((h @ w[f"{p}.self_attn.q_proj.weight"].T).view(T, nh, d), w[f"{p}.self_attn.q_norm.weight"], 1e-6)
         k = plain.rms_norm((h @ w[f"{p}.self_attn.k_proj.weight"].T).view(T, nkv, d), w[f"{p}.self_attn.k_norm.weight"], 1e-6)
         v = (h @ w[f"{p}.self_attn.v_proj.weight"].T).view(T, nkv, d)
-        a = plain.causal_attention(plain.apply_rope(q, cos, sin), plain.apply_rope(k, cos, sin), v, 1.0 / math.sqrt(d))
+        a = plain.causal_attention(rotate_interleaved(q, cos, sin), rotate_interleaved(k, cos, sin), v, 1.0 / math.sqrt(d))
         x = x + a.reshape(T, nh * d) @ w[f"{p}.self_attn.o_proj.weight"].T
         h = plain.rms_norm(x, w[f"{p}.post_attention_layernorm.weight"], 1e-6)
         if kind == "toy_top1_experts":

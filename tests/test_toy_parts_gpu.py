@@ -179,6 +179,18 @@ def test_toy_state_mixer_is_registered_built_and_stepped(tmp_path, dtype):
         runner.close_request(1); runner.close_request(2)
         storage.manager.check()
         assert storage.manager.free_pages(0) == 24 and storage.manager.free_slots() == 3
+        # through the entry point: the per-request state is part of the memory the cache is sized beside
+        from carbon_engine_b200 import Engine, SamplingParams
+        eng = Engine(folder, dtype=dtype, page_size=8, max_running_requests=3, max_prefill_tokens=64, memory_ratio=0.3)
+        assert eng._state_bytes() == 2 * 24 * 4 * 3 == eng.storage.state_bytes()       # two state layers, float32, 3 slots
+        assert eng._workspace_bytes() > eng.model.step_bytes(64, 4, rows=3) > 0
+        assert not eng.cuda_graphs and eng.stats()["kv_pages_total"] == 8 * max_len // 8
+        out = eng.generate([seqs[1]], SamplingParams(max_tokens=4, ignore_eos=True))[0]
+        toks = list(seqs[1])
+        for t in out.token_ids:
+            row = plain_toy_forward(pcfg, w, toks)[-1]
+            assert t == int(row.argmax()) or float(row.max() - row[t]) < 2 * tol * float(row.abs().max())
+            toks.append(t)
     finally:
         unregister_architecture("ToyDecayForCausalLM")
         unregister_part("mixer", "toy_decay")

@@ -26,8 +26,15 @@ _STATUS = {
     2: "a token was to be written to a page its request does not hold",
     3: "a position beyond the rotary table (raise max_seq_len)",
     4: "attention read a page its request does not hold",
-    5: "a bounded wait inside a tensor-core kernel gave up (the step's results are not valid)",
+    5: "a bounded wait inside a tensor-core product gave up (the step's results are not valid)",
+    7: "a bounded wait inside the decode attention kernel gave up (the step's results are not valid)",
 }
+
+
+def _status_text(code: int) -> str:
+    if code >= 10:
+        return "a bounded wait inside the flash attention kernel gave up (the step's results are not valid)"
+    return _STATUS.get(code, "unknown")
 
 
 class ModelRunner:
@@ -282,4 +289,4 @@ class ModelRunner:
             if self.device.type == "cuda":      # a kernel that gave up may have left its split counters half counted
                 from .. import ops_tensor
                 ops_tensor.reset_counters(self.device)
-            raise StepError(f"device status {code}: {_STATUS.get(code, 'unknown')}")
+            raise StepError(f"device status {code}: {_status_text(code)}")

@@ -191,7 +191,8 @@ def main() -> int:
     cfg = dict(SIZES_8B, num_hidden_layers=args.layers)
     h = BenchHarness(cfg, max_batch=2 if args.prefill_only else max(64 if not args.no_points else args.batch, args.batch),
                      context=args.context,
-                     new_tokens=max(256, args.steps + args.warmup + 8), graphs=not args.no_graphs)
+                     new_tokens=max(256, args.steps + args.warmup + 8 + args.batch * ((args.context + 4095) // 4096 + 1)),
+                     graphs=not args.no_graphs)
     if args.prefill_only:
         pf = h.prefill(2048, 2, 2)
         print(json.dumps({"prefill_ms": round(pf["ms"], 3), "layers": args.layers}))

@@ -84,13 +84,21 @@ class BenchHarness:
         """Through Engine.add_request / Engine.step: real prompts are prefilled, then ``steps`` decode
         steps are timed on the host clock between two synchronisations."""
         eng = self.engine
-        # long enough that no request ends inside the timed region (requests whose prompts were done
-        # first have decoded through the other prompts' steps already)
-        sp = SamplingParams(max_tokens=warmup + steps + batch + 8, ignore_eos=True)
+        # long enough that no request ends inside the timed region: a request whose prompt is done decodes
+        # through every step that the later prompts' portions take
+        prompt_steps = batch * ((self.context + eng.max_step_tokens - 1) // eng.max_step_tokens + 1)
+        if warmup + steps + prompt_steps + 8 > self.new_tokens:
+            raise ValueError(f"the harness was sized for {self.new_tokens} new tokens a request; this run needs "
+                             f"{warmup + steps + prompt_steps + 8}")
+        sp = SamplingParams(max_tokens=warmup + steps + prompt_steps + 8, ignore_eos=True)
+        before = eng.scheduler.stats()["prefill_tokens"]
         for _ in range(batch):
             eng.add_request(self._tokens(self.context), sp)
-        while eng.scheduler.stats()["prefill_tokens"] < batch * self.context:
-            eng.step()
+        while eng.scheduler.stats()["prefill_tokens"] - before < batch * self.context:
+            for out in eng.step():
+                raise RuntimeError(f"a request ended during the prompts ({out.finish_reason}: {out.error})")
+            if not eng.has_unfinished():
+                raise RuntimeError("the engine ran out of work before the prompts were done")
         for _ in range(warmup):
             eng.step()
         torch.cuda.synchronize()

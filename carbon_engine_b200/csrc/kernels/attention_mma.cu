@@ -559,8 +559,19 @@ __global__ void __launch_bounds__(AMT_THREADS) attention_decode_tma_kernel(const
 
     if (warp == 4) {
         // ---- producer
+        // The page ids of this split's pieces, looked up by the whole warp at once: one trip to the block table
+        // instead of one per piece in the copying thread's chain (the table is an input of the step).
+        constexpr int PAGES_AHEAD = 512;
+        __shared__ int s_pages[PAGES_AHEAD];
+        {
+            int shift = 31 - __clz(a.page_size);
+            int pieces = n_tiles * (AM_TILE / box_rows);
+            for (int e = lane; e < min(pieces, PAGES_AHEAD); e += 32) s_pages[e] = table[(k_begin + e * box_rows) >> shift];
+            __syncwarp();
+        }
         if (lane == 0) {
             int shift = 31 - __clz(a.page_size);
+            int per_tile = AM_TILE / box_rows;
             int s = 0;
             uint32_t ph = 0;
             bool wrapped = false, ok = true, waited = false;
@@ -578,7 +589,8 @@ __global__ void __launch_bounds__(AMT_THREADS) attention_decode_tma_kernel(const
                 asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
                 for (int j = first; j <= last; ++j) {
                     int key = k0 + j * box_rows;
-                    int page = table[key >> shift];
+                    int piece = it * per_tile + j;
+                    int page = piece < PAGES_AHEAD ? s_pages[piece] : table[key >> shift];
                     if (page < 0 || page >= a.num_pages) { atomicExch(a.status, 4); page = 0; }
                     int row = (page * a.nkv + kvh) * a.page_size + (key & (a.page_size - 1));
                     uint32_t dst = base + (uint32_t)s * stage_bytes + (uint32_t)(j * box_rows) * 128u;

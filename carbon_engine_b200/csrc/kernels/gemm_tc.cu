@@ -745,6 +745,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_pair_kernel(const __grid_cons
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     __shared__ __align__(8) uint64_t full_bar[8], empty_bar[8], acc_full[2], acc_empty[2];
     __shared__ uint32_t tmem_slot;
+    __shared__ int s_acc_ok;                         // the epilogue's verdict on a wait, taken by one thread for all 128
     __shared__ float xbuf[GU ? 2 * 2 * 64 * 17 : 1]; // GU: per buffer, 16 gate and 16 up values of 64 features (padded rows)
 
     constexpr int HALF_N = BN / 2;
@@ -809,7 +810,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_pair_kernel(const __grid_cons
             if (!ok) {
                 // give the copies in flight time to land before the block may leave (the leader's barriers
                 // count the bytes of both blocks; the peer cannot wait on them, so it waits by the clock)
-                atomicExch(a.status, 5);
+                atomicExch(a.status, 51);
                 if (rank == 0) for (int i = max(0, issued - stages); i < issued; ++i) mbar_wait_cluster(&full_bar[i % stages], (i / stages) & 1);
                 else for (int i = 0; i < 64; ++i) __nanosleep(1000);
             }
@@ -828,11 +829,11 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_pair_kernel(const __grid_cons
             for (int tile = pair; tile < total && ok; tile += n_pairs, ++lt) {
                 int buf = lt & 1;
                 if (lt >= 2) ok = mbar_wait_cluster(&acc_empty[buf], ((lt >> 1) - 1) & 1);   // both epilogues have drained this set
-                if (!ok) break;
+                if (!ok) { atomicExch(a.status, 52); break; }
                 uint32_t d_tmem = tmem + buf * ACC_COLS;
                 for (int r = 0; r < rounds; ++r) {
                     if (!ready) ok = mbar_wait_cluster(&full_bar[s], ph);
-                    if (!ok) break;
+                    if (!ok) { atomicExch(a.status, 53); break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     int sn = s + 1 == stages ? 0 : s + 1;
                     uint32_t phn = sn == 0 ? ph ^ 1 : ph;
@@ -852,7 +853,6 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_pair_kernel(const __grid_cons
                 }
                 if (ok) umma2_commit_both(&acc_full[buf]);
             }
-            if (!ok) atomicExch(a.status, 5);
         }
     } else {
         // ---- epilogue (in each CTA): its own 128 rows
@@ -875,8 +875,12 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_pair_kernel(const __grid_cons
 #pragma unroll
                 for (int j = 0; j < 32; ++j) xv[j] = j < m_valid ? xp[(size_t)j * a.ldo] : 0.f;
             }
-            ok = mbar_wait_cluster(&acc_full[buf], (lt >> 1) & 1);
-            if (!ok) { atomicExch(a.status, 5); break; }
+            // One thread waits (bounded) and all 128 take its verdict: if each polled for itself, a wait that ran
+            // out for some threads and not for others would leave them at different barriers for good.
+            if (threadIdx.x == 64) s_acc_ok = mbar_wait_cluster(&acc_full[buf], (lt >> 1) & 1) ? 1 : 0;
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            ok = s_acc_ok != 0;
+            if (!ok) { if (threadIdx.x == 64) atomicExch(a.status, 54); break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             uint32_t taddr = tmem + buf * ACC_COLS + ((uint32_t)(quad * 32) << 16);
             if (!GU && a.mode == TC_ACCUM_F32) {

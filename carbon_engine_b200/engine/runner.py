@@ -7,6 +7,7 @@ by either a prefill batch or a decode batch; here one call takes any mixture.
 """
 from __future__ import annotations
 
+import os
 from typing import List, Optional, Sequence
 
 import numpy as np
@@ -32,12 +33,17 @@ _STATUS = {
 
 
 def _status_text(code: int) -> str:
+    if 50 <= code < 60:
+        return f"a bounded wait inside a tensor-core product gave up (site {code}; the step's results are not valid)"
     if code >= 10:
         return "a bounded wait inside the flash attention kernel gave up (the step's results are not valid)"
     return _STATUS.get(code, "unknown")
 
 
 class ModelRunner:
+    #: steps of more tokens than this run their kernels strictly one after another (see ``step``)
+    DEPENDENT_LAUNCH_MAX_TOKENS = 256
+
     def __init__(self, model, storage: CacheStorage, max_step_tokens: int):
         self.model, self.storage = model, storage
         self.device, self.dtype = model.device, model.dtype
@@ -139,6 +145,11 @@ class ModelRunner:
                                 b.dev_section(f"upd_val{g}", n))
         return ctx, b.dev_section("rows", n_rows), commits
 
+    def _write_table_entries(self, group: int, idx: np.ndarray, val: np.ndarray) -> None:
+        d_idx = torch.from_numpy(np.ascontiguousarray(idx, dtype=np.int32)).to(self.device)
+        d_val = torch.from_numpy(np.ascontiguousarray(val, dtype=np.int32)).to(self.device)
+        ops.scatter_i32(self.storage.device_tables[group], d_idx, d_val)
+
     def _layout(self, entries: Sequence[StepEntry]):
         """Checks, page reservations and the step's layout in the pinned host buffer (nothing is sent)."""
         mgr = self.storage.manager
@@ -214,6 +225,12 @@ class ModelRunner:
         for g in range(len(self.storage.groups)):
             if upd[g][0]:
                 idx = np.concatenate(upd[g][0]); val = np.concatenate(upd[g][1])
+                cap = len(b.host_section(f"upd_idx{g}"))
+                if len(idx) > cap:
+                    # more new table entries than a step's section holds (requests that arrive with long contexts
+                    # already in the cache): the surplus goes to the device tables at once, by a copy of its own
+                    self._write_table_entries(g, idx[cap:], val[cap:])
+                    idx, val = idx[:cap], val[:cap]
                 b.host_section(f"upd_idx{g}")[:len(idx)] = idx
                 b.host_section(f"upd_val{g}")[:len(val)] = val
                 n_upd.append(len(idx))
@@ -226,6 +243,14 @@ class ModelRunner:
         entries and of their ``want`` lists.  With CUDA graphs on, the logits of a pure decode step
         live in a buffer that the next such step overwrites."""
         ctx, rows, commits = self.prepare(entries)
+        # Dependent launches (a kernel starts, and streams its first weights, while the kernel before it still
+        # runs) are what makes the short kernels of small steps overlap.  Steps of more than 256 tokens run the
+        # persistent CTA-pair product, whose grid wants every pair of SMs: with its dependents already resident
+        # and waiting beside it, such a step was seen, rarely (once in a few thousand layers at 4,096 tokens a
+        # step), never to finish: the pair kernel did not complete although all of its blocks that ran had left,
+        # and the next kernel's blocks waited for it for good.  Large steps gain next to nothing from the
+        # overlap, so they run without it.
+        ops.set_dependent_launches(ctx.T <= self.DEPENDENT_LAUNCH_MAX_TOKENS and os.environ.get("CE_PDL", "1") != "0")
         if self.graphs_enabled and ctx.n_decode == ctx.B and all(len(e.want) == 1 for e in entries):
             logits = self._replay_decode(ctx, rows)
         else:

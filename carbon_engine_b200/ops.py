@@ -72,7 +72,8 @@ class KernelProfile:
     def __enter__(self):
         global _profile
         import torch
-        kernels().ce_set_pdl(0)
+        self._pdl_before = _pdl_on
+        set_dependent_launches(False)
         torch.cuda.synchronize()
         self._start = torch.cuda.Event(enable_timing=True)
         self._start.record()
@@ -84,7 +85,7 @@ class KernelProfile:
         import torch
         _profile = None
         torch.cuda.synchronize()
-        kernels().ce_set_pdl(1)
+        set_dependent_launches(self._pdl_before)
 
     def note_work(self, nbytes: int, flops: int) -> None:
         self._work = (int(nbytes), int(flops))
@@ -131,6 +132,18 @@ def _ok(code: int, n: int = 1) -> None:
     _launches += n
     if _profile is not None:
         _profile._launched(n)
+
+
+_pdl_on = True
+
+
+def set_dependent_launches(on: bool) -> None:
+    """Whether kernels launched from now on may start while the kernel before them still runs (programmatic
+    dependent launch).  The step function turns it off for steps of many tokens, see ``ModelRunner.step``."""
+    global _pdl_on
+    if bool(on) != _pdl_on:
+        kernels().ce_set_pdl(1 if on else 0)
+        _pdl_on = bool(on)
 
 
 def kernel_counts() -> dict:

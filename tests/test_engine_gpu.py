@@ -260,3 +260,33 @@ def test_host_lookahead_gives_the_same_tokens(models, graphs, name, dtype):
             assert got == plain.greedy_generate(cfg, w, p, s.max_tokens)
         else:
             check_greedy(cfg, w, p, got, dtype)
+
+
+def test_more_new_table_entries_than_a_steps_section_holds(models):
+    """Requests that arrive with long contexts already in the cache (as the benchmark's harness makes them) bring
+    more new block-table entries in their first step than the step's section of the pinned buffer holds: the
+    surplus reaches the device tables by a copy of its own, and the step gives the same logits."""
+    from carbon_engine_b200.cache.storage import CacheStorage
+    from carbon_engine_b200.engine.batch import StepEntry
+    from carbon_engine_b200.engine.engine import build_model
+    from carbon_engine_b200.engine.runner import ModelRunner
+    d, cfg, w = models["B"]
+    dev = torch.device("cuda:0")
+    model, _, _ = build_model(d, torch.float32, dev, max_seq_len=1024)
+    out = {}
+    for step_tokens in (16, 2048):
+        storage = CacheStorage(model, torch.float32, dev, 8, 512, 4, 1024)
+        g = torch.Generator(device=dev).manual_seed(5)
+        for view in storage.paged_views():
+            view.k_pool.normal_(0.0, 1.0, generator=g)
+            view.v_pool.normal_(0.0, 1.0, generator=g)
+        runner = ModelRunner(model, storage, step_tokens)
+        for rid, ctx_len in enumerate((700, 90, 512, 333)):
+            runner.open_request(rid)
+            storage.manager.reserve(rid, ctx_len)
+            storage.manager.commit(rid, ctx_len)
+        cap = len(runner.bufs.host_section("upd_idx0"))
+        assert (cap < 200) == (step_tokens == 16)                       # 205 entries are new in this step
+        out[step_tokens] = runner.step([StepEntry(rid, [7 + rid], [0]) for rid in range(4)]).clone()
+        runner.check_status()
+    assert torch.isfinite(out[16]).all() and torch.equal(out[16], out[2048])

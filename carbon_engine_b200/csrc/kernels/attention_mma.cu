@@ -949,18 +949,24 @@ extern "C" int ce_attention_decode_bf16(const void* q, const void* k_pool, const
     // Split size: a multiple m of AM_SPLIT.  A block has a fixed cost (launch, the chain of loads that
     // leads to its first tile, combining its warps, writing a partial) worth about six tiles of work, and
     // blocks run in waves of `slots`; m minimises waves x (tiles of a block + 6).  Few sequences get many
-    // short splits that fill one wave; many sequences get one block each.  The choice depends on the
-    // number of one-token sequences and on max_splits, not on their contents.
+    // short splits that fill one wave; many sequences get one block each.  The splits of a sequence merge
+    // inside a cluster (at most 8 of them) or, where that leaves most of the GPU idle (one sequence with a
+    // long context: 8 KV heads x 8 splits are 64 blocks), through scratch memory and a merge kernel, whose
+    // launch is worth about six tiles more.  The choice depends on the number of one-token sequences and on
+    // max_splits, not on their contents.
+    bool use_cluster = false;
     {
         long long pairs = (long long)n_seqs * nkv * ((G + hgroup - 1) / hgroup);
         long long slots = 2LL * ce_sm_count();           // two blocks share an SM (shared memory of three stages each)
         long long best = -1;
         int best_m = 1;
         for (int m = 1; m <= max_splits; ++m) {
-            if (cluster_ok && (max_splits + m - 1) / m > 8) continue;      // a cluster holds at most 8 splits
-            long long blocks = pairs * ((max_splits + m - 1) / m);
-            long long cost = ((blocks + slots - 1) / slots) * ((long long)m * (AM_SPLIT / AM_TILE) + 6);
-            if (best < 0 || cost < best) { best = cost; best_m = m; }
+            int splits = (max_splits + m - 1) / m;
+            long long blocks = pairs * splits;
+            long long work = ((blocks + slots - 1) / slots) * ((long long)m * (AM_SPLIT / AM_TILE) + 6);
+            if (cluster_ok && splits <= 8 && (best < 0 || work < best)) { best = work; best_m = m; use_cluster = true; }
+            long long with_merge = work + (splits > 1 ? 6 : 0);
+            if ((!cluster_ok || splits > 8) && (best < 0 || with_merge < best)) { best = with_merge; best_m = m; use_cluster = false; }
         }
         a.split = best_m * AM_SPLIT;
         a.max_splits = (max_splits + best_m - 1) / best_m;
@@ -988,7 +994,7 @@ extern "C" int ce_attention_decode_bf16(const void* q, const void* k_pool, const
         size_t tsmem = (deep3 ? 3 : 2) * stage;
         if (comb > tsmem) tsmem = comb;
         tsmem += 1024;
-        a.cluster_merge = cluster_ok && max_splits <= 8;
+        a.cluster_merge = use_cluster;
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = grid;
         cfg.blockDim = dim3(AMT_THREADS);

@@ -55,9 +55,8 @@ int sched_submit(void* h, int64_t id, const int32_t* prompt, int n, int max_toke
 // Lays out the next step.  Returns the number of entries; entries are written as 5 x int64 each
 // (id, slot, start, count, sample) up to max_entries, token ids up to max_tokens.  A negative
 // return means a buffer was too small.
-int sched_plan(void* h, int64_t* entries, int max_entries, int32_t* tokens, int max_tokens, int* n_tokens) {
-    Scheduler* s = (Scheduler*)h;
-    const auto& plan = s->plan();
+static int write_plan(Scheduler* s, const std::vector<PlanEntry>& plan, int64_t* entries, int max_entries,
+                      int32_t* tokens, int max_tokens, int* n_tokens) {
     const auto& toks = s->plan_tokens();
     if ((int)plan.size() > max_entries || (int)toks.size() > max_tokens) return -1;
     for (size_t i = 0; i < plan.size(); ++i) {
@@ -71,6 +70,19 @@ int sched_plan(void* h, int64_t* entries, int max_entries, int32_t* tokens, int 
     *n_tokens = (int)toks.size();
     return (int)plan.size();
 }
+int sched_plan(void* h, int64_t* entries, int max_entries, int32_t* tokens, int max_tokens, int* n_tokens) {
+    Scheduler* s = (Scheduler*)h;
+    return write_plan(s, s->plan(), entries, max_entries, tokens, max_tokens, n_tokens);
+}
+// The same for the step that is already on the device for the requests `ids` (Scheduler::plan_for).
+int sched_plan_for(void* h, const int64_t* ids, int n, int64_t* entries, int max_entries, int32_t* tokens,
+                   int max_tokens, int* n_tokens) {
+    Scheduler* s = (Scheduler*)h;
+    return write_plan(s, s->plan_for(ids, n), entries, max_entries, tokens, max_tokens, n_tokens);
+}
+int sched_remaining(void* h, int64_t id) { return ((Scheduler*)h)->remaining(id); }
+int sched_waiting(void* h) { return ((Scheduler*)h)->waiting(); }
+int sched_running(void* h) { return ((Scheduler*)h)->running(); }
 int sched_commit(void* h, const int32_t* sampled, int n) { return ((Scheduler*)h)->commit(sampled, n); }
 void sched_fail_step(void* h) { ((Scheduler*)h)->fail_step(); }
 int sched_abort(void* h, int64_t id) { return ((Scheduler*)h)->abort(id); }

@@ -92,6 +92,28 @@ const std::vector<PlanEntry>& Scheduler::plan() {
     return plan_;
 }
 
+const std::vector<PlanEntry>& Scheduler::plan_for(const int64_t* ids, int n) {
+    plan_.clear();
+    plan_tokens_.clear();
+    for (int i = 0; i < n; ++i) {
+        auto it = requests_.find(ids[i]);
+        if (it == requests_.end() || it->second.reason != FINISH_NONE) continue;
+        Request& r = it->second;
+        int pending = (int)r.tokens.size() - r.computed;
+        if (r.generated == 0 || pending <= 0 || cache_->slot_of(r.id) < 0) continue;
+        if (cache_->reserve(r.id, r.computed + pending) != CACHE_OK) continue;
+        plan_.push_back(PlanEntry{r.id, cache_->slot_of(r.id), r.computed, pending, true});
+        plan_tokens_.insert(plan_tokens_.end(), r.tokens.begin() + r.computed, r.tokens.end());
+    }
+    return plan_;
+}
+
+int Scheduler::remaining(int64_t id) const {
+    auto it = requests_.find(id);
+    if (it == requests_.end() || it->second.reason != FINISH_NONE) return -1;
+    return it->second.max_new - it->second.generated;
+}
+
 void Scheduler::finish(Request& r, int reason) {
     r.reason = reason;
     if (cache_->slot_of(r.id) >= 0) cache_->close(r.id);

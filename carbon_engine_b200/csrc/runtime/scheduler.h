@@ -61,6 +61,15 @@ class Scheduler {
     // entry, are in plan_tokens().
     const std::vector<PlanEntry>& plan();
     const std::vector<int32_t>& plan_tokens() const { return plan_tokens_; }
+    // The step after the last one is already on the device for these requests, one token each, its token
+    // ids taken there from the last step's picks.  Lays out exactly that step for those of them that still
+    // run (a request that ended meanwhile is left out); nothing is admitted.  The fed token of an entry is
+    // the one the last commit appended.
+    const std::vector<PlanEntry>& plan_for(const int64_t* ids, int n);
+    // Tokens the request may still generate; -1 for an unknown or ended request.
+    int remaining(int64_t id) const;
+    int waiting() const { return (int)waiting_.size(); }
+    int running() const { return (int)running_.size(); }
     // The step ran: `sampled` holds one token for every entry with sample == 1, in order.
     int commit(const int32_t* sampled, int n);
     // The step failed: every request of the plan ends with an error, the others go on

@@ -36,6 +36,10 @@ _SIGNATURES = {
     "sched_destroy": (None, [_p]),
     "sched_submit": (_i, [_p, _i64, _pi32, _i, _i, _i, _pi32, _i]),
     "sched_plan": (_i, [_p, _pi64, _i, _pi32, _i, _pi]),
+    "sched_plan_for": (_i, [_p, _pi64, _i, _pi64, _i, _pi32, _i, _pi]),
+    "sched_remaining": (_i, [_p, _i64]),
+    "sched_waiting": (_i, [_p]),
+    "sched_running": (_i, [_p]),
     "sched_commit": (_i, [_p, _pi32, _i]),
     "sched_fail_step": (None, [_p]),
     "sched_abort": (_i, [_p, _i64]),

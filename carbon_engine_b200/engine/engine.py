@@ -26,7 +26,7 @@ from .batch import StepEntry
 from ..cache.manager import CacheError
 from ..csrc.kernel_lib import KernelError
 from .runner import ModelRunner, StepError
-from .scheduler import Scheduler, SubmitError
+from .scheduler import PlanEntry, Scheduler, SubmitError
 
 DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "f32": torch.float32,
           "auto": torch.bfloat16}
@@ -94,12 +94,25 @@ class _Live:
     logprobs: List[dict] = field(default_factory=list)
 
 
+@dataclass
+class _InFlight:
+    """A step that is on the device and whose picks have not been read."""
+    ids: List[int]                      # the requests it samples for, in the order of its picks
+    starts: Dict[int, int]              # where each request's tokens of this step begin
+    steps: List[int] = field(default_factory=list)       # tokens each request had drawn before it
+    want_lp: List[int] = field(default_factory=list)
+    base: Any = None
+    picks: Optional[torch.Tensor] = None
+    ticket: Any = None
+
+
 class Engine:
     def __init__(self, model: Optional[str] = None, *, config=None, dtype: Union[str, torch.dtype] = "auto",
                  device: str = "cuda:0", hf_overrides: Optional[Dict[str, Any]] = None, dummy_weight: bool = False,
                  seed: int = 0, kv_tokens: Optional[int] = None, memory_ratio: float = 0.9, page_size: int = 16,
                  max_seq_len: int = 0, max_running_requests: int = 16, max_prefill_tokens: int = 4096,
-                 cuda_graphs: bool = False, poison_cache: bool = False, host_lookahead: bool = True):
+                 cuda_graphs: bool = False, poison_cache: bool = False, host_lookahead: bool = True,
+                 run_ahead: bool = True):
         self.device = require_gpu(device)
         self.dtype = parse_dtype(dtype)
         self.model, self.config, self.max_seq_len = build_model(
@@ -125,6 +138,10 @@ class Engine:
         self.last_sampled: List[tuple] = []
         # while a decode step runs, the next one is laid out on the host on the guess that the same requests go on
         self.host_lookahead = bool(host_lookahead)
+        # ... and launched too, where that guess can only fail by an end token or an abort (see ``step``)
+        self.run_ahead = bool(run_ahead)
+        self._in_flight: Optional[_InFlight] = None
+        self.run_ahead_steps = 0             # steps launched before the step before them was read
 
     # -- sizing ---------------------------------------------------------------------------------
     def _bytes_per_token(self) -> int:
@@ -184,47 +201,36 @@ class Engine:
         return not self.scheduler.idle()
 
     def step(self) -> List[RequestOutput]:
-        """Run one scheduler step; returns the requests that finished in it."""
-        plan = self.scheduler.plan()
+        """Run one scheduler step; returns the requests that finished in it.
+
+        While requests only decode, the step AFTER this one is launched before this one's tokens are read:
+        it takes its token ids on the device from this step's picks, so the device goes from one step to
+        the next without waiting for the host.  The next call then finds its step already running, launches
+        the one after it, and only reads.  A request that ends on a token the host had not seen yet (an end
+        token, an abort) has been computed one token too far; that token is dropped with the request."""
+        flight, self._in_flight = self._in_flight, None
         self._last_error = None
         self.last_sampled = []
+        plan = self.scheduler.plan_for(flight.ids) if flight is not None else []
+        if not plan:                     # nothing on the device, or every request of it has ended meanwhile
+            flight = None
+            plan = self.scheduler.plan()
         if plan:
-            entries = []
-            for e in plan:
-                live = self._live[e.request_id]
-                if not live.adopted:
-                    self.runner.adopt_request(e.request_id)
-                    live.adopted = True
-                entries.append(StepEntry(e.request_id, e.tokens, [e.count - 1] if e.sample else []))
             try:
-                logits = self.runner.step(entries)
-                sampled_ids = [e.request_id for e in plan if e.sample]
-                tokens: List[int] = []
-                if sampled_ids:
-                    lives = [self._live[r] for r in sampled_ids]
-                    plens = [len(l.prompt) for l in lives]
-                    if any(l.params.has_penalties() for l in lives):    # token histories only where penalties read them
-                        outs = [self.scheduler.tokens_of(r) for r in sampled_ids]
-                        counts = [len(o) - p for o, p in zip(outs, plens)]
-                        generated = [o[p:] for o, p in zip(outs, plens)]
-                    else:
-                        counts = [self.scheduler.num_tokens(r) - p for r, p in zip(sampled_ids, plens)]
-                        generated = None
-                    want_lp = [i for i, l in enumerate(lives) if l.params.logprobs > 0]
-                    base = logits[want_lp].cpu().numpy() if want_lp else None    # before penalties
-                    dev = self.sampler.sample(logits, [l.params for l in lives], [l.seed for l in lives], counts,
-                                              [l.prompt for l in lives], generated)
-                    if self.host_lookahead and all(e.sample and e.count == 1 for e in plan):
-                        # the step is on its way: lay out the next one on the host while it runs
-                        self.runner.prepare_decode_ahead(sampled_ids)
-                    tokens = self.runner.read_back(dev)          # (waits for the step; the status word comes along)
-                    self.d2h_bytes_last = (len(tokens) + 1) * 4
-                    for j, i in enumerate(want_lp):
-                        lives[i].logprobs.append(top_logprobs(base[j], tokens[i], lives[i].params.logprobs))
+                if flight is None:
+                    flight = self._launch(plan)
+                else:
+                    for e in plan:
+                        if e.count != 1 or e.start != flight.starts[e.request_id]:
+                            raise RuntimeError(f"request {e.request_id}: the step on the device is not the one planned")
+                following = self._launch_following(flight, plan)
+                tokens = self._read(flight, plan)
                 self.runner.check_status()
                 self.scheduler.commit(tokens)
-                self.last_sampled = [(r, t, (self._live[r].logprobs[-1] if self._live[r].params.logprobs > 0 else None))
-                                     for r, t in zip(sampled_ids, tokens)]
+                self._in_flight = following
+                self.last_sampled = [(e.request_id, t, (self._live[e.request_id].logprobs[-1]
+                                                        if self._live[e.request_id].params.logprobs > 0 else None))
+                                     for e, t in zip((e for e in plan if e.sample), tokens)]
             except (StepError, KernelError, CacheError, torch.OutOfMemoryError) as exc:
                 # the step failed on the device or for want of memory: its requests end with an error and
                 # give their pages back, the others go on (src/scheduler.rs:1436-1463).  Anything else is
@@ -232,6 +238,76 @@ class Engine:
                 self._last_error = str(exc)
                 self.scheduler.fail_step()
         return self._collect()
+
+    def _launch(self, plan, device_tokens: Optional[torch.Tensor] = None, steps_before: Optional[List[int]] = None):
+        """Put a planned step on the device, its sampling and the copies that bring the picks back included.
+        ``device_tokens``/``steps_before``: the step follows one whose picks are not on the host yet; its token
+        ids come from that tensor, and request i has drawn ``steps_before[i]`` tokens before it."""
+        entries = []
+        for e in plan:
+            live = self._live[e.request_id]
+            if not live.adopted:
+                self.runner.adopt_request(e.request_id)
+                live.adopted = True
+            entries.append(StepEntry(e.request_id, e.tokens, [e.count - 1] if e.sample else []))
+        logits = self.runner.step(entries, device_tokens)
+        flight = _InFlight([e.request_id for e in plan if e.sample],
+                           {e.request_id: e.start for e in plan})
+        if flight.ids:
+            lives = [self._live[r] for r in flight.ids]
+            plens = [len(l.prompt) for l in lives]
+            generated = None
+            if steps_before is not None:
+                flight.steps = list(steps_before)
+            elif any(l.params.has_penalties() for l in lives):       # token histories only where penalties read them
+                outs = [self.scheduler.tokens_of(r) for r in flight.ids]
+                flight.steps = [len(o) - p for o, p in zip(outs, plens)]
+                generated = [o[p:] for o, p in zip(outs, plens)]
+            else:
+                flight.steps = [self.scheduler.num_tokens(r) - p for r, p in zip(flight.ids, plens)]
+            flight.want_lp = [i for i, l in enumerate(lives) if l.params.logprobs > 0]
+            flight.base = logits[flight.want_lp].cpu().numpy() if flight.want_lp else None    # before penalties
+            flight.picks = self.sampler.sample(logits, [l.params for l in lives], [l.seed for l in lives], flight.steps,
+                                               [l.prompt for l in lives], generated)
+            flight.ticket = self.runner.begin_read_back(flight.picks)
+        return flight
+
+    def _launch_following(self, flight: "_InFlight", plan) -> Optional["_InFlight"]:
+        """With ``flight`` on the device and unread: launch the step after it, if it is certain to be one more
+        token for each of the same requests whatever ``flight`` picks short of an end token: every running
+        request is in the plan and samples, nobody waits to be admitted, none ends by length.  Otherwise
+        lay that step out on the host at least (if requests only decode), or do nothing."""
+        decoding = all(e.sample for e in plan)
+        lives = [self._live[e.request_id] for e in plan]
+        if (self.run_ahead and decoding and len(plan) == len(flight.ids) and flight.ticket is not None
+                and self.scheduler.waiting() == 0 and self.scheduler.running() == len(plan)
+                and not any(l.params.has_penalties() or l.params.logprobs > 0 for l in lives)
+                and all(self.scheduler.remaining(r) >= 2 for r in flight.ids)):
+            nxt = [PlanEntry(e.request_id, e.slot, e.start + e.count, 1, True, [0]) for e in plan]
+            try:
+                following = self._launch(nxt, flight.picks, [s + 1 for s in flight.steps])
+                self.run_ahead_steps += 1
+                return following
+            except (StepError, CacheError):
+                return None                                     # the step itself will meet the same error, and report it
+        if self.host_lookahead and decoding and all(e.count == 1 for e in plan):
+            # the step is on its way: lay out the next one on the host while it runs
+            self.runner.prepare_decode_ahead([e.request_id for e in plan])
+        return None
+
+    def _read(self, flight: "_InFlight", plan) -> List[int]:
+        """Wait for ``flight`` and return the picks of the plan's sampled entries (the plan may have lost
+        requests that ``flight`` still computed)."""
+        if not flight.ids or flight.ticket is None:
+            return []
+        picks = self.runner.finish_read_back(flight.ticket)     # (waits for the step; the status word comes along)
+        self.d2h_bytes_last = (len(picks) + 1) * 4
+        for j, i in enumerate(flight.want_lp):
+            live = self._live.get(flight.ids[i])
+            if live is not None:
+                live.logprobs.append(top_logprobs(flight.base[j], picks[i], live.params.logprobs))
+        at = {r: i for i, r in enumerate(flight.ids)}
+        return [picks[at[e.request_id]] for e in plan if e.sample]
 
     def _collect(self) -> List[RequestOutput]:
         out = []

@@ -62,7 +62,8 @@ class ModelRunner:
         self._ahead = None                   # a next step laid out on the host in advance (prepare_decode_ahead)
         self._graph_pool = None
         self.h2d_bytes_last = 0
-        self._back = None                    # pinned int32 buffer of read_back
+        self._back = [None] * 4              # pinned int32 buffers of read_back with their events, used in turn
+        self._back_turn = 0
         self._status_read = None             # the status word read_back brought along, until check_status takes it
         self.kernel_launches = 0
 
@@ -87,9 +88,20 @@ class ModelRunner:
         self.storage.manager.close(request_id)
 
     # -- the step -------------------------------------------------------------------------------
-    def prepare(self, entries: Sequence[StepEntry]):
+    def prepare(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor] = None):
         """Reserve pages, lay the step out in the pinned buffer and upload it.  Returns the context,
-        the device tensor of wanted rows and the (request, new length) pairs to commit."""
+        the device tensor of wanted rows and the (request, new length) pairs to commit.
+
+        ``device_tokens`` (int32, one for every entry, each entry bringing ONE token): the token ids are not
+        known on the host yet; they are copied on the device from this tensor, which an earlier step's
+        sampling fills, so that the step can be launched before that one has been read back."""
+        if device_tokens is not None:
+            if any(len(e.tokens) != 1 for e in entries) or device_tokens.numel() != len(entries):
+                raise StepError("token ids on the device: every entry brings exactly one token")
+            self._discard_ahead()
+            out = self._send(*self._layout_restoring(entries))
+            self.bufs.dev_section("tokens", len(entries)).copy_(device_tokens.reshape(-1))
+            return out
         ahead, self._ahead = self._ahead, None
         if ahead is not None:
             if self._ahead_matches(ahead, entries):
@@ -99,14 +111,16 @@ class ModelRunner:
                 ctx.h_tokens = tokens
                 return self._send(ctx, n_rows, commits, n_upd)
             self.storage._synced[:] = ahead["synced"]        # its table updates were never sent
+        return self._send(*self._layout_restoring(entries))
+
+    def _layout_restoring(self, entries: Sequence[StepEntry]):
         synced = self.storage._synced.copy()
         try:
-            layout = self._layout(entries)
+            return self._layout(entries)
         except Exception:
             # entries laid out before the faulty one took table updates that will never be sent
             self.storage._synced[:] = synced
             raise
-        return self._send(*layout)
 
     def prepare_decode_ahead(self, request_ids: Sequence[int]) -> None:
         """Lay out the NEXT step on the host while the current one runs, on the guess that these requests
@@ -238,11 +252,11 @@ class ModelRunner:
                 n_upd.append(0)
         return ctx, len(rows), commits, n_upd
 
-    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+    def step(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Run one step and return float32 logits [wanted, vocab] on the device, in the order of the
         entries and of their ``want`` lists.  With CUDA graphs on, the logits of a pure decode step
-        live in a buffer that the next such step overwrites."""
-        ctx, rows, commits = self.prepare(entries)
+        live in a buffer that the next such step overwrites.  ``device_tokens``: see :meth:`prepare`."""
+        ctx, rows, commits = self.prepare(entries, device_tokens)
         # Dependent launches (a kernel starts, and streams its first weights, while the kernel before it still
         # runs) are what makes the short kernels of small steps overlap.  Steps of more than 256 tokens run the
         # persistent CTA-pair product, whose grid wants every pair of SMs: with its dependents already resident
@@ -294,14 +308,27 @@ class ModelRunner:
         """A step's small int32 result (the sampled tokens) and the device status word in ONE wait: both are
         copied to pinned memory behind the step on its stream, then the stream is waited for once.  The
         status is kept for the next :meth:`check_status`, which then does not wait again."""
+        return self.finish_read_back(self.begin_read_back(values))
+
+    def begin_read_back(self, values: torch.Tensor):
+        """Queue the copies of :meth:`read_back` behind what has been launched so far and return a ticket;
+        work launched after this call does not delay them."""
         n = values.numel()
-        if self._back is None or self._back.numel() < n + 1:
-            self._back = torch.empty(max(n + 1, 257), dtype=torch.int32, pin_memory=True)
-        self._back[:n].copy_(values.reshape(-1), non_blocking=True)
-        self._back[n:n + 1].copy_(self.bufs.status.reshape(-1)[:1], non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-        self._status_read = int(self._back[n])
-        return self._back[:n].tolist()
+        k = self._back_turn = (self._back_turn + 1) % len(self._back)
+        if self._back[k] is None or self._back[k][0].numel() < n + 1:
+            self._back[k] = (torch.empty(max(n + 1, 257), dtype=torch.int32, pin_memory=True), torch.cuda.Event())
+        buf, event = self._back[k]
+        buf[:n].copy_(values.reshape(-1), non_blocking=True)
+        buf[n:n + 1].copy_(self.bufs.status.reshape(-1)[:1], non_blocking=True)
+        event.record()
+        return k, n
+
+    def finish_read_back(self, ticket) -> List[int]:
+        k, n = ticket
+        buf, event = self._back[k]
+        event.synchronize()
+        self._status_read = int(buf[n])
+        return buf[:n].tolist()
 
     def check_status(self) -> None:
         """Raise if a kernel of an earlier step flagged a bad index (this waits for the device, unless

@@ -72,16 +72,41 @@ class Scheduler:
         n = self._lib.sched_plan(self._h, self._entries.ctypes.data_as(ctypes.POINTER(ctypes.c_int64)),
                                  len(self._entries) // 5, self._tokens.ctypes.data_as(ctypes.POINTER(ctypes.c_int32)),
                                  len(self._tokens), ctypes.byref(n_tok))
+        return self._read_plan(n, n_tok.value)
+
+    def plan_for(self, request_ids: Sequence[int]) -> List[PlanEntry]:
+        """The step that is already on the device for ``request_ids`` (one token each, fed there from the last
+        step's picks): its entries for those of them that still run.  Nothing is admitted."""
+        ids = np.ascontiguousarray(request_ids, dtype=np.int64)
+        n_tok = ctypes.c_int(0)
+        n = self._lib.sched_plan_for(self._h, ids.ctypes.data_as(ctypes.POINTER(ctypes.c_int64)), len(ids),
+                                     self._entries.ctypes.data_as(ctypes.POINTER(ctypes.c_int64)), len(self._entries) // 5,
+                                     self._tokens.ctypes.data_as(ctypes.POINTER(ctypes.c_int32)), len(self._tokens),
+                                     ctypes.byref(n_tok))
+        return self._read_plan(n, n_tok.value)
+
+    def _read_plan(self, n: int, n_tok: int) -> List[PlanEntry]:
         if n < 0:
             raise RuntimeError("the scheduler's plan does not fit its buffers")
         ent = self._entries[:5 * n].tolist()             # (one conversion each: this runs between two steps)
-        toks = self._tokens[:n_tok.value].tolist()
+        toks = self._tokens[:n_tok].tolist()
         out, off = [], 0
         for i in range(n):
             rid, slot, start, count, sample = ent[5 * i:5 * i + 5]
             out.append(PlanEntry(rid, slot, start, count, bool(sample), toks[off:off + count]))
             off += count
         return out
+
+    def remaining(self, request_id: int) -> int:
+        """Tokens the request may still generate (-1: unknown or ended)."""
+        return self._lib.sched_remaining(self._h, request_id)
+
+    def waiting(self) -> int:
+        return self._lib.sched_waiting(self._h)
+
+    def running(self) -> int:
+        """Requests that hold a slot (they decode, or their prompts are under way)."""
+        return self._lib.sched_running(self._h)
 
     def commit(self, sampled: Sequence[int]) -> None:
         s = np.ascontiguousarray(sampled, dtype=np.int32)

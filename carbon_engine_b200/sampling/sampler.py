@@ -41,25 +41,29 @@ def fresh_seed() -> int:
 class Sampler:
     def __init__(self, device: torch.device):
         self.device = device
-        self._rows_host = None      # pinned staging for the per-row parameters: the copy never blocks the host
+        # pinned staging for the per-row parameters, a few in turn: the copy never blocks the host, and a
+        # buffer is rewritten only after the copy that read it has passed (two steps may be on the device)
+        self._rows_host: List[Optional[torch.Tensor]] = [None] * 4
+        self._rows_free: List[Optional["torch.cuda.Event"]] = [None] * 4
+        self._rows_turn = 0
         self._rows_dev = None
-        self._rows_free = None      # recorded after the copy: the staging buffer may be rewritten once it has passed
 
     def _upload_rows(self, blob: bytes) -> torch.Tensor:
         n = len(blob)
-        if self._rows_host is None or self._rows_host.numel() < n:
-            size = max(4096, 2 * n)
-            self._rows_host = torch.empty(size, dtype=torch.uint8, pin_memory=self.device.type == "cuda")
-            self._rows_dev = torch.empty(size, dtype=torch.uint8, device=self.device)
-            self._rows_free = None
-        if self._rows_free is not None:
-            self._rows_free.synchronize()
-        self._rows_host[:n] = torch.frombuffer(bytearray(blob), dtype=torch.uint8)
-        self._rows_dev[:n].copy_(self._rows_host[:n], non_blocking=True)
+        if self._rows_dev is None or self._rows_dev.numel() < n:
+            self._rows_dev = torch.empty(max(4096, 2 * n), dtype=torch.uint8, device=self.device)
+        k = self._rows_turn = (self._rows_turn + 1) % len(self._rows_host)
+        if self._rows_host[k] is None or self._rows_host[k].numel() < n:
+            self._rows_host[k] = torch.empty(max(4096, 2 * n), dtype=torch.uint8, pin_memory=self.device.type == "cuda")
+            self._rows_free[k] = None
+        if self._rows_free[k] is not None:
+            self._rows_free[k].synchronize()
+        self._rows_host[k][:n] = torch.frombuffer(bytearray(blob), dtype=torch.uint8)
+        self._rows_dev[:n].copy_(self._rows_host[k][:n], non_blocking=True)
         if self.device.type == "cuda":
-            if self._rows_free is None:
-                self._rows_free = torch.cuda.Event()
-            self._rows_free.record()
+            if self._rows_free[k] is None:
+                self._rows_free[k] = torch.cuda.Event()
+            self._rows_free[k].record()
         return self._rows_dev[:n]
 
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], seeds: Sequence[int],

@@ -288,6 +288,40 @@ def test_abort_waiting_and_running():
     cm.check()
 
 
+def test_the_step_after_the_last_one_is_planned_for_the_requests_it_was_launched_for():
+    """``plan_for``: the engine has put the step after the last one on the device already, for the requests
+    that decoded; the scheduler lays out exactly that step for those that still run and admits nothing."""
+    cm, s = make(pages=32, max_running=3, budget=8)
+    s.submit(1, [1, 2, 3], max_tokens=6)
+    s.submit(2, [4, 5], max_tokens=6)
+    s.submit(3, [6], max_tokens=3, stop_token_ids=[42])
+    assert s.waiting() == 3 and s.remaining(1) == 6 and s.remaining(77) == -1
+    s.plan(); s.commit([10, 20, 30])
+    assert s.waiting() == 0 and s.running() == 3 and [s.remaining(r) for r in (1, 2, 3)] == [5, 5, 2]
+    s.submit(4, [7, 8], max_tokens=2)                         # arrives while two steps are under way
+    p = s.plan_for([1, 2, 3])
+    assert [(e.request_id, e.start, e.count, e.sample, e.tokens) for e in p] == \
+        [(1, 3, 1, True, [10]), (2, 2, 1, True, [20]), (3, 1, 1, True, [30])]
+    assert s.waiting() == 1                                   # request 4 was not admitted
+    s.commit([11, 21, 42])                                    # request 3 meets its stop token
+    assert s.pop_finished() == [(3, "stop")] and s.remaining(3) == -1
+    p = s.plan_for([1, 2, 3])                                 # the step launched for all three: 3 has ended
+    assert [(e.request_id, e.start, e.tokens) for e in p] == [(1, 4, [11]), (2, 3, [21])]
+    s.commit([12, 22])
+    assert s.abort(1)
+    p = s.plan_for([1, 2])
+    assert [(e.request_id, e.start, e.tokens) for e in p] == [(2, 4, [22])]
+    s.commit([23])
+    assert s.plan_for([1]) == [] and s.plan_for([]) == []
+    p = s.plan()                                              # the ordinary plan goes on, and admits request 4
+    assert [(e.request_id, e.start, e.count) for e in p] == [(2, 5, 1), (4, 0, 2)]
+    s.commit([24, 40])
+    run_all(s, lambda e: 5)
+    assert s.tokens_of(2)[2:] == [20, 21, 22, 23, 24, 5] and s.idle()
+    cm.check()
+    assert cm.free_pages() == 32 and cm.free_slots() == 3
+
+
 def test_stats_count_tokens():
     cm, s = make(pages=32, budget=8)
     s.submit(1, [1] * 11, max_tokens=3)

@@ -237,7 +237,8 @@ def test_host_lookahead_gives_the_same_tokens(models, graphs, name, dtype):
     kw = {} if name == "A" else dict(max_seq_len=1024, kv_tokens=4096)
 
     def run(lookahead):
-        eng = make_engine(d, dtype, name, max_running_requests=4, cuda_graphs=graphs, host_lookahead=lookahead, **kw)
+        eng = make_engine(d, dtype, name, max_running_requests=4, cuda_graphs=graphs, host_lookahead=lookahead,
+                          run_ahead=False, **kw)
         ids = [eng.add_request(p, s) for p, s in zip(prompts[:5], sps[:5])]
         done, steps, used = {}, 0, 0
         while eng.has_unfinished():
@@ -260,6 +261,71 @@ def test_host_lookahead_gives_the_same_tokens(models, graphs, name, dtype):
             assert got == plain.greedy_generate(cfg, w, p, s.max_tokens)
         else:
             check_greedy(cfg, w, p, got, dtype)
+
+
+@pytest.mark.parametrize("graphs", [False, True])
+@pytest.mark.parametrize("name,dtype", [("B", "float32"), ("D", "bfloat16"), ("E", "bfloat16")])
+def test_a_step_launched_before_the_last_one_is_read_gives_the_same_tokens(models, graphs, name, dtype):
+    """While requests only decode, the engine launches the step after the running one before it has read the
+    running one's tokens; that step takes its token ids on the device.  What the host could not know then, a
+    stop token or an abort, ends a request one computed token late, and that token is dropped.  A request
+    that ends by length, or one that waits to be admitted, makes the engine take the ordinary way.  Same
+    tokens either way (bit for bit in float32, seeded temperature rows included; bfloat16 against the plain
+    implementation, since a late admission pairs other steps with the prompt), no page or slot lost, with
+    windows that pages fall out of (B: 37 tokens, E: 200) and pages used again."""
+    from carbon_engine_b200 import SamplingParams
+    d, cfg, w = models[name]
+    rng = np.random.default_rng(33)
+    f32 = dtype == "float32"
+    lengths = (20, 5, 61, 33, 9, 47) if name == "B" else (320, 5, 410, 33, 130, 270)
+    prompts = [random_tokens(rng, n, cfg["vocab_size"]) for n in lengths]
+    new = (60, 12, 50, 7, 41, 23)
+    kw = dict(max_seq_len=512, kv_tokens=1024) if name == "B" else dict(max_seq_len=1024, kv_tokens=2048)
+    budget = 48 if name == "B" else 400
+
+    def params(stop_of_0):
+        return [SamplingParams(max_tokens=m, ignore_eos=i != 0, stop_token_ids=stop_of_0 if i == 0 else (),
+                               temperature=0.7 if f32 and i in (1, 4) else 0.0, seed=50 + i) for i, m in enumerate(new)]
+
+    def run(ahead, sps):
+        eng = make_engine(d, dtype, name, max_running_requests=4, cuda_graphs=graphs, run_ahead=ahead,
+                          max_prefill_tokens=budget, **kw)
+        ids = [eng.add_request(p, s) for p, s in zip(prompts[:5], sps[:5])]
+        done, steps = {}, 0
+        while eng.has_unfinished():
+            for out in eng.step():
+                done[out.request_id] = (out.token_ids, out.finish_reason)
+            steps += 1
+            if steps == 15:                           # a late arrival, in the middle of the others' decoding
+                ids.append(eng.add_request(prompts[5], sps[5]))
+            if steps == 30:
+                assert eng.abort(ids[2])              # ... and an abort while two steps are under way
+        eng.storage.manager.check()
+        assert eng.storage.manager.free_slots() == 4
+        assert eng.stats()["kv_pages_free"] == eng.stats()["kv_pages_total"]
+        return [done[i] for i in ids], eng.run_ahead_steps, steps
+
+    free_run, _, _ = run(False, params(()))
+    stop = free_run[0][0][17]                             # request 0 shall stop on a token it meets while it decodes
+    sps = params([stop])
+    one_by_one, used_off, steps_off = run(False, sps)
+    ahead, used_on, steps_on = run(True, sps)
+    assert used_off == 0 and used_on > 20                 # steps were really launched ahead, many times
+    # nobody was kept waiting by it: the prompts, which take several steps under this budget, and the late
+    # arrival got their turn as soon (a step later at most) as without it
+    assert abs(steps_on - steps_off) <= 3
+    cut = free_run[0][0].index(stop) + 1
+    assert one_by_one[0] == (free_run[0][0][:cut], "stop") and cut < 60
+    assert [r for _, r in ahead] == [r for _, r in one_by_one] == ["stop", "length", "abort", "length", "length", "length"]
+    assert len(ahead[2][0]) == len(one_by_one[2][0]) < 50      # the abort took effect after the same step
+    if f32:
+        assert ahead == one_by_one
+    for i, (p, (got, _)) in enumerate(zip(prompts, ahead)):
+        if sps[i].temperature == 0.0:
+            if f32:
+                assert got == plain.greedy_generate(cfg, w, p, len(got))
+            else:
+                check_greedy(cfg, w, p, got, dtype)
 
 
 def test_more_new_table_entries_than_a_steps_section_holds(models):

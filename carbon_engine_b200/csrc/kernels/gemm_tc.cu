@@ -153,7 +153,7 @@ __global__ void __launch_bounds__(THREADS, 2) gemm_tc_kernel(const __grid_consta
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     __shared__ __align__(8) uint64_t full_bar[8], empty_bar[8], acc_bar;
     __shared__ uint32_t tmem_slot;
-    __shared__ int s_ticket, s_abort;
+    __shared__ int s_ticket, s_abort, s_acc_ok;
     // NACC == 2 stands for SwiGLU: the block's 128 weight rows are 64 gate rows and the 64 up rows of the
     // same features (two TMA boxes into one tile), the product has ONE accumulator like any other, and
     // the two threads of a feature meet in the epilogue through this buffer.  K is never split then.
@@ -280,8 +280,15 @@ __global__ void __launch_bounds__(THREADS, 2) gemm_tc_kernel(const __grid_consta
         int n = n0 + (GU ? (row & 63) : row);
         int m_valid = min(BN, a.M - m0);
         ce_pdl_wait();
-        bool ok = nkb > 0 ? mbar_wait(&acc_bar, 0) : true;
-        if (!ok) { atomicExch(a.status, 5); atomicExch(&s_abort, 1); }
+        // one thread waits for the accumulators and the others take its verdict: threads that each polled for
+        // themselves could disagree at the limit and then miss one another at the barriers below
+        if (threadIdx.x == 64) {
+            bool there = nkb > 0 ? mbar_wait(&acc_bar, 0) : true;
+            if (!there) { atomicExch(a.status, 5); atomicExch(&s_abort, 1); }
+            s_acc_ok = there ? 1 : 0;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        bool ok = s_acc_ok != 0;
         if (tracing && threadIdx.x == 64) s_rec[4] = gtime();
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         uint32_t taddr = tmem + ((uint32_t)(quad * 32) << 16);
@@ -289,7 +296,6 @@ __global__ void __launch_bounds__(THREADS, 2) gemm_tc_kernel(const __grid_consta
             // Rows 64..127 of the tile hold the up values of the features whose gate values rows 0..63 hold.  The
             // two threads of a feature share each chunk of 16 tokens: the gate thread takes tokens 0..7 (and
             // needs their up values), the up thread tokens 8..15 (and needs their gate values).
-            ok = __all_sync(0xffffffffu, ok);            // tensor-memory loads and the barrier below are taken by whole warps
             bool up_row = row >= 64;
 #pragma unroll 1
             for (int c = 0; c < BN; c += 16) {

@@ -249,7 +249,9 @@ def main() -> int:
                    "l2": "inputs larger than L2 (weights over 15 GB per step)", "peaks": pk["source"]},
         "clocks": clocks.summary(t0, t1),
         "e2e": {"value": round(e2e["tokens_per_s"], 1), "unit": "tokens/s", "ms_per_step": round(e2e["ms_per_step"], 4),
-                "h2d_bytes_per_step": e2e["h2d_bytes"], "d2h_bytes_per_step": e2e["d2h_bytes"]},
+                "h2d_bytes_per_step": e2e["h2d_bytes"], "d2h_bytes_per_step": e2e["d2h_bytes"],
+                # timed steps that were launched before the step before them had been read back
+                "steps_launched_ahead": e2e["launched_ahead"]},
         "gpu_launches": main_run["launches"],
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4)},

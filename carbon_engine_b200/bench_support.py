@@ -104,16 +104,18 @@ class BenchHarness:
         torch.cuda.synchronize()
         t0 = time.perf_counter()
         h2d = d2h = 0
+        ahead0 = eng.run_ahead_steps
         for _ in range(steps):
             eng.step()
             h2d += eng.runner.h2d_bytes_last
             d2h += eng.d2h_bytes_last
         torch.cuda.synchronize()
         dt = time.perf_counter() - t0
+        ahead = eng.run_ahead_steps - ahead0
         while eng.has_unfinished():
             eng.step()
         return {"ms_per_step": dt / steps * 1e3, "tokens_per_s": batch * steps / dt, "h2d_bytes": h2d // steps,
-                "d2h_bytes": d2h // steps}
+                "d2h_bytes": d2h // steps, "launched_ahead": ahead}
 
     def serve(self, prompt_lens: List[int], new_tokens: int) -> Dict:
         """A whole workload through Engine.add_request / Engine.step: all requests are queued at once, the

@@ -161,7 +161,8 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
     ap.add_argument("--no-graphs", action="store_true")
     ap.add_argument("--prefill-only", action="store_true",
-                    help="run only the 2,048-token prefill (for profiling) and print its time")
+                    help="run only the prefill of one prompt (for profiling, and for other prompt lengths) and print its time")
+    ap.add_argument("--prefill-tokens", type=int, default=2048, help="with --prefill-only: tokens of the prompt (one step)")
     ap.add_argument("--profile", action="store_true",
                     help="instead of the contract's line: time every kernel of a decode step and of a 2,048-token prefill "
                          "with CUDA events (eager, kernels one after another) and print a table per kernel: launches, "
@@ -189,14 +190,20 @@ def main() -> int:
     if args.workload != "decode":
         return serve_workload(args, BenchHarness)
     cfg = dict(SIZES_8B, num_hidden_layers=args.layers)
-    h = BenchHarness(cfg, max_batch=2 if args.prefill_only else max(64 if not args.no_points else args.batch, args.batch),
+    if args.prefill_only:
+        T = args.prefill_tokens
+        h = BenchHarness(cfg, max_batch=2, context=max(args.context, T), new_tokens=256, graphs=not args.no_graphs,
+                         step_tokens=max(4096, T))
+        pf = h.prefill(T, 3, 2)
+        flops = prefill_flops(cfg, args.layers, T)
+        print(json.dumps({"prefill_ms": round(pf["ms"], 3), "tokens": T, "layers": args.layers,
+                          "tokens_per_s": round(T / (pf["ms"] / 1e3), 1), "tflops": round(flops / (pf["ms"] / 1e3) / 1e12, 1),
+                          "frac": round(flops / (pf["ms"] / 1e3) / (pk["bf16_tflops"] * 1e12), 4), "peaks": pk["source"]}))
+        return 0
+    h = BenchHarness(cfg, max_batch=max(64 if not args.no_points else args.batch, args.batch),
                      context=args.context,
                      new_tokens=max(256, args.steps + args.warmup + 8 + args.batch * ((args.context + 4095) // 4096 + 1)),
                      graphs=not args.no_graphs)
-    if args.prefill_only:
-        pf = h.prefill(2048, 2, 2)
-        print(json.dumps({"prefill_ms": round(pf["ms"], 3), "layers": args.layers}))
-        return 0
     if args.profile:
         prof = h.profile(args.batch, 2048, pk["hbm_gbs"], pk["bf16_tflops"])
         for part in ("decode", "prefill"):

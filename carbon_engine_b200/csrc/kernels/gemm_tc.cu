@@ -7,7 +7,8 @@
 // tokens still fill the tensor core's M dimension and stream each weight exactly once.  Both operands
 // are K-major as stored (W is [out, in], x is [tokens, in]), in 128-byte-swizzled tiles of 64 k.
 //
-// Up to 256 tokens: one CTA computes one 128 x BN output tile, optionally over a slice of K (split-K, used
+// Up to 256 tokens (128 where a product has tiles enough for the CTA pairs): one CTA computes one 128 x BN
+// output tile, optionally over a slice of K (split-K, used
 // when there are fewer tiles than SMs).  For SwiGLU the 128 rows of a tile are 64 gate rows and the 64 up
 // rows of the same features (two TMA boxes), so it is one product with one accumulator like the others,
 // and it is never split.  More tokens: persistent kernels further down (CTA pairs with cta_group::2).
@@ -1081,12 +1082,25 @@ static bool cluster_split_k() {
     return on != 0;
 }
 
+// 129 to 256 tokens: a one-block tile of 128 weight rows x 256 tokens needs 48 KB of operands per 64 k, more
+// than an SM takes in while it multiplies them; a pair's tile of 256 rows x 256 tokens needs 32 KB a block.  So
+// products with at least a dozen pair tiles go to the CTA pairs from 129 tokens on (measured at 8B sizes: a
+// 256-token step 8.26 -> 7.95 ms, a decode step at batch 256 20.9 -> 20.0 ms); fewer tiles would leave most
+// pairs idle, and the one-block kernel splits K instead.  (CE_GEMM_PAIR_MIN_TOKENS / _TILES move the bounds.)
+static bool pairs_from_129(int M, int N, int nacc) {
+    static int pair_min_tokens = getenv("CE_GEMM_PAIR_MIN_TOKENS") ? atoi(getenv("CE_GEMM_PAIR_MIN_TOKENS")) : 129;
+    static int pair_min_tiles = getenv("CE_GEMM_PAIR_MIN_TILES") ? atoi(getenv("CE_GEMM_PAIR_MIN_TILES")) : 12;
+    static int no_pairs = getenv("CE_GEMM_NO_PAIRS") ? 1 : 0;
+    long long pair_tiles = nacc == 2 ? (N + BM - 1) / BM : (N + 2 * BM - 1) / (2 * BM);
+    return M <= 256 && M >= pair_min_tokens && N >= 2 * BM && pair_tiles >= pair_min_tiles && !no_pairs;
+}
+
 // How many splits of K a product of these sizes uses (it depends on N and K only while the tokens
 // fit one tile, so a token's sums are taken in the same order whatever else is in the batch).
 extern "C" int ce_gemm_tc_tile_tokens(int M);
 extern "C" int ce_gemm_tc_splits(int M, int N, int K) {
     int kblocks = (K + BK - 1) / BK;
-    if (M > 256) return 1;
+    if (M > 256 || pairs_from_129(M, N, 1)) return 1;
     int bn = ce_gemm_tc_tile_tokens(M);
     int tiles = ((N + BM - 1) / BM) * ((M + bn - 1) / bn);
     static int target = getenv("CE_GEMM_TARGET_CTAS") ? atoi(getenv("CE_GEMM_TARGET_CTAS")) : 0;
@@ -1140,7 +1154,8 @@ extern "C" int ce_gemm_tc(const void* A, const void* W, void* C, int M, int N, i
     if (mode < 0 || mode > 3) return ce_fail(CE_ERR_ARG, "ce_gemm_tc: unknown epilogue %d", mode);
     int nacc = mode == TC_SWIGLU ? 2 : 1;
     int kblocks = (K + BK - 1) / BK;
-    if (M > 256) {       // many tokens: the persistent kernel, no split-K
+    bool early_pairs = pairs_from_129(M, N, nacc);
+    if (M > 256 || early_pairs) {       // many tokens: the persistent kernels, no split-K
         int pbn = nacc == 2 ? 128 : 256;
         long long tiles_m = (M + pbn - 1) / pbn, tiles_n = (N + BM - 1) / BM;
         if (tiles_m * tiles_n > 2147483647LL) return ce_fail(CE_ERR_SIZE, "ce_gemm_tc: too many tiles");

@@ -42,7 +42,7 @@ def _status_text(code: int) -> str:
 
 class ModelRunner:
     #: steps of more tokens than this run their kernels strictly one after another (see ``step``)
-    DEPENDENT_LAUNCH_MAX_TOKENS = 256
+    DEPENDENT_LAUNCH_MAX_TOKENS = 128
 
     def __init__(self, model, storage: CacheStorage, max_step_tokens: int):
         self.model, self.storage = model, storage
@@ -258,12 +258,12 @@ class ModelRunner:
         live in a buffer that the next such step overwrites.  ``device_tokens``: see :meth:`prepare`."""
         ctx, rows, commits = self.prepare(entries, device_tokens)
         # Dependent launches (a kernel starts, and streams its first weights, while the kernel before it still
-        # runs) are what makes the short kernels of small steps overlap.  Steps of more than 256 tokens run the
+        # runs) are what makes the short kernels of small steps overlap.  Steps of more than 128 tokens may run the
         # persistent CTA-pair product, whose grid wants every pair of SMs: with its dependents already resident
         # and waiting beside it, such a step was seen, rarely (once in a few thousand layers at 4,096 tokens a
         # step), never to finish: the pair kernel did not complete although all of its blocks that ran had left,
-        # and the next kernel's blocks waited for it for good.  Large steps gain next to nothing from the
-        # overlap, so they run without it.
+        # and the next kernel's blocks waited for it for good.  Large steps gain little from the overlap, so
+        # they run without it.
         ops.set_dependent_launches(ctx.T <= self.DEPENDENT_LAUNCH_MAX_TOKENS and os.environ.get("CE_PDL", "1") != "0")
         if self.graphs_enabled and ctx.n_decode == ctx.B and all(len(e.want) == 1 for e in entries):
             logits = self._replay_decode(ctx, rows)

@@ -541,9 +541,12 @@ def tc_product(a, w, mode, N, x0=None):
 
 @pytest.mark.parametrize("M,N,K", [(1, 128, 64), (8, 256, 4096), (16, 96, 80), (17, 301, 136), (64, 4096, 512), (100, 200, 1000),
                                    (256, 384, 256), (300, 520, 192), (5, 1000, 2048), (2048, 512, 256), (1000, 5120, 128),
-                                   (257, 19000, 64)])
+                                   (257, 19000, 64), (200, 4096, 512), (130, 3200, 192), (256, 1600, 128)])
 def test_tcgen05_product_all_epilogues(ops, M, N, K):
+    """The last three sizes have 129 to 256 tokens and at least a dozen tiles of a CTA pair (the third only as a
+    SwiGLU product): they go to the pair kernel, with one partly filled tile of tokens."""
     torch.manual_seed(M * 7 + N)
+    pairs_before = ops.kernel_counts().get("gemm_tc_pair_kernel", 0)
     a = torch.randn(M, K, device=dev()).to(torch.bfloat16)
     w = (torch.randn(N, K, device=dev()) / math.sqrt(K)).to(torch.bfloat16)
     ref = a.double().cpu() @ w.double().cpu().T
@@ -555,6 +558,11 @@ def test_tcgen05_product_all_epilogues(ops, M, N, K):
     g = a.double().cpu() @ w2[:N].double().cpu().T
     u = a.double().cpu() @ w2[N:].double().cpu().T
     assert rel_err(tc_product(a, w2, ops.GEMM_SWIGLU, N), g * torch.sigmoid(g) * u) < 1e-2
+    pair_launches = ops.kernel_counts().get("gemm_tc_pair_kernel", 0) - pairs_before
+    want_pairs = {(200, 4096, 512): 4, (130, 3200, 192): 4, (256, 1600, 128): 1, (256, 384, 256): 0, (100, 200, 1000): 0,
+                  (64, 4096, 512): 0, (300, 520, 192): 4}
+    if (M, N, K) in want_pairs:
+        assert pair_launches == want_pairs[(M, N, K)], pair_launches
 
 
 @pytest.mark.parametrize("M,N,K", [(9, 256, 4096), (48, 520, 4096), (128, 256, 8192), (200, 384, 12288)])

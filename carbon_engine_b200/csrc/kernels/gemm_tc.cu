@@ -1086,7 +1086,8 @@ static bool cluster_split_k() {
 // than an SM takes in while it multiplies them; a pair's tile of 256 rows x 256 tokens needs 32 KB a block.  So
 // products with at least a dozen pair tiles go to the CTA pairs from 129 tokens on (measured at 8B sizes: a
 // 256-token step 8.26 -> 7.95 ms, a decode step at batch 256 20.9 -> 20.0 ms); fewer tiles would leave most
-// pairs idle, and the one-block kernel splits K instead.  (CE_GEMM_PAIR_MIN_TOKENS / _TILES move the bounds.)
+// pairs idle, and the one-block kernel splits K instead; for 65 to 128 tokens the pairs were slower (batch 128:
+// 13.9 against 12.9 ms a step).  (CE_GEMM_PAIR_MIN_TOKENS / _TILES move the bounds.)
 static bool pairs_from_129(int M, int N, int nacc) {
     static int pair_min_tokens = getenv("CE_GEMM_PAIR_MIN_TOKENS") ? atoi(getenv("CE_GEMM_PAIR_MIN_TOKENS")) : 129;
     static int pair_min_tiles = getenv("CE_GEMM_PAIR_MIN_TILES") ? atoi(getenv("CE_GEMM_PAIR_MIN_TILES")) : 12;

@@ -153,6 +153,9 @@ class ModelRunner:
     def _send(self, ctx, n_rows: int, commits, n_upd):
         b = self.bufs
         self.h2d_bytes_last = b.upload()
+        prof = ops.profiling()
+        if prof is not None:
+            prof.mark()                  # the layout on the host and the upload are not the first kernel's time
         for g, n in enumerate(n_upd):
             if n:
                 ops.scatter_i32(self.storage.device_tables[g], b.dev_section(f"upd_idx{g}", n),

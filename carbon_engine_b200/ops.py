@@ -90,6 +90,14 @@ class KernelProfile:
     def note_work(self, nbytes: int, flops: int) -> None:
         self._work = (int(nbytes), int(flops))
 
+    def mark(self) -> None:
+        """The next launch's time counts from here (the step function marks the point where a step's host
+        work and upload are done, so that they are not charged to the step's first kernel)."""
+        import torch
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record()
+        self.records.append((None, ev, 0, 0))
+
     def _launched(self, n: int) -> None:
         import torch
         ev = torch.cuda.Event(enable_timing=True)
@@ -105,6 +113,8 @@ class KernelProfile:
         for name, ev, nbytes, flops in self.records:
             us = prev.elapsed_time(ev) * 1e3
             prev = ev
+            if name is None:             # a mark: what came before it is nobody's
+                continue
             a = agg.setdefault(name, [0, 0.0, 0, 0])
             a[0] += 1; a[1] += us; a[2] += nbytes; a[3] += flops
             total += us

@@ -90,6 +90,12 @@ class CacheManager:
         """Positions below ``new_len`` are written; windowed groups give back pages now behind the window."""
         self._check(self._lib.cm_commit(self._h, request_id, new_len), f"commit({request_id}, {new_len})")
 
+    def commit_many(self, request_ids: np.ndarray, new_lens: np.ndarray) -> None:
+        """:meth:`commit` for several requests (int64 ids, int32 lengths) in one call."""
+        n = len(request_ids)
+        self._check(self._lib.cm_commit_many(self._h, request_ids.ctypes.data_as(ctypes.POINTER(ctypes.c_int64)),
+                                             new_lens.ctypes.data_as(ctypes.POINTER(ctypes.c_int32)), n), f"commit of {n} requests")
+
     def close(self, request_id: int) -> None:
         self._check(self._lib.cm_close(self._h, request_id), f"close({request_id})")
 
@@ -98,6 +104,10 @@ class CacheManager:
 
     def length_of(self, request_id: int) -> int:
         return self._check(self._lib.cm_length_of(self._h, request_id), f"length_of({request_id})")
+
+    def reserved_of(self, request_id: int) -> int:
+        """Positions the request holds pages for (at least its length)."""
+        return self._check(self._lib.cm_reserved_of(self._h, request_id), f"reserved_of({request_id})")
 
     def has(self, request_id: int) -> bool:
         return self._lib.cm_slot_of(self._h, request_id) >= 0

@@ -3,6 +3,7 @@
 
 #include "cache_manager.h"
 #include "scheduler.h"
+#include "step_layout.h"
 
 using namespace carbon;
 
@@ -23,6 +24,15 @@ void cm_destroy(void* h) { delete (CacheManager*)h; }
 int cm_open(void* h, int64_t id) { return ((CacheManager*)h)->open(id); }
 int cm_reserve(void* h, int64_t id, int new_len) { return ((CacheManager*)h)->reserve(id, new_len); }
 int cm_commit(void* h, int64_t id, int new_len) { return ((CacheManager*)h)->commit(id, new_len); }
+// commit for n requests at once; returns the first status that is not CACHE_OK (the others are still committed)
+int cm_commit_many(void* h, const int64_t* ids, const int32_t* new_lens, int n) {
+    int first = CACHE_OK;
+    for (int i = 0; i < n; ++i) {
+        int rc = ((CacheManager*)h)->commit(ids[i], new_lens[i]);
+        if (rc != CACHE_OK && first == CACHE_OK) first = rc;
+    }
+    return first;
+}
 int cm_close(void* h, int64_t id) { return ((CacheManager*)h)->close(id); }
 int cm_slot_of(void* h, int64_t id) { return ((CacheManager*)h)->slot_of(id); }
 int cm_length_of(void* h, int64_t id) { return ((CacheManager*)h)->length_of(id); }
@@ -114,5 +124,9 @@ void sched_stats(void* h, int64_t* out /* 7 values */) {
     out[0] = s.steps; out[1] = s.prefill_tokens; out[2] = s.decode_tokens; out[3] = s.finished; out[4] = s.failed;
     out[5] = s.running; out[6] = s.waiting;
 }
+
+// ---- step layout ---------------------------------------------------------------------------
+// `args`: a StepLayoutArgs (step_layout.h), field for field.  Returns 0, a LayoutStatus or a CacheStatus.
+int step_layout(void* cache, const void* args) { return layout_step(*(CacheManager*)cache, *(const StepLayoutArgs*)args); }
 
 }  // extern "C"

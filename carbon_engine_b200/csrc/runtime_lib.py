@@ -20,6 +20,7 @@ _SIGNATURES = {
     "cm_open": (_i, [_p, _i64]),
     "cm_reserve": (_i, [_p, _i64, _i]),
     "cm_commit": (_i, [_p, _i64, _i]),
+    "cm_commit_many": (_i, [_p, _pi64, _pi32, _i]),
     "cm_close": (_i, [_p, _i64]),
     "cm_slot_of": (_i, [_p, _i64]),
     "cm_length_of": (_i, [_p, _i64]),
@@ -32,6 +33,7 @@ _SIGNATURES = {
     "cm_pages_to_reserve": (_i, [_p, _i64, _i, _i]),
     "cm_table": (_pi32, [_p, _i]),
     "cm_check": (_i, [_p]),
+    "step_layout": (_i, [_p, _p]),
     "sched_create": (_p, [_p, _i, _i, _i, _i, _pi, _i]),
     "sched_destroy": (None, [_p]),
     "sched_submit": (_i, [_p, _i64, _pi32, _i, _i, _i, _pi32, _i]),
@@ -64,3 +66,12 @@ def runtime() -> ctypes.CDLL:
                 fn.argtypes = args
             _lib = lib
     return _lib
+
+
+class StepLayoutArgs(ctypes.Structure):
+    """``carbon::StepLayoutArgs`` of csrc/runtime/step_layout.h, field for field."""
+    _fields_ = [("n", _i), ("ids", _p), ("counts", _p), ("tokens", _p), ("want_counts", _p), ("wants", _p),
+                ("max_step_tokens", _i),
+                ("tok", _p), ("pos", _p), ("seq_of_token", _p), ("seq_slot", _p), ("q_start", _p), ("ctx_len", _p), ("rows", _p),
+                ("synced", _p), ("upd_idx", _p), ("upd_val", _p), ("upd_stride", _i), ("n_upd", _p),
+                ("out_ids", _p), ("out_slot", _p), ("out_ctx_before", _p), ("out_new_len", _p), ("out", _p), ("detail", _p)]

@@ -94,7 +94,6 @@ class StepContext:
         self.ctx_len = bufs.dev_section("ctx_len", B)
         self.status = bufs.status
         self.block_tables = block_tables
-        self.h_tokens: List[int] = []
         self.h_slots: List[int] = []
         self.h_q_start: List[int] = []       # B + 1 entries
         self.h_ctx_before: List[int] = []    # tokens of each sequence already in the cache

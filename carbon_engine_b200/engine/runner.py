@@ -7,6 +7,7 @@ by either a prefill batch or a decode batch; here one call takes any mixture.
 """
 from __future__ import annotations
 
+import ctypes
 import os
 from typing import List, Optional, Sequence
 
@@ -40,6 +41,56 @@ def _status_text(code: int) -> str:
     return _STATUS.get(code, "unknown")
 
 
+class _Commits:
+    """The requests of a laid-out step with their new lengths, to be committed once the step is on its way;
+    iterates as (request, new length) pairs."""
+
+    def __init__(self, ids: np.ndarray, new_lens: np.ndarray):
+        self.ids, self.new_lens = ids, new_lens
+
+    def __iter__(self):
+        return iter(zip(self.ids.tolist(), self.new_lens.tolist()))
+
+    def __len__(self):
+        return len(self.ids)
+
+
+class _NativeLayout:
+    """The arrays the host runtime's ``step_layout`` reads and fills, made once: the flattened entries, the
+    block-table entries a step adds, the per-sequence results; and its argument block, whose pointers into the
+    pinned buffer's sections never change."""
+
+    def __init__(self, bufs: StepBuffers, storage: CacheStorage, max_step_tokens: int):
+        from ..csrc.runtime_lib import StepLayoutArgs, runtime
+        self.lib = runtime()
+        n, groups = storage.max_requests, max(len(storage.groups), 1)
+        self.ids = np.zeros(n, dtype=np.int64)
+        self.counts = np.zeros(n, dtype=np.int32)
+        self.want_counts = np.zeros(n, dtype=np.int32)
+        self.tokens = np.zeros(max_step_tokens, dtype=np.int32)
+        self.wants = np.zeros(max_step_tokens, dtype=np.int32)
+        stride = n * storage.max_pages_per_request          # every entry of every row: a step can never add more
+        self.upd_idx = np.zeros((groups, stride), dtype=np.int32)
+        self.upd_val = np.zeros((groups, stride), dtype=np.int32)
+        self.n_upd = np.zeros(groups, dtype=np.int32)
+        self.out_ids = np.zeros(n, dtype=np.int64)
+        self.out_slot = np.zeros(n, dtype=np.int32)
+        self.out_ctx_before = np.zeros(n, dtype=np.int32)
+        self.out_new_len = np.zeros(n, dtype=np.int32)
+        self.out = np.zeros(8, dtype=np.int32)
+        self.detail = np.zeros(3, dtype=np.int64)
+        a = self.args = StepLayoutArgs()
+        ptr = lambda arr: arr.ctypes.data
+        a.ids, a.counts, a.tokens, a.want_counts, a.wants = map(ptr, (self.ids, self.counts, self.tokens, self.want_counts, self.wants))
+        a.max_step_tokens = int(max_step_tokens)
+        a.tok, a.pos, a.seq_of_token = (ptr(bufs.host_section(k)) for k in ("tokens", "positions", "seq_of_token"))
+        a.seq_slot, a.q_start, a.ctx_len, a.rows = (ptr(bufs.host_section(k)) for k in ("seq_slot", "q_start", "ctx_len", "rows"))
+        a.synced = ptr(storage._synced)
+        a.upd_idx, a.upd_val, a.upd_stride, a.n_upd = ptr(self.upd_idx), ptr(self.upd_val), stride, ptr(self.n_upd)
+        a.out_ids, a.out_slot, a.out_ctx_before, a.out_new_len = map(ptr, (self.out_ids, self.out_slot, self.out_ctx_before, self.out_new_len))
+        a.out, a.detail = ptr(self.out), ptr(self.detail)
+
+
 class ModelRunner:
     #: steps of more tokens than this run their kernels strictly one after another (see ``step``)
     DEPENDENT_LAUNCH_MAX_TOKENS = 128
@@ -66,6 +117,7 @@ class ModelRunner:
         self._back_turn = 0
         self._status_read = None             # the status word read_back brought along, until check_status takes it
         self.kernel_launches = 0
+        self._native = _NativeLayout(self.bufs, storage, self.max_step_tokens)
 
     # -- requests -------------------------------------------------------------------------------
     def open_request(self, request_id: int) -> int:
@@ -90,7 +142,7 @@ class ModelRunner:
     # -- the step -------------------------------------------------------------------------------
     def prepare(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor] = None):
         """Reserve pages, lay the step out in the pinned buffer and upload it.  Returns the context,
-        the device tensor of wanted rows and the (request, new length) pairs to commit.
+        the device tensor of wanted rows and the requests with their new lengths to commit.
 
         ``device_tokens`` (int32, one for every entry, each entry bringing ONE token): the token ids are not
         known on the host yet; they are copied on the device from this tensor, which an earlier step's
@@ -108,7 +160,6 @@ class ModelRunner:
                 ctx, n_rows, commits, n_upd = ahead["layout"]
                 tokens = [e.tokens[0] for e in entries]
                 self.bufs.host_section("tokens")[:len(tokens)] = np.asarray(tokens, dtype=np.int32)
-                ctx.h_tokens = tokens
                 return self._send(ctx, n_rows, commits, n_upd)
             self.storage._synced[:] = ahead["synced"]        # its table updates were never sent
         return self._send(*self._layout_restoring(entries))
@@ -168,92 +219,85 @@ class ModelRunner:
         ops.scatter_i32(self.storage.device_tables[group], d_idx, d_val)
 
     def _layout(self, entries: Sequence[StepEntry]):
-        """Checks, page reservations and the step's layout in the pinned host buffer (nothing is sent)."""
-        mgr = self.storage.manager
-        if not entries:
+        """Checks, page reservations and the step's layout in the pinned host buffer (nothing is sent).  The
+        work is done by the host runtime (csrc/runtime/step_layout.cpp); here the entries are flattened into
+        its arrays, its errors become exceptions, and the mixers plan their own tables."""
+        n = len(entries)
+        if n == 0:
             raise StepError("a step needs at least one entry")
-        if len(entries) > self.storage.max_requests:
-            raise StepError(f"{len(entries)} entries, but only {self.storage.max_requests} requests may be live")
-        order = sorted(range(len(entries)), key=lambda i: 0 if len(entries[i].tokens) == 1 else 1)
-        T = sum(len(e.tokens) for e in entries)
-        if T > self.max_step_tokens:
-            raise StepError(f"{T} tokens in one step, but the engine was built for {self.max_step_tokens}")
-        seen = set()
-        if sum(len(e.want) for e in entries) > T:
-            raise StepError("more wanted places than tokens in the step (a place is named twice)")
-        for e in entries:
-            if len(e.tokens) == 0:
+        if n > self.storage.max_requests:
+            raise StepError(f"{n} entries, but only {self.storage.max_requests} requests may be live")
+        L = self._native
+        T = W = 0
+        for i, e in enumerate(entries):
+            c, w = len(e.tokens), len(e.want)
+            if c == 0:
                 raise StepError(f"request {e.request_id}: an entry needs at least one token")
-            if e.request_id in seen:
-                raise StepError(f"request {e.request_id} appears twice in one step")
-            seen.add(e.request_id)
-            for w in e.want:
-                if not 0 <= w < len(e.tokens):
-                    raise StepError(f"request {e.request_id}: wanted place {w} is outside its {len(e.tokens)} tokens")
-
+            if T + c > self.max_step_tokens:
+                raise StepError(f"{sum(len(x.tokens) for x in entries)} tokens in one step, but the engine was built for "
+                                f"{self.max_step_tokens}")
+            if W + w > self.max_step_tokens:
+                raise StepError("more wanted places than tokens in the step (a place is named twice)")
+            L.ids[i], L.counts[i], L.want_counts[i] = e.request_id, c, w
+            L.tokens[T:T + c] = e.tokens
+            if w:
+                L.wants[W:W + w] = e.want
+            T += c
+            W += w
         b = self.bufs
         b.wait_host_free()
-        h_tok, h_pos, h_seq = b.host_section("tokens"), b.host_section("positions"), b.host_section("seq_of_token")
-        h_slot, h_qs, h_ctx = b.host_section("seq_slot"), b.host_section("q_start"), b.host_section("ctx_len")
-        ctx = StepContext(b, T, len(entries), self.dtype, self.device, self.storage.device_tables)
+        L.args.n = n
+        code = L.lib.step_layout(self.storage.manager.handle, ctypes.byref(L.args))
+        if code != 0:
+            self._raise_layout_error(code, L.detail.tolist())
+        T, n_rows, n_decode, max_position, max_ctx = L.out[:5].tolist()
+        ctx = StepContext(b, T, n, self.dtype, self.device, self.storage.device_tables)
         ctx.fast_attention = self.fast_attention
-        commits = []
-        starts_sorted = {}
-        upd = [([], []) for _ in self.storage.groups]
-        off = 0
-        for bi, i in enumerate(order):
-            e = entries[i]
-            n = len(e.tokens)
-            start = mgr.length_of(e.request_id)
-            slot = mgr.slot_of(e.request_id)
-            mgr.reserve(e.request_id, start + n)
-            h_tok[off:off + n] = np.asarray(e.tokens, dtype=np.int32)
-            h_pos[off:off + n] = np.arange(start, start + n, dtype=np.int32)
-            h_seq[off:off + n] = bi
-            h_slot[bi] = slot
-            h_qs[bi] = off
-            h_ctx[bi] = start + n
-            starts_sorted[i] = off
-            ctx.h_slots.append(slot)
-            ctx.h_q_start.append(off)
-            ctx.h_ctx_before.append(start)
-            if n == 1 and bi == ctx.n_decode:
-                ctx.n_decode += 1
-            ctx.max_position = max(ctx.max_position, start + n - 1)
-            ctx.max_ctx = max(ctx.max_ctx, start + n)
-            commits.append((e.request_id, start + n))
-            for g in range(len(self.storage.groups)):
-                u = self.storage.pending_table_updates(g, slot, start + n)
-                if u is not None:
-                    upd[g][0].append(u[0]); upd[g][1].append(u[1])
-            off += n
-        h_qs[len(entries)] = off
-        ctx.h_q_start.append(off)
+        ctx.h_slots = L.out_slot[:n].tolist()
+        ctx.h_q_start = b.host_section("q_start")[:n + 1].tolist()
+        ctx.h_ctx_before = L.out_ctx_before[:n].tolist()
+        ctx.n_decode, ctx.max_position, ctx.max_ctx = n_decode, max_position, max_ctx
+        commits = _Commits(L.out_ids[:n].copy(), L.out_new_len[:n].copy())
         for key, mixer in self._planners.items():
             ctx.plans[key] = mixer.plan_step(ctx)
-        ctx.h_tokens = h_tok[:T].tolist()
-
-        rows: List[int] = []
-        for i, e in enumerate(entries):
-            rows.extend(starts_sorted[i] + w for w in e.want)
-        h_rows = b.host_section("rows")
-        h_rows[:len(rows)] = np.asarray(rows, dtype=np.int32) if rows else 0
         n_upd = []
         for g in range(len(self.storage.groups)):
-            if upd[g][0]:
-                idx = np.concatenate(upd[g][0]); val = np.concatenate(upd[g][1])
+            k = int(L.n_upd[g])
+            if k:
+                idx, val = L.upd_idx[g, :k], L.upd_val[g, :k]
                 cap = len(b.host_section(f"upd_idx{g}"))
-                if len(idx) > cap:
+                if k > cap:
                     # more new table entries than a step's section holds (requests that arrive with long contexts
                     # already in the cache): the surplus goes to the device tables at once, by a copy of its own
                     self._write_table_entries(g, idx[cap:], val[cap:])
-                    idx, val = idx[:cap], val[:cap]
-                b.host_section(f"upd_idx{g}")[:len(idx)] = idx
-                b.host_section(f"upd_val{g}")[:len(val)] = val
-                n_upd.append(len(idx))
-            else:
-                n_upd.append(0)
-        return ctx, len(rows), commits, n_upd
+                    idx, val, k = idx[:cap], val[:cap], cap
+                b.host_section(f"upd_idx{g}")[:k] = idx
+                b.host_section(f"upd_val{g}")[:k] = val
+            n_upd.append(k)
+        return ctx, n_rows, commits, n_upd
+
+    @staticmethod
+    def _raise_layout_error(code: int, detail) -> None:
+        from ..cache.manager import CacheError, OutOfPages
+        if code == -101:
+            raise StepError("a step needs at least one entry")
+        if code == -102:
+            raise StepError(f"{detail[0]} entries, but only {detail[1]} requests may be live")
+        if code == -103:
+            raise StepError(f"{detail[0]} tokens in one step, but the engine was built for {detail[1]}")
+        if code == -104:
+            raise StepError("more wanted places than tokens in the step (a place is named twice)")
+        if code == -105:
+            raise StepError(f"request {detail[0]}: an entry needs at least one token")
+        if code == -106:
+            raise StepError(f"request {detail[0]} appears twice in one step")
+        if code == -107:
+            raise StepError(f"request {detail[0]}: wanted place {detail[1]} is outside its {detail[2]} tokens")
+        what = f"reserve({detail[0]}, {detail[1]})"
+        if code == -4:
+            raise OutOfPages(f"{what}: out of pages")
+        from ..cache.manager import _MESSAGES
+        raise CacheError(f"{what}: {_MESSAGES.get(code, code)}")
 
     def step(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Run one step and return float32 logits [wanted, vocab] on the device, in the order of the
@@ -273,8 +317,7 @@ class ModelRunner:
         else:
             x = self.model.forward(ctx, self.storage)
             logits = self.model.logits(ctx, x, rows)
-        for request_id, new_len in commits:
-            self.storage.manager.commit(request_id, new_len)
+        self.storage.manager.commit_many(commits.ids, commits.new_lens)
         return logits
 
     # -- CUDA graphs for decode steps -----------------------------------------------------------

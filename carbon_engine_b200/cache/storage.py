@@ -72,7 +72,8 @@ class CacheStorage:
         self.manager = CacheManager(groups, max_requests, self.max_pages_per_request)
         self.device_tables = [torch.full((max_requests, self.max_pages_per_request), -1, dtype=torch.int32, device=device)
                               for _ in groups]
-        # per group and slot: how many leading table entries the device copy already has
+        # per group and slot: how many leading table entries the device copy already has (kept up by the host
+        # runtime's step layout, which gathers the entries a step adds; int64, C-contiguous: it holds a pointer to it)
         self._synced = np.zeros((max(len(groups), 1), max_requests), dtype=np.int64)
 
     def view(self, call: LayerCall) -> LayerCacheView:
@@ -94,18 +95,6 @@ class CacheStorage:
     def slot_opened(self, slot: int) -> None:
         """A new request took ``slot``: its table rows start over."""
         self._synced[:, slot] = 0
-
-    def pending_table_updates(self, group: int, slot: int, new_len: int):
-        """(flat indices, page ids) of the table entries of ``slot`` the device does not have yet."""
-        ps = self.groups[group].page_size
-        hi = (new_len + ps - 1) // ps
-        lo = int(self._synced[group, slot])
-        if hi <= lo:
-            return None
-        row = self.manager.table(group)[slot, lo:hi]
-        idx = np.arange(lo, hi, dtype=np.int32) + slot * self.max_pages_per_request
-        self._synced[group, slot] = hi
-        return idx, row
 
     def state_bytes(self) -> int:
         """Bytes of the fixed-size per-request state tensors (all slots)."""

@@ -98,7 +98,7 @@ def gemm_bf16(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int) ->
         return False
     ops._ok(k.ce_gemm_tc(a.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), out.stride(0), mode,
                          ws.scratch.data_ptr(), ws.scratch.numel(), ws.counters.data_ptr(), ws.counters.numel(),
-                         ws.status.data_ptr(), torch.cuda.current_stream().cuda_stream))
+                         ws.status.data_ptr(), ops._stream()))
     return True
 
 
@@ -112,7 +112,7 @@ def attention_bf16(ctx, plan, qkv, out, cache, table, nh, nkv, d, window, scale)
     if not attention_supported(d, qkv.shape[1]):
         return False
     k = kernels()
-    stream = torch.cuda.current_stream().cuda_stream
+    stream = ops._stream()
     args = (cache.page_size, table.shape[1], cache.k_pool.shape[0], int(window), float(scale))
     if ctx.n_decode > 0:
         splits = plan.decode_splits

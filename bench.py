@@ -202,7 +202,7 @@ def main() -> int:
         return 0
     h = BenchHarness(cfg, max_batch=max(64 if not args.no_points else args.batch, args.batch),
                      context=args.context,
-                     new_tokens=max(256, args.steps + args.warmup + 8 + args.batch * ((args.context + 4095) // 4096 + 1)),
+                     new_tokens=max(256, args.steps + max(args.warmup, 32) + 8 + args.batch * ((args.context + 4095) // 4096 + 1)),
                      graphs=not args.no_graphs)
     if args.profile:
         prof = h.profile(args.batch, 2048, pk["hbm_gbs"], pk["bf16_tflops"])
@@ -226,6 +226,7 @@ def main() -> int:
     main_run = h.decode(args.batch, args.steps, args.warmup)
     t1 = clocks.mark()
     e2e = h.decode_e2e(args.batch, args.steps, args.warmup)
+    t2 = clocks.mark()
     points, prefill = {}, None
     if not args.no_points:
         pf = h.prefill(2048, 3, 3)
@@ -258,7 +259,9 @@ def main() -> int:
         "e2e": {"value": round(e2e["tokens_per_s"], 1), "unit": "tokens/s", "ms_per_step": round(e2e["ms_per_step"], 4),
                 "h2d_bytes_per_step": e2e["h2d_bytes"], "d2h_bytes_per_step": e2e["d2h_bytes"],
                 # timed steps that were launched before the step before them had been read back
-                "steps_launched_ahead": e2e["launched_ahead"]},
+                "steps_launched_ahead": e2e["launched_ahead"],
+                # over the whole e2e run: its prompts' prefill (which may meet the power cap), warm-up and timed steps
+                "clocks": clocks.summary(t1, t2)},
         "gpu_launches": main_run["launches"],
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4)},

@@ -84,6 +84,9 @@ class BenchHarness:
         """Through Engine.add_request / Engine.step: real prompts are prefilled, then ``steps`` decode
         steps are timed on the host clock between two synchronisations."""
         eng = self.engine
+        # The prompts' prefill just before draws the most power a step can; the clocks need some tens of
+        # milliseconds of decoding to settle again, so at least 32 steps are left untimed.
+        warmup = max(warmup, 32)
         # long enough that no request ends inside the timed region: a request whose prompt is done decodes
         # through every step that the later prompts' portions take
         prompt_steps = batch * ((self.context + eng.max_step_tokens - 1) // eng.max_step_tokens + 1)

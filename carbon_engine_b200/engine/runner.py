@@ -115,6 +115,7 @@ class ModelRunner:
         self.h2d_bytes_last = 0
         self._back = [None] * 4              # pinned int32 buffers of read_back with their events, used in turn
         self._back_turn = 0
+        self._copy_stream = None             # the stream the read-back copies run on
         self._status_read = None             # the status word read_back brought along, until check_status takes it
         self.kernel_launches = 0
         self._native = _NativeLayout(self.bufs, storage, self.max_step_tokens)
@@ -357,22 +358,31 @@ class ModelRunner:
         return self.finish_read_back(self.begin_read_back(values))
 
     def begin_read_back(self, values: torch.Tensor):
-        """Queue the copies of :meth:`read_back` behind what has been launched so far and return a ticket;
-        work launched after this call does not delay them."""
+        """Queue the copies of :meth:`read_back` and return a ticket.  They run on a stream of their own, behind
+        what has been launched so far on the current one: the upload and the kernels of the NEXT step, launched
+        after this call, neither wait for them nor delay them."""
         n = values.numel()
         k = self._back_turn = (self._back_turn + 1) % len(self._back)
         if self._back[k] is None or self._back[k][0].numel() < n + 1:
-            self._back[k] = (torch.empty(max(n + 1, 257), dtype=torch.int32, pin_memory=True), torch.cuda.Event())
-        buf, event = self._back[k]
-        buf[:n].copy_(values.reshape(-1), non_blocking=True)
-        buf[n:n + 1].copy_(self.bufs.status.reshape(-1)[:1], non_blocking=True)
-        event.record()
+            self._back[k] = (torch.empty(max(n + 1, 257), dtype=torch.int32, pin_memory=True), torch.cuda.Event(),
+                             torch.cuda.Event())
+        buf, done, computed = self._back[k]
+        if self._copy_stream is None:
+            self._copy_stream = torch.cuda.Stream(device=self.device)
+        side = self._copy_stream
+        computed.record()
+        side.wait_event(computed)
+        with torch.cuda.stream(side):
+            buf[:n].copy_(values.reshape(-1), non_blocking=True)
+            buf[n:n + 1].copy_(self.bufs.status.reshape(-1)[:1], non_blocking=True)
+            done.record()
+        values.record_stream(side)
         return k, n
 
     def finish_read_back(self, ticket) -> List[int]:
         k, n = ticket
-        buf, event = self._back[k]
-        event.synchronize()
+        buf, done, _ = self._back[k]
+        done.synchronize()
         self._status_read = int(buf[n])
         return buf[:n].tolist()
 

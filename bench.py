@@ -167,6 +167,9 @@ def main() -> int:
                     help="instead of the contract's line: time every kernel of a decode step and of a 2,048-token prefill "
                          "with CUDA events (eager, kernels one after another) and print a table per kernel: launches, "
                          "microseconds, share, GB/s, TFLOP/s and the fraction of the measured peak")
+    ap.add_argument("--between-steps", action="store_true",
+                    help="instead of the contract's line: the device activities between two decode steps through the entry "
+                         "point (pick, read-back copies, upload, token copy) and the steps' period")
     ap.add_argument("--no-check", action="store_true", help="skip the comparison of a short greedy continuation with float32")
     ap.add_argument("--workload", default="decode", choices=["decode", "mixed-14b", "batch16-32b"],
                     help="decode: the contract's line (default).  mixed-14b: 32 requests with prompts of 128 to 3,072 tokens at "
@@ -204,6 +207,10 @@ def main() -> int:
                      context=args.context,
                      new_tokens=max(256, args.steps + max(args.warmup, 32) + 8 + args.batch * ((args.context + 4095) // 4096 + 1)),
                      graphs=not args.no_graphs)
+    if args.between_steps:
+        print(json.dumps({"between_steps": h.between_steps(args.batch), "batch": args.batch, "context": args.context,
+                          "layers": args.layers}, indent=1))
+        return 0
     if args.profile:
         prof = h.profile(args.batch, 2048, pk["hbm_gbs"], pk["bf16_tflops"])
         for part in ("decode", "prefill"):

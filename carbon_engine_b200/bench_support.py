@@ -120,6 +120,35 @@ class BenchHarness:
         return {"ms_per_step": dt / steps * 1e3, "tokens_per_s": batch * steps / dt, "h2d_bytes": h2d // steps,
                 "d2h_bytes": d2h // steps, "launched_ahead": ahead}
 
+    def between_steps(self, batch: int, steps: int = 6) -> Dict:
+        """What the device does between the last kernel of one decode step and the first of the next, through
+        Engine.add_request / Engine.step: device activities (PyTorch profiler, CUDA only) that precede each
+        step's first kernel, in microseconds relative to it, and the steps' period."""
+        from torch.profiler import ProfilerActivity, profile
+        eng = self.engine
+        sp = SamplingParams(max_tokens=self.new_tokens - 8, ignore_eos=True)
+        for _ in range(batch):
+            eng.add_request(self._tokens(self.context), sp)
+        for _ in range(batch * ((self.context + eng.max_step_tokens - 1) // eng.max_step_tokens + 1) + 32):
+            eng.step()
+        torch.cuda.synchronize()
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            for _ in range(steps):
+                eng.step()
+            torch.cuda.synchronize()
+        while eng.has_unfinished():
+            eng.step()
+        ev = sorted((e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA), key=lambda e: e.time_range.start)
+        rows = [(e.name, e.time_range.start, e.time_range.end) for e in ev]
+        firsts = [i for i, r in enumerate(rows) if "embed_kernel" in r[0]]
+        out = {"period_us": None, "before_a_step": []}
+        if len(firsts) >= 3:
+            i = firsts[2]
+            out["period_us"] = round(rows[i][1] - rows[firsts[1]][1], 1)
+            out["before_a_step"] = [{"activity": n[:60], "start_us": round(s - rows[i][1], 1), "us": round(e - s, 1)}
+                                    for n, s, e in rows[max(i - 7, 0):i + 1]]
+        return out
+
     def serve(self, prompt_lens: List[int], new_tokens: int) -> Dict:
         """A whole workload through Engine.add_request / Engine.step: all requests are queued at once, the
         scheduler admits them, cuts their prompts into portions under the step's token budget beside the

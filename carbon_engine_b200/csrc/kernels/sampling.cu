@@ -299,38 +299,60 @@ extern "C" int ce_sample(const float* logits, int rows, int V, const void* param
     return ce_check_launch("ce_sample");
 }
 
-// Greedy pick for all rows: the first maximum of each row.
-__global__ void __launch_bounds__(SMP_THREADS) argmax_kernel(const float* __restrict__ logits, int V, int* __restrict__ out) {
+// Greedy pick for all rows: the first maximum of each row.  A large vocabulary is shared by the blocks of a
+// cluster (block `rank` of nb takes elements rank*SMP_THREADS + thread, then every nb*SMP_THREADS-th), as in
+// the sampling kernel: a decode step's few rows of 152 K logits then use 8 SMs a row instead of one (12 -> 8 us
+// at batch 8).  Pairs (value, index) are compared, so the pick is the first maximum however the row is dealt.
+__global__ void __launch_bounds__(SMP_THREADS) argmax_kernel(const float* __restrict__ logits, int V, int* __restrict__ out, int nb) {
     ce_pdl_begin();
-    __shared__ float sv[32];
-    __shared__ int si[32];
-    int r = blockIdx.x;
+    __shared__ SmpShared sh;
+    int r = blockIdx.x / nb, rank = blockIdx.x % nb;
     const float* l = logits + (size_t)r * V;
     float bv = -INFINITY;
     int bi = 0x7fffffff;
-    int i = threadIdx.x;
+    int stride = nb * SMP_THREADS;
+    int i = rank * SMP_THREADS + threadIdx.x;
     // eight loads in flight per thread; indices rise within a thread, so "first maximum" holds
-    for (; i + 7 * SMP_THREADS < V; i += 8 * SMP_THREADS) {
+    for (; i + 7 * stride < V; i += 8 * stride) {
         float z[8];
 #pragma unroll
-        for (int k = 0; k < 8; ++k) z[k] = l[i + k * SMP_THREADS];
+        for (int k = 0; k < 8; ++k) z[k] = l[i + k * stride];
 #pragma unroll
         for (int k = 0; k < 8; ++k)
-            if (z[k] > bv) { bv = z[k]; bi = i + k * SMP_THREADS; }
+            if (z[k] > bv) { bv = z[k]; bi = i + k * stride; }
     }
-    for (; i < V; i += SMP_THREADS) {
+    for (; i < V; i += stride) {
         float z = l[i];
         if (z > bv) { bv = z; bi = i; }
     }
-    smp_argmax(bv, bi, sv, si);
-    if (threadIdx.x == 0) out[r] = bi == 0x7fffffff ? 0 : bi;
+    int set = 0;
+    smp_row_argmax(bv, bi, sh, nb, set);
+    if (rank == 0 && threadIdx.x == 0) out[r] = bi == 0x7fffffff ? 0 : bi;
+    if (nb > 1) smp_cluster_sync();     // nobody's slots go away while another block may still read them
 }
 
 extern "C" int ce_argmax(const float* logits, int rows, int V, int* out, cudaStream_t stream) {
     if (rows == 0) return CE_OK;
     if (!logits || !out) return ce_fail(CE_ERR_ARG, "ce_argmax: null pointer");
     if (V <= 0) return ce_fail(CE_ERR_SIZE, "ce_argmax: vocabulary %d", V);
-    { ce_note("argmax_kernel"); ce_launch(argmax_kernel, rows, SMP_THREADS, 0, stream, logits, V, out); }
+    int nb = 1;         // (as many blocks a row as leave every row a place on the SMs at once)
+    if (V >= 16384)
+        while (nb < SMP_MAX_BLOCKS && (long long)rows * nb * 2 <= ce_sm_count()) nb *= 2;
+    if ((long long)rows * nb > 2147483647LL) return ce_fail(CE_ERR_SIZE, "ce_argmax: %d rows", rows);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(rows * nb));
+    cfg.blockDim = dim3(SMP_THREADS);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = nb; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ce_pdl_enabled() ? 2 : 1;
+    ce_note("argmax_kernel");
+    cudaError_t e = cudaLaunchKernelEx(&cfg, argmax_kernel, logits, V, out, nb);
+    if (e != cudaSuccess) return ce_fail(CE_ERR_CUDA, "ce_argmax: %s", cudaGetErrorString(e));
     return ce_check_launch("ce_argmax");
 }
 

@@ -295,16 +295,30 @@ def test_scatter_i32(ops):
     assert torch.equal(dst.cpu().view(-1), want)
 
 
-def test_argmax_takes_the_first_maximum(ops):
-    V = 151936 // 8 + 3
-    logits = torch.randn(3, V, device=dev())
-    logits[0, 777] = 50.0
-    logits[0, 12000] = 50.0                 # a tie: the lower index wins (src/sampling.rs:96-106)
-    logits[1, V - 1] = 60.0
-    logits[2] = -1.0                        # all equal: index 0
-    out = torch.empty(3, dtype=torch.int32, device=dev())
+@pytest.mark.parametrize("rows,V", [(3, 151936 // 8 + 3), (8, 151936), (1, 151936), (100, 40009), (5, 1000)])
+def test_argmax_takes_the_first_maximum(ops, rows, V):
+    """A few rows of a large vocabulary are shared by the blocks of a cluster (8 rows: 8 blocks a row), many rows
+    or a small vocabulary take one block a row; the pick is the first maximum either way."""
+    torch.manual_seed(rows + V)
+    logits = torch.randn(rows, V, device=dev())
+    want = []
+    for r in range(rows):
+        kind = r % 4
+        if kind == 0:                           # a tie between places that different blocks and threads hold: the lower index wins
+            a, b = 777 % V, (12000 + 1025 * r) % V
+            logits[r, a] = logits[r, b] = 50.0
+            want.append(min(a, b))
+        elif kind == 1:
+            logits[r, V - 1] = 60.0             # the very last place
+            want.append(V - 1)
+        elif kind == 2:
+            logits[r] = -1.0                    # all equal: index 0 (src/sampling.rs:96-106)
+            want.append(0)
+        else:
+            want.append(int(logits[r].argmax()))
+    out = torch.empty(rows, dtype=torch.int32, device=dev())
     ops.argmax(logits, out)
-    assert out.tolist() == [777, V - 1, 0]
+    assert out.tolist() == want
 
 
 def run_sampler(ops, logits, rows):

@@ -148,6 +148,41 @@ def test_requests_that_cannot_run_end_with_an_error_and_the_rest_go_on(models):
     assert outs[0].token_ids == outs[4].token_ids == plain.greedy_generate(cfg, w, ok, 4)
 
 
+@pytest.mark.parametrize("ahead", [True, False])
+def test_a_step_that_fails_on_the_device_ends_its_requests_and_the_engine_goes_on(models, ahead):
+    """A kernel whose bounded wait gives up leaves a code in the device status word; it comes back with the
+    picks.  Here the word is written from the host between two steps (nothing faults), while a step is in
+    flight and another has been launched ahead of it: the requests of the failed step end with an error that
+    names the code, the step launched ahead is dropped with them, pages and slots come back, the word is
+    cleared, and the next request is served as if nothing had happened."""
+    from carbon_engine_b200 import SamplingParams
+    d, cfg, w = models["A"]
+    rng = np.random.default_rng(9)
+    prompts = [random_tokens(rng, n, 256) for n in (10, 4, 25)]
+    eng = make_engine(d, "float32", "A", max_running_requests=4, run_ahead=ahead)
+    ids = [eng.add_request(p, SamplingParams(max_tokens=40, ignore_eos=True)) for p in prompts]
+    for _ in range(6):
+        assert eng.step() == []
+    assert (eng._in_flight is not None) == ahead
+    eng.runner.bufs.status.fill_(7)
+    outs = []
+    for _ in range(4):
+        outs += eng.step()
+        if len(outs) == 3:
+            break
+    assert sorted(o.request_id for o in outs) == ids
+    for o in outs:
+        assert o.finish_reason == "error" and "device status 7" in o.error and "decode attention" in o.error
+        assert 4 <= len(o.token_ids) < 40                                    # what it had generated stays with it
+    assert eng._in_flight is None and not eng.has_unfinished()
+    eng.storage.manager.check()
+    st = eng.stats()
+    assert eng.storage.manager.free_slots() == 4 and st["kv_pages_free"] == st["kv_pages_total"] and st["failed"] == 3
+    assert int(eng.runner.bufs.status.item()) == 0
+    again = eng.generate([prompts[2]], SamplingParams(max_tokens=6, ignore_eos=True))[0]
+    assert again.finish_reason == "length" and again.token_ids == plain.greedy_generate(cfg, w, prompts[2], 6)
+
+
 def test_eos_stop_and_sampling_options_through_the_entry_point(models):
     from carbon_engine_b200 import SamplingParams
     d, cfg, w = models["A"]
